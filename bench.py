@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Headline benchmark: int4 group-32 dequant-GEMV, K=4096 -> N=14336 (Llama-3-8B FFN up-projection
+shape), f16 block scales, bf16 activations, M decode tokens (default 1).
+
+A *step* is one decode pass over LAYERS distinct weight matrices of that shape (default 32, about
+1.06 GB, so every launch streams weights that are not in the 126 MB L2), replayed from one CUDA
+graph.  `value` is the whole-job HBM stream rate in TB/s: algorithmic bytes (packed nibbles + f16
+scales + activations in + bf16 results out) divided by device time.  With N GPUs every rank owns
+its own LAYERS matrices (column-parallel shards never exchange data on this path), so scaling is
+weak and the aggregate is the sum over ranks.
+
+    python bench.py --gpus 1 --steps 50 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference        # the CPU restatement of tang-infer on the host cores
+
+The JSON line also carries: `e2e` (the same rate through the reference-shaped call q4_matvec with
+HOST vectors, copies inside the timed region), `roofline` (dominant kernel vs measured HBM peak),
+`cpu_baseline` (the oracle port on a bounded sample), `decode` (Llama-3-8B-shaped decode step,
+tokens/s, when --decode is given), `clocks`, `gpu_launches`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_OUT, K_IN, GROUP = 14336, 4096, 32
+METRIC, UNIT = "int4_gemv_hbm_tbps", "TB/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# capture summarised in profiles/ (None until a capture exists for the current kernel).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def algorithmic_bytes(m: int) -> int:
+    """Bytes one launch has to move: nibbles + f16 scales + bf16 activations in + bf16 results out."""
+    return N_OUT * K_IN // 2 + N_OUT * (K_IN // GROUP) * 2 + m * K_IN * 2 + m * N_OUT * 2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.lines, self.proc, self.thread = gpu_index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [l for (t, l) in self.lines if t0 <= t <= t1 + 0.2] or [l for (_, l) in self.lines]
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in rows:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_matvec_rate(scales_f16_bits, packed, m_x, threads: int, budget_s: float):
+    """Times the oracle's q4 matvec (f16 scales) on the host: returns (TB/s, reps, seconds)."""
+    import oracle
+
+    oracle.build()
+    x = m_x.astype(np.float64)
+    oracle.qmatmul(oracle.KIND_Q4_F16, scales_f16_bits, packed, N_OUT, K_IN, x, threads)  # warm
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        oracle.qmatmul(oracle.KIND_Q4_F16, scales_f16_bits, packed, N_OUT, K_IN, x, threads)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s:
+            break
+    return algorithmic_bytes(x.shape[0]) * reps / dt / 1e12, reps, dt
+
+
+def host_weight(seed: int):
+    rng = np.random.default_rng(seed)
+    packed = rng.integers(0, 256, (N_OUT, K_IN // 2), dtype=np.uint8)
+    scales = rng.uniform(0.002, 0.02, (N_OUT, K_IN // GROUP)).astype(np.float16).view(np.uint16)
+    return scales, packed
+
+
+def run_reference(args, rank: int) -> None:
+    """The reference's CPU implementation of the path (its restatement in oracle/, since the Rust
+    crate cannot be built here) on all host threads.  One step = --ref-sample matvecs."""
+    if rank != 0:
+        return
+    import oracle
+
+    oracle.build()
+    threads = oracle.max_threads()
+    scales, packed = host_weight(43)
+    rng = np.random.default_rng(44)
+    x = rng.standard_normal((args.m, K_IN)).astype(np.float32).astype(np.float64)
+    per_step = args.ref_sample
+    for _ in range(max(args.warmup, 1)):
+        oracle.qmatmul(oracle.KIND_Q4_F16, scales, packed, N_OUT, K_IN, x, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps * per_step):
+        oracle.qmatmul(oracle.KIND_Q4_F16, scales, packed, N_OUT, K_IN, x, threads)
+    dt = time.perf_counter() - t0
+    value = algorithmic_bytes(args.m) * args.steps * per_step / dt / 1e12
+    sample = f"{per_step} of the {args.layers} matvecs of a step per timed step, M={args.m}, {threads} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": workload_config(args),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(args) -> dict:
+    return {"workload": f"int4-g32/f16-scale dequant-GEMV K={K_IN} N={N_OUT} M={args.m} (BASELINE configs[1])",
+            "layers_per_step": args.layers, "m": args.m,
+            "l2": f"{args.layers} distinct weight matrices per step ({args.layers * algorithmic_bytes(args.m) / 1e6:.0f} MB) >> 126 MB L2",
+            "parallelism": f"replicated column shards x{args.gpus}, no data-path collective"}
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import torch
+
+    import tang_b200 as tb
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    stream = torch.cuda.Stream()
+    dev = tb.QuantComputeDevice(local_rank, stream=stream.cuda_stream)
+    L, m = args.layers, args.m
+
+    with torch.cuda.stream(stream):
+        gen = torch.Generator(device="cuda").manual_seed(43 + rank)
+        packed = torch.randint(0, 256, (L, N_OUT, K_IN // 2), dtype=torch.uint8, device="cuda", generator=gen)
+        scales = (torch.rand((L, N_OUT, K_IN // GROUP), device="cuda", generator=gen) * 0.018 + 0.002).half()
+        x = torch.randn((m, K_IN), device="cuda", generator=gen).bfloat16()
+        y = torch.empty((L, m, N_OUT), dtype=torch.bfloat16, device="cuda")
+    stream.synchronize()
+    L_ = dev._L
+    import ctypes as C
+
+    handles = []
+    for i in range(L):
+        h = C.c_void_p()
+        dev._check(L_.tq_qweight_wrap_device(dev._ctx, tb.Q4_F16, C.c_void_p(packed[i].data_ptr()),
+                                             C.c_void_p(scales[i].data_ptr()), N_OUT, K_IN, C.byref(h)))
+        handles.append(h)
+
+    def one_pass():
+        for i in range(L):
+            dev._check(L_.tq_qlinear(dev._ctx, handles[i], C.c_void_p(x.data_ptr()), tb.BF16, 0, m,
+                                     C.c_void_p(y[i].data_ptr()), tb.BF16, 0, None))
+
+    one_pass()          # eager once: sizes workspaces, sets kernel attributes
+    dev.sync()
+    dev.begin_capture()
+    one_pass()
+    graph = dev.end_capture()
+
+    # parity spot check against the oracle on rank 0 (256 output rows of layer 0)
+    parity = None
+    if rank == 0:
+        import oracle
+
+        oracle.build()
+        rows = 256
+        sc_h = scales[0, :rows].cpu().numpy().view(np.uint16)
+        pk_h = packed[0, :rows].cpu().numpy()
+        x_h = x.float().cpu().numpy().astype(np.float64)
+        want = oracle.qmatmul(oracle.KIND_Q4_F16, sc_h, pk_h, rows, K_IN, x_h, 0)
+        got = y[0, :, :rows].float().cpu().numpy().astype(np.float64)
+        rms = float(np.sqrt(np.mean(want * want)))
+        parity = float(np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-2 * rms)))
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    for _ in range(args.warmup):
+        graph.launch()
+    barrier()
+    launches0 = dev.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.perf_counter()
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        for _ in range(args.steps):
+            graph.launch()
+        ev1.record(stream)
+    barrier()
+    t_wall1 = time.perf_counter()
+    ms = ev0.elapsed_time(ev1)
+    gpu_launches = dev.launch_count - launches0
+
+    # ---- end to end: the reference-shaped host call, pinned host vectors, copies inside the timing
+    xh = torch.empty((m, K_IN), dtype=torch.bfloat16).pin_memory()
+    xh.copy_(x.cpu())
+    yh = torch.empty((m, N_OUT), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_pass():
+        for i in range(L):
+            dev._check(L_.tq_q_matvec_host(dev._ctx, handles[i], C.c_void_p(xh.data_ptr()), C.c_void_p(yh.data_ptr()),
+                                           tb.BF16, m))
+
+    e2e_steps = max(1, min(args.steps, 20))
+    e2e_pass()
+    barrier()
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_pass()
+        ev1.record(stream)
+    barrier()
+    e2e_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        bytes_launch = algorithmic_bytes(m)
+        ms_per_step = ms / args.steps
+        value = world * L * bytes_launch / (ms_per_step * 1e-3) / 1e12
+        e2e_value = world * L * bytes_launch / (e2e_ms / e2e_steps * 1e-3) / 1e12
+        peak, peak_kind = measured_peaks()
+        achieved = bytes_launch / (ms_per_step * 1e-3 / L) / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            import oracle
+
+            threads = oracle.max_threads()
+            sc_h = scales[0].cpu().numpy().view(np.uint16)
+            pk_h = packed[0].cpu().numpy()
+            v, reps, dt = cpu_matvec_rate(sc_h, pk_h, x.float().cpu().numpy(), threads, args.cpu_budget)
+            cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                   "sample": f"{reps} matvecs of one K={K_IN} N={N_OUT} matrix, M={m}, in {dt:.1f} s"}
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int4 weights x bf16 activations, f32 accumulate", "data": "synthetic",
+            "config": workload_config(args),
+            "pct_of_8tbps_nominal": 100.0 * value / world / 8.0,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_kind, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "kernel": "qgemm_mma_kernel<Q4_F16,NT>", "algorithmic_bytes_per_launch": bytes_launch,
+                         "avg_launch_us": ms_per_step * 1e3 / L},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": L * m * K_IN * 2,
+                    "d2h_bytes_per_step": L * m * N_OUT * 2, "steps": e2e_steps,
+                    "call": "tq_q_matvec_host (q4_matvec with host vectors), weights resident"},
+            "cpu_baseline": cpu, "gpu_launches": int(gpu_launches), "clocks": clocks,
+            "parity_max_rel_err_vs_oracle": parity,
+        }
+        print(json.dumps(out))
+    graph.free()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="decode tokens per GEMV (1..64)")
+    ap.add_argument("--layers", type=int, default=32, help="distinct weight matrices per step")
+    ap.add_argument("--cpu-budget", type=float, default=8.0, help="seconds of CPU baseline timing")
+    ap.add_argument("--ref-sample", type=int, default=4, help="matvecs per step of the reference arm")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        sys.exit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,75 @@
+"""ctypes loader for libtangq.so.  There is no fallback: a missing library is an ImportError-like
+failure the first time any operator is used."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libtangq.so")
+
+TQ_OK, TQ_EINVAL, TQ_ECUDA, TQ_ENCCL, TQ_ETIMEOUT, TQ_ENOMEM, TQ_EUNSUPPORTED = range(7)
+F32, BF16, F16, I8, U8, I32, F64 = range(7)
+Q4_F32, Q4_F16, Q8_F32, I8_ROW = range(4)
+
+_STATUS = {0: "TQ_OK", 1: "TQ_EINVAL", 2: "TQ_ECUDA", 3: "TQ_ENCCL", 4: "TQ_ETIMEOUT", 5: "TQ_ENOMEM",
+           6: "TQ_EUNSUPPORTED"}
+
+
+class TangqError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{_STATUS.get(status, status)}: {message}")
+        self.status = status
+
+
+_p, _sz, _i = C.c_void_p, C.c_size_t, C.c_int
+_pp = C.POINTER(C.c_void_p)
+
+# name -> (restype, argtypes); must list every symbol include/tangq.h declares
+PROTOTYPES = {
+    "tq_version": (_i, []),
+    "tq_ctx_create": (_i, [_i, _p, _pp]),
+    "tq_ctx_destroy": (_i, [_p]),
+    "tq_last_error": (C.c_char_p, [_p]),
+    "tq_sync": (_i, [_p]),
+    "tq_ctx_stream": (_p, [_p]),
+    "tq_buf_alloc": (_i, [_p, _sz, _pp]),
+    "tq_buf_free": (_i, [_p, _p]),
+    "tq_upload": (_i, [_p, _p, _p, _sz]),
+    "tq_download": (_i, [_p, _p, _p, _sz]),
+    "tq_memset": (_i, [_p, _p, _i, _sz]),
+    "tq_convert": (_i, [_p, _p, _i, _p, _i, _sz]),
+    "tq_qweight_from_blocks": (_i, [_p, _i, _p, _sz, _sz, _pp]),
+    "tq_qweight_from_arrays": (_i, [_p, _i, _p, _p, _sz, _sz, _pp]),
+    "tq_qweight_wrap_device": (_i, [_p, _i, _p, _p, _sz, _sz, _pp]),
+    "tq_qweight_free": (_i, [_p, _p]),
+    "tq_qweight_shape": (_i, [_p, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_i)]),
+    "tq_qweight_bytes": (_sz, [_p]),
+    "tq_dequantize": (_i, [_p, _p, _p, _p]),
+    "tq_qlinear": (_i, [_p, _p, _p, _i, _sz, _sz, _p, _i, _sz, _p]),
+    "tq_q_matvec_host": (_i, [_p, _p, _p, _p, _i, _sz]),
+    "tq_qlinear_set_config": (_i, [_p, _i, _i, _i]),
+    "tq_graph_begin": (_i, [_p]),
+    "tq_graph_end": (_i, [_p, _pp]),
+    "tq_graph_launch": (_i, [_p, _p]),
+    "tq_graph_free": (_i, [_p, _p]),
+    "tq_launch_count": (C.c_ulonglong, [_p]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the shared library and binds every prototype.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise TangqError(TQ_EUNSUPPORTED,
+                             f"{LIB_PATH} is missing; build it with `python -m tang_b200._build` (needs nvcc). "
+                             "There is no CPU fallback.")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib

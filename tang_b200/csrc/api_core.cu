@@ -1,0 +1,182 @@
+// Context, raw buffers and dtype conversion of the C ABI (include/tangq.h).
+#include <cuda_bf16.h>
+
+#include <cstring>
+#include <new>
+
+#include "internal.h"
+
+namespace tq {
+
+int ensure_xprep(tq_ctx* ctx, size_t bytes) {
+  if (ctx->xprep_bytes >= bytes) return TQ_OK;
+  if (ctx->xprep) {
+    TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    TQ_CUDA(ctx, cudaFree(ctx->xprep));
+    ctx->xprep = nullptr;
+    ctx->xprep_bytes = 0;
+  }
+  size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+  TQ_CUDA(ctx, cudaMalloc(&ctx->xprep, want));
+  ctx->xprep_bytes = want;
+  return TQ_OK;
+}
+
+int ensure_scratch(tq_ctx* ctx, size_t bytes) {
+  if (ctx->scratch_bytes >= bytes) return TQ_OK;
+  if (ctx->scratch) {
+    TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    TQ_CUDA(ctx, cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+  }
+  size_t want = bytes < (4u << 20) ? (4u << 20) : bytes;
+  TQ_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
+  ctx->scratch_bytes = want;
+  return TQ_OK;
+}
+
+__global__ void convert_kernel(const void* src, int sdt, void* dst, int ddt, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float v;
+    if (sdt == TQ_F32) v = reinterpret_cast<const float*>(src)[i];
+    else if (sdt == TQ_BF16) v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[i]);
+    else v = (float)reinterpret_cast<const double*>(src)[i];
+    if (ddt == TQ_F32) reinterpret_cast<float*>(dst)[i] = v;
+    else if (ddt == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(v);
+    else reinterpret_cast<double*>(dst)[i] = (double)v;
+  }
+}
+
+}  // namespace tq
+
+using namespace tq;
+
+extern "C" {
+
+int tq_version(void) { return 100; }
+
+int tq_ctx_create(int device, void* stream, tq_ctx** out) {
+  if (!out) return TQ_EINVAL;
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n <= 0 || device < 0 || device >= n) return TQ_ECUDA;
+  tq_ctx* ctx = new (std::nothrow) tq_ctx();
+  if (!ctx) return TQ_ENOMEM;
+  ctx->device = device;
+  auto bail = [&](int st) {
+    delete ctx;
+    return st;
+  };
+  if (cudaSetDevice(device) != cudaSuccess) return bail(TQ_ECUDA);
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return bail(TQ_ECUDA);
+  if (prop.major != 10) return bail(TQ_EUNSUPPORTED);  // kernels are built for sm_100a only
+  ctx->sm_count = prop.multiProcessorCount;
+  if (stream) {
+    ctx->stream = reinterpret_cast<cudaStream_t>(stream);
+  } else {
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(TQ_ECUDA);
+    ctx->owns_stream = true;
+  }
+  if (cudaMalloc(&ctx->dev_err, sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
+  *out = ctx;
+  return TQ_OK;
+}
+
+int tq_ctx_destroy(tq_ctx* ctx) {
+  if (!ctx) return TQ_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->xprep) cudaFree(ctx->xprep);
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->dev_err) cudaFree(ctx->dev_err);
+  if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return TQ_OK;
+}
+
+const char* tq_last_error(const tq_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+void* tq_ctx_stream(tq_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int tq_sync(tq_ctx* ctx) {
+  if (int st = bind(ctx)) return st;
+  TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  int code = 0;
+  TQ_CUDA(ctx, cudaMemcpy(&code, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+  if (code != 0) {
+    cudaMemset(ctx->dev_err, 0, sizeof(int));
+    return fail(ctx, TQ_ETIMEOUT, "a kernel gave up a bounded wait (device code %d)", code);
+  }
+  return TQ_OK;
+}
+
+int tq_buf_alloc(tq_ctx* ctx, size_t bytes, void** dev_out) {
+  if (int st = bind(ctx)) return st;
+  TQ_REQUIRE(ctx, dev_out != nullptr, "tq_buf_alloc: null output");
+  *dev_out = nullptr;
+  if (bytes == 0) bytes = 16;
+  cudaError_t e = cudaMalloc(dev_out, bytes);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    return fail(ctx, TQ_ENOMEM, "tq_buf_alloc: out of device memory (%zu bytes)", bytes);
+  }
+  TQ_CUDA(ctx, e);
+  return TQ_OK;
+}
+
+int tq_buf_free(tq_ctx* ctx, void* dev) {
+  if (int st = bind(ctx)) return st;
+  if (!dev) return TQ_OK;
+  TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  TQ_CUDA(ctx, cudaFree(dev));
+  return TQ_OK;
+}
+
+int tq_upload(tq_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
+  if (int st = bind(ctx)) return st;
+  if (bytes == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, dst_dev && src_host, "tq_upload: null pointer");
+  TQ_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return TQ_OK;
+}
+
+int tq_download(tq_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes) {
+  if (int st = bind(ctx)) return st;
+  if (bytes == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, dst_host && src_dev, "tq_download: null pointer");
+  TQ_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return TQ_OK;
+}
+
+int tq_memset(tq_ctx* ctx, void* dst_dev, int byte, size_t bytes) {
+  if (int st = bind(ctx)) return st;
+  if (bytes == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, dst_dev != nullptr, "tq_memset: null pointer");
+  TQ_CUDA(ctx, cudaMemsetAsync(dst_dev, byte, bytes, ctx->stream));
+  return TQ_OK;
+}
+
+int tq_convert(tq_ctx* ctx, const void* src_dev, int src_dtype, void* dst_dev, int dst_dtype, size_t n) {
+  if (int st = bind(ctx)) return st;
+  auto okdt = [](int d) { return d == TQ_F32 || d == TQ_BF16 || d == TQ_F64; };
+  TQ_REQUIRE(ctx, okdt(src_dtype) && okdt(dst_dtype), "tq_convert: dtypes must be f32, bf16 or f64");
+  if (n == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, src_dev && dst_dev, "tq_convert: null pointer");
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+  convert_kernel<<<blocks, 256, 0, ctx->stream>>>(src_dev, src_dtype, dst_dev, dst_dtype, n);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
+  return TQ_OK;
+}
+
+}  // extern "C"

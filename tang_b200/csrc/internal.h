@@ -1,0 +1,85 @@
+// Host-side internals shared by the translation units of libtangq.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "../../include/tangq.h"
+
+struct tq_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool owns_stream = false;
+  int* dev_err = nullptr;        // device status word written by kernels that give up a bounded wait
+  void* xprep = nullptr;         // activation staging for tq_qlinear (bf16 copy / 3-way f32 split)
+  size_t xprep_bytes = 0;
+  void* scratch = nullptr;       // general workspace (attention partials, host-call staging, ...)
+  size_t scratch_bytes = 0;
+  int sm_count = 148;
+  int cfg_wr = 0, cfg_wk = 0, cfg_stages = 0;  // tq_qlinear_set_config override
+  unsigned long long launches = 0;             // kernels launched through this context
+  bool capturing = false;                      // between tq_graph_begin and tq_graph_end
+  unsigned long long launches_at_capture = 0;
+  std::string last_error = "";
+};
+
+struct tq_qweight {
+  int kind = 0;
+  size_t rows = 0, cols = 0;
+  size_t kpad = 0;        // cols rounded up to a multiple of 32
+  uint8_t* payload = nullptr;
+  uint8_t* scales = nullptr;
+  size_t ldw = 0;         // payload row stride, bytes
+  size_t lds = 0;         // scale row stride, bytes (4 for per-row scales)
+  bool owns = false;
+};
+
+namespace tq {
+
+inline int fail(tq_ctx* ctx, int status, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->last_error = buf;
+  return status;
+}
+
+#define TQ_CUDA(ctx, expr)                                                                         \
+  do {                                                                                             \
+    cudaError_t e__ = (expr);                                                                      \
+    if (e__ != cudaSuccess)                                                                        \
+      return ::tq::fail((ctx), TQ_ECUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+  } while (0)
+
+#define TQ_REQUIRE(ctx, cond, ...)                                \
+  do {                                                            \
+    if (!(cond)) return ::tq::fail((ctx), TQ_EINVAL, __VA_ARGS__); \
+  } while (0)
+
+// Makes the device of `ctx` current for the calling thread.
+inline int bind(tq_ctx* ctx) {
+  if (!ctx) return TQ_EINVAL;
+  TQ_CUDA(ctx, cudaSetDevice(ctx->device));
+  return TQ_OK;
+}
+
+int ensure_xprep(tq_ctx* ctx, size_t bytes);
+int ensure_scratch(tq_ctx* ctx, size_t bytes);
+
+inline size_t dtype_size(int dt) {
+  switch (dt) {
+    case TQ_F32: case TQ_I32: return 4;
+    case TQ_BF16: case TQ_F16: return 2;
+    case TQ_I8: case TQ_U8: return 1;
+    case TQ_F64: return 8;
+    default: return 0;
+  }
+}
+
+}  // namespace tq

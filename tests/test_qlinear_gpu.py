@@ -1,0 +1,211 @@
+"""GPU parity of the quantised linear layer against the CPU oracle, through the C ABI.
+
+Bars (stated by the task): integer unpacking bit-exact; f32-accumulated results within 1e-3
+relative error (tests/util.py::rel_err, floor = 1% of the output RMS); bf16 outputs within 2e-2.
+"""
+import numpy as np
+import pytest
+
+from util import bf16_round, make_weight, rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-3
+TOL_BF16 = 2e-2
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import tang_b200
+
+    d = tang_b200.QuantComputeDevice(0)
+    yield d
+    d.close()
+
+
+def _upload(dev, kind, sc, pay, rows, cols):
+    return dev.upload_qarrays(kind, pay, sc, rows, cols)
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+@pytest.mark.parametrize("rows,cols", [(40, 256), (33, 100), (16, 32)])
+def test_unpack_bit_exact(dev, orc, kind, rows, cols):
+    rng = np.random.default_rng(100 + kind)
+    sc, pay = make_weight(rng, kind, rows, cols)
+    w = _upload(dev, kind, sc, pay, rows, cols)
+    deq, ints = dev.dequantize(w)
+    bpr = (cols + 31) // 32
+    if kind in (0, 1):
+        want_int = orc.unpack_q4(pay).reshape(rows, bpr * 32)[:, :cols]
+        s32 = sc if kind == 0 else sc.view(np.float16).astype(np.float32)
+        want = orc.dequantize_q4(s32.reshape(-1), pay.reshape(-1)).reshape(rows, bpr * 32)[:, :cols]
+    elif kind == 2:
+        want_int = pay.reshape(rows, bpr * 32)[:, :cols]
+        want = orc.dequantize_q8(sc.reshape(-1), pay.reshape(-1)).reshape(rows, bpr * 32)[:, :cols]
+    else:
+        want_int = pay
+        want = pay.astype(np.float32) * sc[:, None]
+    assert np.array_equal(ints, want_int)
+    assert np.array_equal(deq, want)          # (q as f32) * scale, one f32 rounding on both sides
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+def test_one_hot_probe_through_gemm(dev, orc, kind):
+    """x = unit vectors: y[m, n] must be EXACTLY q[n, k_m] * scale — the GEMM's own unpack, the
+    K permutation on the activation side and the scale lookup, all bit for bit."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(200 + kind)
+    rows, cols = 48, 256
+    sc, pay = make_weight(rng, kind, rows, cols)
+    w = _upload(dev, kind, sc, pay, rows, cols)
+    want, _ = dev.dequantize(w)
+    for k0 in range(0, cols, 64):
+        x = np.zeros((64, cols), np.float32)
+        x[np.arange(64), k0 + np.arange(64)] = 1.0
+        xb = dev.upload(bf16_round(x)[0], tb.BF16)
+        y = dev.qlinear(xb, w, 64).to_vec().reshape(64, rows)
+        dev.sync()
+        assert np.array_equal(y, want[:, k0:k0 + 64].T), (kind, k0)
+
+
+SHAPES = [(96, 256), (100, 160), (16, 4096), (257, 1024), (64, 100)]
+MS = [1, 3, 8, 9, 17, 33, 64, 70]
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+@pytest.mark.parametrize("rows,cols", SHAPES)
+def test_qlinear_matches_oracle_bf16_x(dev, orc, kind, rows, cols):
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(rows * 7 + cols + kind)
+    sc, pay = make_weight(rng, kind, rows, cols)
+    w = _upload(dev, kind, sc, pay, rows, cols)
+    for m in MS:
+        xbits, xf = bf16_round(rng.standard_normal((m, cols)).astype(np.float32))
+        want = orc.qmatmul(kind, sc, pay, rows, cols, xf.astype(np.float64))
+        xb = dev.upload(xbits, tb.BF16)
+        y32 = dev.qlinear(xb, w, m, tb.F32).to_vec().reshape(m, rows)
+        y16 = dev.qlinear(xb, w, m, tb.BF16).to_vec().reshape(m, rows)
+        dev.sync()
+        assert rel_err(y32, want) < TOL_F32, (kind, rows, cols, m)
+        y16f = (y16.astype(np.uint32) << 16).view(np.float32)
+        assert rel_err(y16f, want) < TOL_BF16, (kind, rows, cols, m)
+        assert np.array_equal(y16, bf16_round(y32)[0])   # bf16 output = RNE of the f32 result
+
+
+@pytest.mark.parametrize("kind", [0, 2, 3])
+def test_qlinear_f32_activations_are_exact_inputs(dev, orc, kind):
+    """f32 x is consumed as three bf16 terms, so the result must match the oracle fed the SAME f32
+    values (not their bf16 roundings) to f32-accumulation accuracy."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(300 + kind)
+    rows, cols = 200, 512
+    sc, pay = make_weight(rng, kind, rows, cols)
+    w = _upload(dev, kind, sc, pay, rows, cols)
+    for m in (1, 5, 21, 30):
+        x = rng.standard_normal((m, cols)).astype(np.float32)
+        want = orc.qmatmul(kind, sc, pay, rows, cols, x.astype(np.float64))
+        y = dev.qlinear(dev.upload(x), w, m).to_vec().reshape(m, rows)
+        assert rel_err(y, want) < 2e-5, (kind, m)
+
+
+def test_residual_and_strides(dev, orc):
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(5)
+    rows, cols, m = 80, 256, 4
+    sc, pay = make_weight(rng, 1, rows, cols)
+    w = _upload(dev, 1, sc, pay, rows, cols)
+    xbits, xf = bf16_round(rng.standard_normal((m, cols)).astype(np.float32))
+    res = rng.standard_normal((m, rows)).astype(np.float32)
+    want = orc.qmatmul(1, sc, pay, rows, cols, xf.astype(np.float64)) + res
+    rbuf = dev.upload(res)
+    y = dev.qlinear(dev.upload(xbits, tb.BF16), w, m, out=rbuf, residual=rbuf).to_vec().reshape(m, rows)
+    assert rel_err(y, want) < TOL_F32
+
+
+def test_reference_call_with_host_vectors(dev, orc):
+    """q4_matvec / q8_matvec as the reference declares them: host f64 in, host f64 out."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(9)
+    rows, cols = 576, 576                      # the reference's benchmark shape (cpu_training.rs:267-275)
+    wf = (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32)
+    x = rng.standard_normal(cols)
+    s8, v8 = orc.quantize_matrix_q8(wf, rows, cols)
+    s4, p4 = orc.quantize_matrix_q4(wf, rows, cols)
+    w8 = dev.upload_q8(tb.QuantizedQ8(s8.reshape(-1), v8.reshape(-1), (rows, cols)))
+    w4 = dev.upload_q4(tb.QuantizedQ4(s4.reshape(-1), p4.reshape(-1), (rows, cols)))
+    y8 = dev.q8_matvec(w8, x)
+    y4 = dev.q4_matvec(w4, x)
+    assert y8.dtype == np.float64 and y8.shape == (rows,)
+    x32 = x.astype(np.float32).astype(np.float64)   # the call narrows f64 activations to f32
+    assert rel_err(y8, orc.q8_matvec(s8, v8, rows, cols, x32)) < 2e-5
+    assert rel_err(y4, orc.q4_matvec(s4, p4, rows, cols, x32)) < 2e-5
+    assert rel_err(y4, orc.q4_matvec(s4, p4, rows, cols, x)) < TOL_F32   # and stays within the bar vs raw f64
+    # the reference's own 2x3 example (quantize.rs:327-354)
+    s, v = orc.quantize_matrix_q8([1, 2, 3, 4, 5, 6], 2, 3)
+    y = dev.q8_matvec(dev.upload_q8(tb.QuantizedQ8(s.reshape(-1), v.reshape(-1), (2, 3))), np.array([1.0, 0.5, -1.0]))
+    assert abs(y[0] + 1.0) < 0.15 and abs(y[1] - 0.5) < 0.15
+
+
+def test_argument_errors(dev, orc):
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(1)
+    sc, pay = make_weight(rng, 0, 32, 64)
+    w = _upload(dev, 0, sc, pay, 32, 64)
+    with pytest.raises(tb.TangqError):          # assert_eq!(x.len(), in_dim)  (quantize.rs:259-260)
+        dev.q4_matvec(w, np.zeros(63))
+    with pytest.raises(tb.TangqError):
+        dev.q8_matvec(w, np.zeros(64))          # wrong weight family
+    empty = dev.alloc(0, tb.BF16)
+    out = dev.qlinear(empty, w, 0)              # zero activation rows: no work, no error
+    assert out.n == 0
+    with pytest.raises(tb.TangqError):
+        dev.upload_qarrays(0, pay, sc, 0, 64)   # empty matrix
+
+
+# ------------------------------------------------------------------ benchmark-sized cases
+
+def test_config0_int8_gemv_full_size(dev, orc):
+    """int8 [4096, 4096], per-row f32 scale in [0.001, 0.01], x f32 N(0,1) — the CPU-runnable config."""
+    rng = np.random.default_rng(42)
+    rows = cols = 4096
+    sc, pay = make_weight(rng, 3, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    w = _upload(dev, 3, sc, pay, rows, cols)
+    y = dev.q8_matvec(w, x)
+    want = orc.qmatmul(3, sc, pay, rows, cols, x.astype(np.float64), threads=0)
+    assert rel_err(y, want) < TOL_F32
+    # native Q8Block layout of the same integers (f32 scale per 32 weights)
+    scb = np.repeat(sc[:, None], cols // 32, 1)
+    wb = _upload(dev, 2, scb, pay, rows, cols)
+    assert rel_err(dev.q8_matvec(wb, x), want) < TOL_F32
+
+
+@pytest.mark.parametrize("m", [1, 8, 32, 64])
+def test_config1_int4_full_size(dev, orc, m):
+    """int4 group-32, f16 scales, K=4096, N=14336, bf16 activations."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(43)
+    rows, cols = 14336, 4096
+    sc, pay = make_weight(rng, 1, rows, cols)
+    w = _upload(dev, 1, sc, pay, rows, cols)
+    xbits, xf = bf16_round(rng.standard_normal((m, cols)).astype(np.float32))
+    xb = dev.upload(xbits, tb.BF16)
+    y = dev.qlinear(xb, w, m).to_vec().reshape(m, rows)
+    # the oracle on every row for m <= 8, on a seeded sample of token rows beyond that
+    sel = np.arange(m) if m <= 8 else np.sort(rng.choice(m, 8, replace=False))
+    want = orc.qmatmul(1, sc, pay, rows, cols, xf[sel].astype(np.float64), threads=0)
+    assert rel_err(y[sel], want) < TOL_F32
+    # linearity (size-independent property): W(a+b) = Wa + Wb for bf16-exact a, b, a+b
+    a = np.round(rng.standard_normal((m, cols)) * 4) / 4
+    b = np.round(rng.standard_normal((m, cols)) * 4) / 4
+    ya = dev.qlinear(dev.upload(bf16_round(a)[0], tb.BF16), w, m).to_vec()
+    yb = dev.qlinear(dev.upload(bf16_round(b)[0], tb.BF16), w, m).to_vec()
+    yab = dev.qlinear(dev.upload(bf16_round(a + b)[0], tb.BF16), w, m).to_vec()
+    assert rel_err(yab, ya.astype(np.float64) + yb) < 1e-4
