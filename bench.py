@@ -199,7 +199,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     handles = []
     for i in range(L):
         h = C.c_void_p()
-        dev._check(L_.tq_qweight_wrap_device(dev._ctx, tb.Q4_F16, C.c_void_p(packed[i].data_ptr()),
+        dev._check(L_.tq_qweight_from_device_arrays(dev._ctx, tb.Q4_F16, C.c_void_p(packed[i].data_ptr()),
                                              C.c_void_p(scales[i].data_ptr()), N_OUT, K_IN, C.byref(h)))
         handles.append(h)
 

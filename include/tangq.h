@@ -91,10 +91,13 @@ TQ_API int tq_qweight_from_blocks(tq_ctx* ctx, int kind, const void* blocks_host
  * f32 for TQ_I8_ROW. */
 TQ_API int tq_qweight_from_arrays(tq_ctx* ctx, int kind, const void* payload_host, const void* scales_host, size_t rows,
                            size_t cols, tq_qweight** out);
-/* Wraps arrays already in HBM (same shapes as above; cols % 32 == 0; rows of both arrays must
- * start on 16-byte boundaries).  The handle does not own them. */
-TQ_API int tq_qweight_wrap_device(tq_ctx* ctx, int kind, const void* payload_dev, const void* scales_dev, size_t rows,
-                           size_t cols, tq_qweight** out);
+/* The same structure-of-arrays form, but already in HBM (payload 8-byte, scales 4-byte aligned).
+ * The arrays are read once and can be freed after the next tq_sync.
+ *
+ * All three constructors regroup the numbers into the library's device layout (16-row x 128-k
+ * fragment tiles, see csrc/qlayout.cuh); integer codes and scale bits are copied unchanged. */
+TQ_API int tq_qweight_from_device_arrays(tq_ctx* ctx, int kind, const void* payload_dev, const void* scales_dev,
+                                         size_t rows, size_t cols, tq_qweight** out);
 TQ_API int tq_qweight_free(tq_ctx* ctx, tq_qweight* w);
 TQ_API int tq_qweight_shape(const tq_qweight* w, size_t* rows, size_t* cols, int* kind);
 TQ_API size_t tq_qweight_bytes(const tq_qweight* w); /* payload + scale bytes one matvec has to stream */

@@ -41,7 +41,7 @@ PROTOTYPES = {
     "tq_convert": (_i, [_p, _p, _i, _p, _i, _sz]),
     "tq_qweight_from_blocks": (_i, [_p, _i, _p, _sz, _sz, _pp]),
     "tq_qweight_from_arrays": (_i, [_p, _i, _p, _p, _sz, _sz, _pp]),
-    "tq_qweight_wrap_device": (_i, [_p, _i, _p, _p, _sz, _sz, _pp]),
+    "tq_qweight_from_device_arrays": (_i, [_p, _i, _p, _p, _sz, _sz, _pp]),
     "tq_qweight_free": (_i, [_p, _p]),
     "tq_qweight_shape": (_i, [_p, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_i)]),
     "tq_qweight_bytes": (_sz, [_p]),

@@ -30,12 +30,11 @@ struct tq_ctx {
 struct tq_qweight {
   int kind = 0;
   size_t rows = 0, cols = 0;
-  size_t kpad = 0;        // cols rounded up to a multiple of 32
-  uint8_t* payload = nullptr;
-  uint8_t* scales = nullptr;
-  size_t ldw = 0;         // payload row stride, bytes
-  size_t lds = 0;         // scale row stride, bytes (4 for per-row scales)
-  bool owns = false;
+  size_t kpad = 0;             // cols rounded up to a multiple of 32
+  int n_rb = 0, n_kc = 0;      // 16-row blocks, 128-k chunks
+  uint8_t* tiles = nullptr;    // fragment tiles (csrc/qlayout.cuh), owned
+  size_t tile_bytes = 0;
+  float* row_scales = nullptr; // TQ_I8_ROW only, owned
 };
 
 namespace tq {

@@ -16,38 +16,106 @@ static inline bool is_q4(int kind) { return kind == TQ_Q4_F32 || kind == TQ_Q4_F
 static inline size_t scale_elem(int kind) { return kind == TQ_Q4_F16 ? 2 : 4; }
 
 // ---------------------------------------------------------------------------------------------
-// dequantize_q4 / dequantize_q8 (crates/tang-infer/src/quantize.rs:73-81,121-132) through the same
-// register dequantisers the GEMM uses, so a bit-exact check of this kernel's integers is a check
-// of the GEMM's unpack.  One thread per 8 consecutive k.
+// Repack: plain block arrays (payload [rows][ld_pay], scales [rows][ld_sc]) -> fragment tiles.
+// One thread per (tile, half, lane, block): it moves the eight weights of one lane-block and,
+// for t == 0, the block's scale.  Integer codes and scale bits are copied, never recomputed.
 // ---------------------------------------------------------------------------------------------
-__global__ void dequantize_kernel(const uint8_t* payload, const uint8_t* scales, size_t ldw, size_t lds, int kind,
-                                  size_t rows, size_t cols, size_t kpad, float* out, int8_t* ints) {
-  const size_t per_row = kpad / 8;
+__global__ void repack_kernel(const uint8_t* pay, const uint8_t* sc, size_t ld_pay, size_t ld_sc, int kind, size_t rows,
+                              size_t cols, int n_rb, int n_kc, uint8_t* tiles) {
+  const size_t total = (size_t)n_rb * n_kc * 2 * 32 * 4;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int j = idx & 3;
+  const int lane = (idx >> 2) & 31;
+  const int h = (idx >> 7) & 1;
+  const size_t tile_idx = idx >> 8;
+  const int kc = (int)(tile_idx % n_kc);
+  const size_t rb = tile_idx / n_kc;
+  const int g = lane >> 2, t = lane & 3;
+  const size_t row = rb * 16 + g + 8 * h;
+  const size_t k0 = (size_t)kc * kTileK + 32 * j + 8 * t;   // first of this thread's eight k
+  const size_t kblocks = (cols + 31) / 32;                   // blocks present per input row
+  const bool live = row < rows && (k0 / 32) < kblocks;
+  uint8_t* tile = tiles + tile_idx * qk_tile_bytes(kind);
+  if (kind == Q4_F32 || kind == Q4_F16) {
+    uint32_t w = 0x88888888u;  // eight zeros (stored q+8)
+    if (live) w = *reinterpret_cast<const uint32_t*>(pay + row * ld_pay + k0 / 2);
+    // nibble i of w is k0+i; output nibble order k0+{0,2,4,6,1,3,5,7}
+    uint32_t o = 0;
+#pragma unroll
+    for (int pos = 0; pos < 8; ++pos) {
+      const int src = pos < 4 ? 2 * pos : 2 * (pos - 4) + 1;
+      o |= ((w >> (4 * src)) & 0xFu) << (4 * pos);
+    }
+    *reinterpret_cast<uint32_t*>(tile + h * 512 + 16 * lane + 4 * j) = o;
+  } else {
+    uint2 w = make_uint2(0u, 0u);
+    if (live) {
+      if (kind == I8_ROW) {  // rows are exactly `cols` bytes: guard the tail byte by byte
+        uint8_t b[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) b[i] = (k0 + i < cols) ? pay[row * ld_pay + k0 + i] : 0;
+        w.x = b[0] | (b[1] << 8) | (b[2] << 16) | ((uint32_t)b[3] << 24);
+        w.y = b[4] | (b[5] << 8) | (b[6] << 16) | ((uint32_t)b[7] << 24);
+      } else {
+        w = *reinterpret_cast<const uint2*>(pay + row * ld_pay + k0);
+      }
+    }
+    // bytes k0..k0+7 -> [k0,k2,k4,k6][k1,k3,k5,k7]
+    const uint32_t even = prmt(w.x, w.y, 0x6420u), odd = prmt(w.x, w.y, 0x7531u);
+    const int pl = j >> 1;
+    *reinterpret_cast<uint2*>(tile + h * 1024 + pl * 512 + 16 * lane + 8 * (j & 1)) = make_uint2(even, odd);
+  }
+  if (t == 0 && kind != I8_ROW) {
+    const int off = qk_scale_offset(kind, g + 8 * h, j);
+    if (kind == Q4_F16) {
+      uint16_t v = 0;
+      if (live) v = *reinterpret_cast<const uint16_t*>(sc + row * ld_sc + 2 * (k0 / 32));
+      *reinterpret_cast<uint16_t*>(tile + off) = v;
+    } else {
+      uint32_t v = 0;
+      if (live) v = *reinterpret_cast<const uint32_t*>(sc + row * ld_sc + 4 * (k0 / 32));
+      *reinterpret_cast<uint32_t*>(tile + off) = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dequantize_q4 / dequantize_q8 (crates/tang-infer/src/quantize.rs:73-81,121-132) through the same
+// register dequantisers the GEMM uses, reading the fragment tiles: a bit-exact check of this
+// kernel's integers is a check of the repack and of the GEMM's unpack.  One thread per eight k.
+// ---------------------------------------------------------------------------------------------
+__global__ void dequantize_kernel(const uint8_t* tiles, const float* row_scales, int kind, size_t rows, size_t cols,
+                                  int n_kc, float* out, int8_t* ints) {
+  const size_t per_row = (size_t)n_kc * 16;  // eight-k units per row
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * per_row) return;
   const size_t row = idx / per_row, oct = idx % per_row;
-  const size_t k0 = oct * 8;
+  const int kc = (int)(oct / 16), j = (int)(oct % 16) / 4, t = (int)(oct % 4);
+  const size_t k0 = (size_t)kc * kTileK + 32 * j + 8 * t;
+  const int r = (int)(row % 16), h = r >> 3, g = r & 7, lane = 4 * g + t;
+  const uint8_t* tile = tiles + ((row / 16) * n_kc + kc) * qk_tile_bytes(kind);
   uint32_t v[4];
-  if (kind == TQ_Q4_F32 || kind == TQ_Q4_F16) {
-    dequant_q4_word(*reinterpret_cast<const uint32_t*>(payload + row * ldw + k0 / 2), v);
+  if (kind == Q4_F32 || kind == Q4_F16) {
+    dequant_q4_word(*reinterpret_cast<const uint32_t*>(tile + h * 512 + 16 * lane + 4 * j), v);
   } else {
-    const uint2 u = *reinterpret_cast<const uint2*>(payload + row * ldw + k0);
+    const uint2 u = *reinterpret_cast<const uint2*>(tile + h * 1024 + (j >> 1) * 512 + 16 * lane + 8 * (j & 1));
     dequant_i8_words(u.x, u.y, v);
   }
   float scale;
-  if (kind == TQ_I8_ROW) scale = reinterpret_cast<const float*>(scales)[row];
-  else if (kind == TQ_Q4_F16) scale = __half2float(*reinterpret_cast<const __half*>(scales + row * lds + 2 * (k0 / 32)));
-  else scale = *reinterpret_cast<const float*>(scales + row * lds + 4 * (k0 / 32));
+  if (kind == I8_ROW) scale = row_scales[row];
+  else if (kind == Q4_F16) scale = __half2float(*reinterpret_cast<const __half*>(tile + qk_scale_offset(kind, r, j)));
+  else scale = *reinterpret_cast<const float*>(tile + qk_scale_offset(kind, r, j));
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float lo = bf16_bits_to_float(v[i] & 0xFFFFu), hi = bf16_bits_to_float(v[i] >> 16);  // k0+i, k0+i+4
-    if (k0 + i < cols) {
-      if (out) out[row * cols + k0 + i] = lo * scale;
-      if (ints) ints[row * cols + k0 + i] = (int8_t)(int)lo;
+    const float lo = bf16_bits_to_float(v[i] & 0xFFFFu), hi = bf16_bits_to_float(v[i] >> 16);  // k0+2i, k0+2i+1
+    if (k0 + 2 * i < cols) {
+      if (out) out[row * cols + k0 + 2 * i] = lo * scale;
+      if (ints) ints[row * cols + k0 + 2 * i] = (int8_t)(int)lo;
     }
-    if (k0 + i + 4 < cols) {
-      if (out) out[row * cols + k0 + i + 4] = hi * scale;
-      if (ints) ints[row * cols + k0 + i + 4] = (int8_t)(int)hi;
+    if (k0 + 2 * i + 1 < cols) {
+      if (out) out[row * cols + k0 + 2 * i + 1] = hi * scale;
+      if (ints) ints[row * cols + k0 + 2 * i + 1] = (int8_t)(int)hi;
     }
   }
 }
@@ -105,9 +173,8 @@ struct QgConfig {
 static QgConfig choose_config(const tq_ctx* ctx, const tq_qweight* w, int mx) {
   QgConfig c;
   c.nt = mx <= 8 ? 1 : mx <= 16 ? 2 : mx <= 32 ? 4 : 8;
-  const int kind = w->kind;
   int wr = c.nt >= 4 ? 4 : 2;
-  while (wr > 1 && (long long)((w->rows + 16 * wr - 1) / (16 * wr)) < 2LL * ctx->sm_count) wr >>= 1;
+  while (wr > 1 && (long long)((w->n_rb + wr - 1) / wr) < 2LL * ctx->sm_count) wr >>= 1;
   c.wr = wr;
   c.wk = 8 / wr;
   if (c.nt == 8 && c.wk > 2) c.wk = 2;
@@ -117,9 +184,10 @@ static QgConfig choose_config(const tq_ctx* ctx, const tq_qweight* w, int mx) {
     c.wk = ctx->cfg_wk;
     c.stages = ctx->cfg_stages;
   }
+  while (c.wk > 1 && c.wk > w->n_kc) c.wk >>= 1;
   // shrink until the CTA fits in shared memory
-  while (qg_smem_bytes(kind, c.nt, c.wr, c.wk, c.stages, mx, (int)w->kpad) > 200 * 1024 && c.stages > 2) c.stages--;
-  while (qg_smem_bytes(kind, c.nt, c.wr, c.wk, c.stages, mx, (int)w->kpad) > 200 * 1024 && c.wk > 1) c.wk >>= 1;
+  while (qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.stages, mx) > 200 * 1024 && c.stages > 2) c.stages--;
+  while (qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.stages, mx) > 200 * 1024 && c.wk > 1) c.wk >>= 1;
   return c;
 }
 
@@ -128,17 +196,17 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
                         void* y, int y_dtype, size_t ldy, const float* residual) {
   QgConfig c = choose_config(ctx, w, mx);
   QGemmParams p;
-  p.payload = w->payload;
-  p.scales = w->scales;
+  p.tiles = w->tiles;
+  p.row_scales = w->row_scales;
   p.x = xs;
   p.y = y;
   p.residual = residual;
-  p.ldw = (long long)w->ldw;
-  p.lds = (long long)w->lds;
   p.ldx = (long long)ldxs;
   p.ldy = (long long)ldy;
   p.n_rows = (int)w->rows;
-  p.kpad = (int)w->kpad;
+  p.n_row_blocks = w->n_rb;
+  p.kc_total = w->n_kc;
+  p.kx = (int)w->kpad;
   p.mx = mx;
   p.m_out = mx / combine;
   p.combine = combine;
@@ -147,9 +215,9 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   p.wk = c.wk;
   p.stages = c.stages;
   p.err = ctx->dev_err;
-  const size_t smem = qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.stages, mx, p.kpad);
-  if (smem > 227 * 1024) return fail(ctx, TQ_EUNSUPPORTED, "tq_qlinear: K=%zu needs %zu bytes of shared memory", w->cols, smem);
-  dim3 grid((unsigned)((w->rows + 16 * c.wr - 1) / (16 * c.wr)));
+  const size_t smem = qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.stages, mx);
+  if (smem > 227 * 1024) return fail(ctx, TQ_EUNSUPPORTED, "tq_qlinear: launch needs %zu bytes of shared memory", smem);
+  dim3 grid((unsigned)((w->n_rb + c.wr - 1) / c.wr));
   dim3 block((unsigned)(32 * (c.wr * c.wk + 1)));
   cudaError_t e;
   switch (w->kind) {
@@ -179,53 +247,92 @@ static int make_weight(tq_ctx* ctx, int kind, size_t rows, size_t cols, tq_qweig
   w->rows = rows;
   w->cols = cols;
   w->kpad = (cols + 31) / 32 * 32;
-  w->ldw = is_q4(kind) ? w->kpad / 2 : w->kpad;
-  w->lds = kind == TQ_I8_ROW ? 4 : ((w->kpad / 32) * scale_elem(kind) + 15) / 16 * 16;
+  w->n_rb = (int)((rows + kTileRows - 1) / kTileRows);
+  w->n_kc = (int)((cols + kTileK - 1) / kTileK);
+  w->tile_bytes = (size_t)w->n_rb * w->n_kc * qk_tile_bytes(kind);
+  cudaError_t e = cudaMalloc(&w->tiles, w->tile_bytes);
+  if (e == cudaSuccess && kind == TQ_I8_ROW) e = cudaMalloc(&w->row_scales, rows * sizeof(float));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (w->tiles) cudaFree(w->tiles);
+    delete w;
+    return fail(ctx, e == cudaErrorMemoryAllocation ? TQ_ENOMEM : TQ_ECUDA, "weight allocation failed: %s",
+                cudaGetErrorString(e));
+  }
   *out = w;
   return TQ_OK;
 }
 
-static int alloc_weight(tq_ctx* ctx, tq_qweight* w) {
-  // 16 spare bytes: the scale-row bulk copy of the last row may read up to the padded row end
-  TQ_CUDA(ctx, cudaMalloc(&w->payload, w->rows * w->ldw + 16));
-  TQ_CUDA(ctx, cudaMalloc(&w->scales, w->rows * w->lds + 16));
-  w->owns = true;
+// Input strides of the plain arrays for a given kind.
+static void plain_strides(int kind, size_t cols, size_t* ld_pay, size_t* ld_sc) {
+  const size_t bpr = (cols + 31) / 32;
+  *ld_pay = kind == TQ_I8_ROW ? cols : is_q4(kind) ? bpr * 16 : bpr * 32;
+  *ld_sc = kind == TQ_I8_ROW ? 0 : bpr * scale_elem(kind);
+}
+
+// Repacks plain device arrays into w->tiles.
+static int repack_from_device(tq_ctx* ctx, tq_qweight* w, const uint8_t* pay, const uint8_t* sc) {
+  size_t ld_pay, ld_sc;
+  plain_strides(w->kind, w->cols, &ld_pay, &ld_sc);
+  const size_t n = (size_t)w->n_rb * w->n_kc * 256;
+  repack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(pay, sc, ld_pay, ld_sc, w->kind, w->rows, w->cols,
+                                                                     w->n_rb, w->n_kc, w->tiles);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
+  if (w->kind == TQ_I8_ROW)
+    TQ_CUDA(ctx, cudaMemcpyAsync(w->row_scales, sc, w->rows * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
   return TQ_OK;
 }
 
 extern "C" {
 
-int tq_qweight_from_arrays(tq_ctx* ctx, int kind, const void* payload_host, const void* scales_host, size_t rows,
-                           size_t cols, tq_qweight** out) {
+int tq_qweight_from_device_arrays(tq_ctx* ctx, int kind, const void* payload_dev, const void* scales_dev, size_t rows,
+                                  size_t cols, tq_qweight** out) {
   if (int st = bind(ctx)) return st;
-  TQ_REQUIRE(ctx, payload_host && scales_host, "tq_qweight_from_arrays: null array");
+  TQ_REQUIRE(ctx, payload_dev && scales_dev, "tq_qweight_from_device_arrays: null array");
+  TQ_REQUIRE(ctx, ((uintptr_t)payload_dev & 7) == 0 && ((uintptr_t)scales_dev & 3) == 0,
+             "tq_qweight_from_device_arrays: payload must be 8-byte and scales 4-byte aligned");
+  TQ_REQUIRE(ctx, kind == TQ_I8_ROW || kind == TQ_Q4_F32 || kind == TQ_Q8_F32 || ((cols + 31) / 32) % 2 == 0 || rows == 1,
+             "tq_qweight_from_device_arrays: f16 scale rows must stay 4-byte aligned (even block count)");
   tq_qweight* w = nullptr;
   if (int st = make_weight(ctx, kind, rows, cols, &w)) return st;
-  if (int st = alloc_weight(ctx, w)) {
+  if (int st = repack_from_device(ctx, w, static_cast<const uint8_t*>(payload_dev), static_cast<const uint8_t*>(scales_dev))) {
     tq_qweight_free(ctx, w);
     return st;
   }
-  const size_t bpr = w->kpad / 32;
-  // payload: host rows are whole blocks (Q4/Q8) or exactly `cols` bytes (I8_ROW)
-  const size_t host_ldw = kind == TQ_I8_ROW ? cols : w->ldw;
-  cudaError_t e = cudaSuccess;
-  if (host_ldw != w->ldw) e = cudaMemsetAsync(w->payload, 0, rows * w->ldw, ctx->stream);
-  if (e == cudaSuccess)
-    e = cudaMemcpy2DAsync(w->payload, w->ldw, payload_host, host_ldw, host_ldw, rows, cudaMemcpyHostToDevice, ctx->stream);
-  if (e == cudaSuccess) {
-    if (kind == TQ_I8_ROW) {
-      e = cudaMemcpyAsync(w->scales, scales_host, rows * 4, cudaMemcpyHostToDevice, ctx->stream);
-    } else {
-      const size_t host_lds = bpr * scale_elem(kind);
-      if (host_lds != w->lds) e = cudaMemsetAsync(w->scales, 0, rows * w->lds, ctx->stream);
-      if (e == cudaSuccess)
-        e = cudaMemcpy2DAsync(w->scales, w->lds, scales_host, host_lds, host_lds, rows, cudaMemcpyHostToDevice, ctx->stream);
-    }
-  }
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-  if (e != cudaSuccess) {
-    tq_qweight_free(ctx, w);
-    return fail(ctx, TQ_ECUDA, "tq_qweight_from_arrays: %s", cudaGetErrorString(e));
+  *out = w;
+  return TQ_OK;
+}
+
+int tq_qweight_from_arrays(tq_ctx* ctx, int kind, const void* payload_host, const void* scales_host, size_t rows,
+                           size_t cols, tq_qweight** out) {
+  if (int st = bind(ctx)) return st;
+  TQ_REQUIRE(ctx, out != nullptr, "null output handle");
+  *out = nullptr;
+  TQ_REQUIRE(ctx, payload_host && scales_host, "tq_qweight_from_arrays: null array");
+  TQ_REQUIRE(ctx, kind >= TQ_Q4_F32 && kind <= TQ_I8_ROW, "unknown weight kind %d", kind);
+  TQ_REQUIRE(ctx, rows > 0 && cols > 0, "empty weight matrix");
+  size_t ld_pay, ld_sc;
+  plain_strides(kind, cols, &ld_pay, &ld_sc);
+  const size_t pay_bytes = rows * ld_pay, sc_bytes = kind == TQ_I8_ROW ? rows * 4 : rows * ld_sc;
+  uint8_t *dpay = nullptr, *dsc = nullptr;
+  cudaError_t e = cudaMalloc(&dpay, pay_bytes + 16);
+  if (e == cudaSuccess) e = cudaMalloc(&dsc, sc_bytes + 16);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(dpay, payload_host, pay_bytes, cudaMemcpyHostToDevice, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(dsc, scales_host, sc_bytes, cudaMemcpyHostToDevice, ctx->stream);
+  int st = TQ_OK;
+  tq_qweight* w = nullptr;
+  if (e != cudaSuccess) st = fail(ctx, TQ_ECUDA, "tq_qweight_from_arrays: %s", cudaGetErrorString(e));
+  if (st == TQ_OK) st = make_weight(ctx, kind, rows, cols, &w);
+  if (st == TQ_OK) st = repack_from_device(ctx, w, dpay, dsc);
+  if (st == TQ_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) st = fail(ctx, TQ_ECUDA, "repack failed");
+  else cudaStreamSynchronize(ctx->stream);
+  if (dpay) cudaFree(dpay);
+  if (dsc) cudaFree(dsc);
+  if (st != TQ_OK) {
+    if (w) tq_qweight_free(ctx, w);
+    cudaGetLastError();
+    return st;
   }
   *out = w;
   return TQ_OK;
@@ -248,33 +355,12 @@ int tq_qweight_from_blocks(tq_ctx* ctx, int kind, const void* blocks_host, size_
   return tq_qweight_from_arrays(ctx, kind, payload.data(), scales.data(), rows, cols, out);
 }
 
-int tq_qweight_wrap_device(tq_ctx* ctx, int kind, const void* payload_dev, const void* scales_dev, size_t rows,
-                           size_t cols, tq_qweight** out) {
-  if (int st = bind(ctx)) return st;
-  TQ_REQUIRE(ctx, payload_dev && scales_dev, "tq_qweight_wrap_device: null array");
-  TQ_REQUIRE(ctx, cols % 32 == 0, "tq_qweight_wrap_device: cols must be a multiple of 32");
-  tq_qweight* w = nullptr;
-  if (int st = make_weight(ctx, kind, rows, cols, &w)) return st;
-  const size_t dense_lds = kind == TQ_I8_ROW ? 4 : (cols / 32) * scale_elem(kind);
-  if (dense_lds != w->lds || ((uintptr_t)payload_dev & 15) || ((uintptr_t)scales_dev & 15)) {
-    delete w;
-    return fail(ctx, TQ_EINVAL, "tq_qweight_wrap_device: rows of both arrays must start on 16-byte boundaries");
-  }
-  w->payload = const_cast<uint8_t*>(static_cast<const uint8_t*>(payload_dev));
-  w->scales = const_cast<uint8_t*>(static_cast<const uint8_t*>(scales_dev));
-  w->owns = false;
-  *out = w;
-  return TQ_OK;
-}
-
 int tq_qweight_free(tq_ctx* ctx, tq_qweight* w) {
   if (!w) return TQ_OK;
   if (int st = bind(ctx)) return st;
-  if (w->owns) {
-    cudaStreamSynchronize(ctx->stream);
-    if (w->payload) cudaFree(w->payload);
-    if (w->scales) cudaFree(w->scales);
-  }
+  cudaStreamSynchronize(ctx->stream);
+  if (w->tiles) cudaFree(w->tiles);
+  if (w->row_scales) cudaFree(w->row_scales);
   delete w;
   return TQ_OK;
 }
@@ -299,9 +385,9 @@ int tq_dequantize(tq_ctx* ctx, const tq_qweight* w, float* out_dev, int8_t* ints
   if (int st = bind(ctx)) return st;
   TQ_REQUIRE(ctx, w != nullptr, "tq_dequantize: null weight");
   TQ_REQUIRE(ctx, out_dev || ints_dev, "tq_dequantize: nothing to write");
-  const size_t n = w->rows * (w->kpad / 8);
-  dequantize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(w->payload, w->scales, w->ldw, w->lds, w->kind,
-                                                                         w->rows, w->cols, w->kpad, out_dev, ints_dev);
+  const size_t n = w->rows * (size_t)w->n_kc * 16;
+  dequantize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(w->tiles, w->row_scales, w->kind, w->rows,
+                                                                         w->cols, w->n_kc, out_dev, ints_dev);
   ctx->launches++;
   TQ_CUDA(ctx, cudaGetLastError());
   return TQ_OK;

@@ -218,11 +218,13 @@ class QuantComputeDevice:
                                                    C.c_void_p(sc.ctypes.data), rows, cols, C.byref(h)))
         return self._wrap_q(h)
 
-    def wrap_qarrays(self, kind: int, payload: Buffer, scales: Buffer, rows: int, cols: int) -> QBuffer:
+    def qweight_from_device(self, kind: int, payload_ptr: int, scales_ptr: int, rows: int, cols: int) -> QBuffer:
+        """Builds a weight from plain block arrays that already live in HBM (read once, see
+        ``tq_qweight_from_device_arrays``)."""
         h = C.c_void_p()
-        self._check(self._L.tq_qweight_wrap_device(self._ctx, kind, C.c_void_p(payload.ptr), C.c_void_p(scales.ptr),
-                                                   rows, cols, C.byref(h)))
-        return self._wrap_q(h, keep=(payload, scales))
+        self._check(self._L.tq_qweight_from_device_arrays(self._ctx, kind, C.c_void_p(payload_ptr),
+                                                          C.c_void_p(scales_ptr), rows, cols, C.byref(h)))
+        return self._wrap_q(h)
 
     def dequantize(self, w: QBuffer):
         """``dequantize_q4`` / ``dequantize_q8``: returns (f32 [rows, cols], signed integers i8 [rows, cols])."""
