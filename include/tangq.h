@@ -125,8 +125,9 @@ TQ_API int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x
 TQ_API int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m);
 
 /* Launch-shape override for tq_qlinear, for tuning runs: rows-per-CTA = 16*wr, K slices = wk,
- * ring depth = stages.  Zero restores the built-in choice. */
-TQ_API int tq_qlinear_set_config(tq_ctx* ctx, int wr, int wk, int stages);
+ * ring depth = stages, 128-k tiles per warp and stage = tiles_per_warp.  wr = 0 restores the
+ * built-in choice. */
+TQ_API int tq_qlinear_set_config(tq_ctx* ctx, int wr, int wk, int stages, int tiles_per_warp);
 
 /* ---- CUDA graphs ------------------------------------------------------------------------------
  * CudaComputeDevice::begin_capture / end_capture (crates/tang-compute/src/cuda.rs:344-356): every

@@ -48,7 +48,7 @@ PROTOTYPES = {
     "tq_dequantize": (_i, [_p, _p, _p, _p]),
     "tq_qlinear": (_i, [_p, _p, _p, _i, _sz, _sz, _p, _i, _sz, _p]),
     "tq_q_matvec_host": (_i, [_p, _p, _p, _p, _i, _sz]),
-    "tq_qlinear_set_config": (_i, [_p, _i, _i, _i]),
+    "tq_qlinear_set_config": (_i, [_p, _i, _i, _i, _i]),
     "tq_graph_begin": (_i, [_p]),
     "tq_graph_end": (_i, [_p, _pp]),
     "tq_graph_launch": (_i, [_p, _p]),

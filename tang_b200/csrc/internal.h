@@ -20,7 +20,7 @@ struct tq_ctx {
   void* scratch = nullptr;       // general workspace (attention partials, host-call staging, ...)
   size_t scratch_bytes = 0;
   int sm_count = 148;
-  int cfg_wr = 0, cfg_wk = 0, cfg_stages = 0;  // tq_qlinear_set_config override
+  int cfg_wr = 0, cfg_wk = 0, cfg_stages = 0, cfg_tpw = 0;  // tq_qlinear_set_config override
   unsigned long long launches = 0;             // kernels launched through this context
   bool capturing = false;                      // between tq_graph_begin and tq_graph_end
   unsigned long long launches_at_capture = 0;

@@ -164,7 +164,7 @@ static cudaError_t launch_nt(int nt, const QGemmParams& p, dim3 grid, dim3 block
 }
 
 struct QgConfig {
-  int nt, wr, wk, stages;
+  int nt, wr, wk, tpw, stages;
 };
 
 // Launch shape: enough CTAs to cover the SMs about twice with every CTA resident at once (the
@@ -179,15 +179,19 @@ static QgConfig choose_config(const tq_ctx* ctx, const tq_qweight* w, int mx) {
   c.wk = 8 / wr;
   if (c.nt == 8 && c.wk > 2) c.wk = 2;
   c.stages = 4;
+  c.tpw = 1;
   if (ctx->cfg_wr > 0) {
     c.wr = ctx->cfg_wr;
     c.wk = ctx->cfg_wk;
     c.stages = ctx->cfg_stages;
+    c.tpw = ctx->cfg_tpw > 0 ? ctx->cfg_tpw : 1;
   }
   while (c.wk > 1 && c.wk > w->n_kc) c.wk >>= 1;
+  while (c.tpw > 1 && c.wk * c.tpw > w->n_kc) c.tpw >>= 1;
   // shrink until the CTA fits in shared memory
-  while (qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.stages, mx) > 200 * 1024 && c.stages > 2) c.stages--;
-  while (qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.stages, mx) > 200 * 1024 && c.wk > 1) c.wk >>= 1;
+  while (qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.tpw, c.stages, mx) > 200 * 1024 && c.stages > 2) c.stages--;
+  while (qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.tpw, c.stages, mx) > 200 * 1024 && c.tpw > 1) c.tpw >>= 1;
+  while (qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.tpw, c.stages, mx) > 200 * 1024 && c.wk > 1) c.wk >>= 1;
   return c;
 }
 
@@ -206,7 +210,7 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   p.n_rows = (int)w->rows;
   p.n_row_blocks = w->n_rb;
   p.kc_total = w->n_kc;
-  p.kx = (int)w->kpad;
+  p.kx = w->n_kc * kTileK;
   p.mx = mx;
   p.m_out = mx / combine;
   p.combine = combine;
@@ -214,8 +218,13 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   p.wr = c.wr;
   p.wk = c.wk;
   p.stages = c.stages;
+  p.tpw = c.tpw;
   p.err = ctx->dev_err;
-  const size_t smem = qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.stages, mx);
+  {
+    static const char* dbg = std::getenv("TQ_QGEMM_DEBUG");
+    p.debug = dbg ? std::atoi(dbg) : 0;
+  }
+  const size_t smem = qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.tpw, c.stages, mx);
   if (smem > 227 * 1024) return fail(ctx, TQ_EUNSUPPORTED, "tq_qlinear: launch needs %zu bytes of shared memory", smem);
   dim3 grid((unsigned)((w->n_rb + c.wr - 1) / c.wr));
   dim3 block((unsigned)(32 * (c.wr * c.wk + 1)));
@@ -393,17 +402,18 @@ int tq_dequantize(tq_ctx* ctx, const tq_qweight* w, float* out_dev, int8_t* ints
   return TQ_OK;
 }
 
-int tq_qlinear_set_config(tq_ctx* ctx, int wr, int wk, int stages) {
+int tq_qlinear_set_config(tq_ctx* ctx, int wr, int wk, int stages, int tiles_per_warp) {
   if (!ctx) return TQ_EINVAL;
   if (wr == 0) {
-    ctx->cfg_wr = ctx->cfg_wk = ctx->cfg_stages = 0;
+    ctx->cfg_wr = ctx->cfg_wk = ctx->cfg_stages = ctx->cfg_tpw = 0;
     return TQ_OK;
   }
-  TQ_REQUIRE(ctx, wr > 0 && wk > 0 && wr * wk <= 8 && stages >= 2 && stages <= 8,
-             "tq_qlinear_set_config: need wr*wk <= 8 and 2 <= stages <= 8");
+  TQ_REQUIRE(ctx, wr > 0 && wk > 0 && wr * wk <= 8 && stages >= 2 && stages <= 8 && tiles_per_warp >= 1 && tiles_per_warp <= 8,
+             "tq_qlinear_set_config: need wr*wk <= 8, 2 <= stages <= 8, 1 <= tiles_per_warp <= 8");
   ctx->cfg_wr = wr;
   ctx->cfg_wk = wk;
   ctx->cfg_stages = stages;
+  ctx->cfg_tpw = tiles_per_warp;
   return TQ_OK;
 }
 
@@ -423,10 +433,11 @@ int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x_dtype,
 
   const int combine = x_dtype == TQ_F32 ? 3 : 1;
   const size_t chunk = x_dtype == TQ_F32 ? 21 : 64;
-  const bool direct = x_dtype == TQ_BF16 && w->cols == w->kpad && ldx % 8 == 0 && ((uintptr_t)x_dev & 15) == 0;
+  const size_t kx = (size_t)w->n_kc * kTileK;  // the kernel consumes whole 128-k chunks
+  const bool direct = x_dtype == TQ_BF16 && w->cols == kx && ldx % 8 == 0 && ((uintptr_t)x_dev & 15) == 0;
   if (!direct) {
     const size_t rows_staged = (m < chunk ? m : chunk) * combine;
-    if (int st = ensure_xprep(ctx, rows_staged * w->kpad * 2)) return st;
+    if (int st = ensure_xprep(ctx, rows_staged * kx * 2)) return st;
   }
   const size_t xe = x_dtype == TQ_F32 ? 4 : 2, ye = y_dtype == TQ_F32 ? 4 : 2;
   for (size_t m0 = 0; m0 < m; m0 += chunk) {
@@ -440,13 +451,13 @@ int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x_dtype,
       xs = reinterpret_cast<const __nv_bfloat16*>(xc);
       ldxs = ldx;
     } else {
-      const size_t n = mc * w->kpad;
-      prep_x_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(xc, x_dtype, ldx, mc, w->cols, w->kpad,
+      const size_t n = mc * kx;
+      prep_x_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(xc, x_dtype, ldx, mc, w->cols, kx,
                                                                          static_cast<__nv_bfloat16*>(ctx->xprep));
       ctx->launches++;
       TQ_CUDA(ctx, cudaGetLastError());
       xs = static_cast<const __nv_bfloat16*>(ctx->xprep);
-      ldxs = w->kpad;
+      ldxs = kx;
     }
     if (int st = launch_qgemm(ctx, w, xs, ldxs, (int)(mc * combine), combine, yc, y_dtype, ldy, rc)) return st;
   }
