@@ -129,6 +129,113 @@ TQ_API int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host
  * built-in choice. */
 TQ_API int tq_qlinear_set_config(tq_ctx* ctx, int wr, int wk, int stages, int tiles_per_warp);
 
+/* Row-wise concatenation of weights already on the device (same kind and column count; every part
+ * but the last with a multiple of 16 rows): builds the fused [q;k;v] and [gate;up] projections
+ * from the reference's separate matrices (weight order [wq, wk, wv, wo, gate, up, down],
+ * crates/tang-mesh/src/inference.rs:1306-1413). */
+TQ_API int tq_qweight_concat_rows(tq_ctx* ctx, const tq_qweight* const* parts, size_t n_parts, tq_qweight** out);
+
+/* ---- small operators of the decode step ------------------------------------------------------
+ * dtypes are TQ_F32 or TQ_BF16 throughout. */
+
+/* ComputeDevice::rms_norm (crates/tang-compute/src/device.rs:121-128; cpu.rs:126-149) and, with
+ * residual_dev != NULL, rms_norm_residual (device.rs:546-575): v = x + residual,
+ * out = v / sqrt(mean(v^2) + eps) * weight, and v itself to sum_out_dev (f32, may alias
+ * residual_dev) when that is non-NULL.  dim <= 8192. */
+TQ_API int tq_rms_norm(tq_ctx* ctx, const void* x_dev, int x_dtype, const float* residual_dev, const void* weight_dev,
+                       int w_dtype, size_t n_groups, size_t dim, float eps, void* out_dev, int out_dtype,
+                       float* sum_out_dev);
+/* InterleavedRoPE::new (crates/tang-compute/src/modules.rs:495-510): cos/sin tables
+ * [max_seq_len, head_dim/2], computed in f64 on the host and stored as f32 on the device. */
+TQ_API int tq_rope_tables(tq_ctx* ctx, size_t head_dim, size_t max_seq_len, double base, float* cos_dev, float* sin_dev);
+/* ComputeDevice::rope_forward (device.rs:582-610): x [seq_len, n_heads, head_dim], pairs (2i, 2i+1)
+ * rotated by the table row of position start_pos + s — or positions_dev[s] when that is non-NULL
+ * (one decode token per sequence, each at its own position). */
+TQ_API int tq_rope_forward(tq_ctx* ctx, const void* x_dev, int x_dtype, const float* cos_dev, const float* sin_dev,
+                           const int* positions_dev, size_t seq_len, size_t n_heads, size_t head_dim, size_t start_pos,
+                           void* out_dev, int out_dtype);
+/* ComputeDevice::swiglu_fused_buf (device.rs:727-736): out[r, i] = silu(gate[r*ld + i]) * up[r*ld + i]
+ * (ld = 0: dense).  gate and up may be the two halves of one fused projection. */
+TQ_API int tq_swiglu(tq_ctx* ctx, const void* gate_dev, const void* up_dev, int in_dtype, size_t ld, size_t rows, size_t n,
+                     void* out_dev, int out_dtype);
+/* ComputeDevice::embedding (device.rs:131-138; cpu.rs:151-167): out[i, :] = weight[ids[i], :];
+ * ids are int32 (the reference smuggles u32 bit patterns through an f32 buffer, cpu.rs:51-56). */
+TQ_API int tq_embedding(tq_ctx* ctx, const void* weight_dev, int w_dtype, const int* ids_dev, size_t seq_len, size_t dim,
+                        size_t vocab, void* out_dev, int out_dtype);
+
+/* ---- attention -------------------------------------------------------------------------------
+ * ComputeDevice::kv_attention (device.rs:161-180; cpu.rs:257-315) on f32 buffers, exactly the
+ * reference's signature: q [q_len, n_heads*head_dim], caches [cache_start + q_len, n_kv_heads*
+ * head_dim], query i attends positions 0..cache_start+i.  Any q_len; head_dim <= 256. */
+TQ_API int tq_kv_attention(tq_ctx* ctx, const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
+                           size_t cache_start, size_t q_len, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                           float* out_dev);
+/* The decode hot path: the same attention for ONE new token of each of `batch` sequences, bf16
+ * q [batch, n_heads*128] and bf16 caches [batch][position][n_kv_heads*128] (sequence b starts at
+ * element b*seq_stride; tang-infer's KVCache layout, crates/tang-infer/src/kv_cache.rs:12-24).
+ * Sequence b attends positions 0..lens_dev[b]-1; max_len >= every length.  head_dim = 128,
+ * n_heads/n_kv_heads <= 8.  out [batch, n_heads*128] bf16 or f32. */
+TQ_API int tq_gqa_decode(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev,
+                         const int* lens_dev, size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                         size_t seq_stride, size_t max_len, void* out_dev, int out_dtype);
+
+/* ---- collectives -----------------------------------------------------------------------------
+ * NCCL over NVLink at the shard boundaries (the reference's only collective is a star sum over
+ * QUIC, crates/tang-mesh/src/allreduce.rs:43-70).  One communicator per context; calls are
+ * issued on the context's stream.  tq_comm_unique_id fills 128 bytes that rank 0 shares with the
+ * other ranks by any host-side means. */
+typedef struct tq_comm tq_comm;
+TQ_API int tq_comm_unique_id(void* id_out128);
+TQ_API int tq_comm_create(tq_ctx* ctx, const void* id128, int rank, int world, tq_comm** out);
+TQ_API int tq_comm_destroy(tq_ctx* ctx, tq_comm* comm);
+/* Tears the communicator down from the host without waiting for peers (ncclCommAbort); later
+ * collective calls on it fail with TQ_EINVAL. */
+TQ_API int tq_comm_abort(tq_comm* comm);
+TQ_API int tq_comm_rank(const tq_comm* comm);
+TQ_API int tq_comm_world(const tq_comm* comm);
+TQ_API int tq_all_reduce_f32(tq_ctx* ctx, tq_comm* comm, float* buf_dev, size_t n);
+TQ_API int tq_all_gather(tq_ctx* ctx, tq_comm* comm, const void* send_dev, void* recv_dev, size_t bytes_per_rank);
+TQ_API int tq_all_to_all(tq_ctx* ctx, tq_comm* comm, const void* send_dev, void* recv_dev, size_t bytes_per_peer);
+
+/* ---- Llama-shaped decode step ----------------------------------------------------------------
+ * The reference's decode loop (crates/tang-train/examples/smollm.rs:215-296) for `batch`
+ * sequences at once, one new token each, KV cache resident in HBM.  Dimensions in the config are
+ * the WHOLE model's; with a communicator of size n each rank holds n_heads/n, n_kv_heads/n,
+ * ffn/n and vocab/n and is given weights of those shard shapes:
+ *   wqkv [ (n_heads + 2 n_kv_heads)/n * head_dim, d_model ]   rows = this rank's q heads, k heads, v heads
+ *   wo   [ d_model, n_heads/n * head_dim ]                    columns = this rank's heads
+ *   wgate_up [ 2 ffn/n, d_model ] (gate rows then up rows)    wdown [ d_model, ffn/n ]
+ *   lm_head [ vocab/n, d_model ]
+ * Norm gains and the embedding table are bf16 and replicated.  Weight handles are borrowed. */
+typedef struct tq_llama tq_llama;
+typedef struct tq_llama_config {
+  uint32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn, vocab;
+  uint32_t max_seq;   /* cache positions per sequence */
+  uint32_t max_batch; /* sequences (<= 64) */
+  float eps;          /* RMSNorm epsilon (1e-5 in smollm.rs:29) */
+  double rope_base;   /* RoPE theta */
+} tq_llama_config;
+TQ_API int tq_llama_create(tq_ctx* ctx, const tq_llama_config* cfg, tq_comm* comm_or_null, tq_llama** out);
+TQ_API int tq_llama_destroy(tq_llama* model);
+TQ_API int tq_llama_set_layer(tq_llama* model, size_t layer, const tq_qweight* wqkv, const tq_qweight* wo,
+                              const tq_qweight* wgate_up, const tq_qweight* wdown, const void* attn_norm_bf16_dev,
+                              const void* ffn_norm_bf16_dev);
+TQ_API int tq_llama_set_head(tq_llama* model, const void* embed_bf16_dev, const void* final_norm_bf16_dev,
+                             const tq_qweight* lm_head);
+/* This rank's bf16 caches of one layer, [max_batch][max_seq][n_kv_heads/n * head_dim], so a caller
+ * can prefill them; seq_stride_elems = elements between sequences. */
+TQ_API int tq_llama_kv_cache(tq_llama* model, size_t layer, void** k_cache_dev, void** v_cache_dev,
+                             size_t* seq_stride_elems);
+/* The f32 residual stream [max_batch, d_model] after the last tq_llama_decode (before the final
+ * norm's residual add is applied to it: it holds h after the last attention block). */
+TQ_API int tq_llama_hidden(tq_llama* model, float** hidden_dev);
+/* One decode step: sequence b consumes token_ids_dev[b] at position positions_dev[b] (its k, v are
+ * appended there) and attends positions 0..positions_dev[b].  max_len > every position.
+ * logits_dev: f32 [batch, vocab] for one rank; with n ranks [n][batch][vocab/n] (rank-major
+ * vocabulary slices).  Asynchronous; capturable once run eagerly. */
+TQ_API int tq_llama_decode(tq_llama* model, const int* token_ids_dev, const int* positions_dev, size_t batch,
+                           size_t max_len, float* logits_dev);
+
 /* ---- CUDA graphs ------------------------------------------------------------------------------
  * CudaComputeDevice::begin_capture / end_capture (crates/tang-compute/src/cuda.rs:344-356): every
  * asynchronous call made on the context between begin and end is recorded instead of run, and

@@ -49,6 +49,30 @@ PROTOTYPES = {
     "tq_qlinear": (_i, [_p, _p, _p, _i, _sz, _sz, _p, _i, _sz, _p]),
     "tq_q_matvec_host": (_i, [_p, _p, _p, _p, _i, _sz]),
     "tq_qlinear_set_config": (_i, [_p, _i, _i, _i, _i]),
+    "tq_qweight_concat_rows": (_i, [_p, _pp, _sz, _pp]),
+    "tq_rms_norm": (_i, [_p, _p, _i, _p, _p, _i, _sz, _sz, C.c_float, _p, _i, _p]),
+    "tq_rope_tables": (_i, [_p, _sz, _sz, C.c_double, _p, _p]),
+    "tq_rope_forward": (_i, [_p, _p, _i, _p, _p, _p, _sz, _sz, _sz, _sz, _p, _i]),
+    "tq_swiglu": (_i, [_p, _p, _p, _i, _sz, _sz, _sz, _p, _i]),
+    "tq_embedding": (_i, [_p, _p, _i, _p, _sz, _sz, _sz, _p, _i]),
+    "tq_kv_attention": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p]),
+    "tq_gqa_decode": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),
+    "tq_comm_unique_id": (_i, [_p]),
+    "tq_comm_create": (_i, [_p, _p, _i, _i, _pp]),
+    "tq_comm_destroy": (_i, [_p, _p]),
+    "tq_comm_abort": (_i, [_p]),
+    "tq_comm_rank": (_i, [_p]),
+    "tq_comm_world": (_i, [_p]),
+    "tq_all_reduce_f32": (_i, [_p, _p, _p, _sz]),
+    "tq_all_gather": (_i, [_p, _p, _p, _p, _sz]),
+    "tq_all_to_all": (_i, [_p, _p, _p, _p, _sz]),
+    "tq_llama_create": (_i, [_p, _p, _p, _pp]),
+    "tq_llama_destroy": (_i, [_p]),
+    "tq_llama_set_layer": (_i, [_p, _sz, _p, _p, _p, _p, _p, _p]),
+    "tq_llama_set_head": (_i, [_p, _p, _p, _p]),
+    "tq_llama_kv_cache": (_i, [_p, _sz, _pp, _pp, C.POINTER(_sz)]),
+    "tq_llama_hidden": (_i, [_p, _pp]),
+    "tq_llama_decode": (_i, [_p, _p, _p, _sz, _sz, _p]),
     "tq_graph_begin": (_i, [_p]),
     "tq_graph_end": (_i, [_p, _pp]),
     "tq_graph_launch": (_i, [_p, _p]),

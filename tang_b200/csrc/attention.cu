@@ -1,0 +1,398 @@
+// Decode attention over a bf16 KV cache (include/tangq.h: tq_gqa_decode, tq_kv_attention).
+//
+// tq_gqa_decode is the hot path: one new query token per sequence, grouped-query attention
+// (kv_head = head / (n_heads / n_kv_heads), crates/tang-compute/src/cpu.rs:257-315), batched over
+// sequences, the cache of each sequence laid out [position, n_kv_heads*head_dim]
+// (crates/tang-infer/src/kv_cache.rs:12-24).  It is bound by the HBM read of K and V, so the
+// cache is split along positions across CTAs (flash-decoding): grid = (splits, kv heads, batch).
+// A CTA streams 64-position K/V tiles through a cp.async double buffer; each of its four warps
+// takes 16 positions of a tile, forms S = Q K^T and O += P V with mma.sync m16n8k16 (the group's
+// query heads are the 16 MMA rows, of which up to 8 are used; P as a two-term bf16 sum) and keeps a
+// running max / sum per
+// head (online softmax, f32).  Warps, then splits, are merged with the usual max-rescaled sum.
+//
+// tq_kv_attention is the reference call itself (ComputeDevice::kv_attention, device.rs:161-180)
+// on f32 buffers, any q_len, causal; a plain one-warp-per-(query, head) kernel in f32.
+#include <cuda_bf16.h>
+
+#include <cfloat>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace tq {
+
+constexpr int kHD = 128;              // head dimension of the MMA kernel
+constexpr int kTileKeys = 64;         // positions per smem tile
+constexpr int kRowBytes = kHD * 2 + 16;  // padded smem row: 272 B keeps ldmatrix / 4-byte reads conflict-free
+constexpr int kAttnThreads = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct GqaParams {
+  const __nv_bfloat16* q;        // [B, n_heads, kHD]
+  const __nv_bfloat16* k_cache;  // [B][max_seq][n_kv*kHD]
+  const __nv_bfloat16* v_cache;
+  const int* lens;               // [B] positions to attend (including the newest)
+  size_t seq_stride;             // elements between sequences
+  int n_heads, n_kv, group;      // group = n_heads / n_kv  (<= 8)
+  int n_splits, chunk;           // positions per split (multiple of kTileKeys)
+  float scale;                   // 1/sqrt(head_dim)
+  void* out;                     // [B, n_heads*kHD] bf16 or f32 (n_splits == 1)
+  int out_f32;
+  float* part_o;                 // [B, n_heads, n_splits, kHD]
+  float* part_ml;                // [B, n_heads, n_splits, 2]
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;  // src-size 0 -> the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kAttnThreads) gqa_decode_kernel(const GqaParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  // smem: K[2][64][272] | V[2][64][272]; reused for the warp merge at the end
+  uint8_t* k_s = smem;
+  uint8_t* v_s = smem + 2 * kTileKeys * kRowBytes;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int len = p.lens[b];
+  const int k_begin = split * p.chunk;
+  const int k_end = min(len, k_begin + p.chunk);
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
+  const size_t row_elems = (size_t)p.n_kv * kHD;
+  const __nv_bfloat16* kbase = p.k_cache + (size_t)b * p.seq_stride + (size_t)kvh * kHD;
+  const __nv_bfloat16* vbase = p.v_cache + (size_t)b * p.seq_stride + (size_t)kvh * kHD;
+
+  // Q fragments: row g of the MMA = query head (kvh*group + g), zero for g >= group.
+  uint32_t qa[8][2];  // [k-step][a0 (d 2t..), a2 (d 2t+8..)]
+  {
+    const __nv_bfloat16* qrow = p.q + ((size_t)b * p.n_heads + (size_t)kvh * p.group + g) * kHD;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][0] = g < p.group ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t) : 0u;
+      qa[ks][1] = g < p.group ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t + 8) : 0u;
+    }
+  }
+
+  auto load_tile = [&](int tile, int buf) {
+    const int key0 = k_begin + tile * kTileKeys;
+    // 64 rows x 16 chunks of 16 B for K and for V: 2048 chunks / 128 threads
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int c = threadIdx.x + i * kAttnThreads;  // 0..2047
+      const int which = c >> 10, rc = c & 1023, row = rc >> 4, ch = rc & 15;
+      const int key = key0 + row;
+      const bool valid = key < k_end;
+      const __nv_bfloat16* src = (which ? vbase : kbase) + (size_t)(valid ? key : k_begin) * row_elems + ch * 8;
+      uint8_t* dst = (which ? v_s : k_s) + ((size_t)buf * kTileKeys + row) * kRowBytes + ch * 16;
+      cp_async16(dst, src, valid);
+    }
+    cp_async_commit();
+  };
+
+  float o[16][2];  // row g (head), d = 8*dn + 2t, +1
+#pragma unroll
+  for (int dn = 0; dn < 16; ++dn) o[dn][0] = o[dn][1] = 0.f;
+  float m_run = -FLT_MAX, l_run = 0.f;  // l_run: this lane's share of the row sum
+
+  if (n_tiles > 0) load_tile(0, 0);
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int buf = tile & 1;
+    if (tile + 1 < n_tiles) {
+      load_tile(tile + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    const int key0 = k_begin + tile * kTileKeys + 16 * warp;  // first of this warp's 16 positions
+    if (key0 < k_end) {
+      const uint8_t* kt = k_s + ((size_t)buf * kTileKeys + 16 * warp) * kRowBytes;
+      const uint8_t* vt = v_s + ((size_t)buf * kTileKeys + 16 * warp) * kRowBytes;
+      float s[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        const uint8_t* krow = kt + (size_t)(8 * nt + g) * kRowBytes + 4 * t;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks + 16);
+          mma_bf16_16816(s[nt], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+        }
+      }
+      // scores of row g: positions key0 + 8*nt + 2t, +1
+      float sc[4];
+      float mx = -FLT_MAX;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int key = key0 + 8 * nt + 2 * t + c;
+          const float v = key < k_end ? s[nt][c] * p.scale : -FLT_MAX;
+          sc[2 * nt + c] = v;
+          mx = fmaxf(mx, v);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = exp2f((m_run - m_new) * kLog2e);
+      float pr[4];
+      float psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        pr[i] = sc[i] == -FLT_MAX ? 0.f : exp2f((sc[i] - m_new) * kLog2e);
+        psum += pr[i];
+      }
+      l_run = l_run * alpha + psum;
+      m_run = m_new;
+#pragma unroll
+      for (int dn = 0; dn < 16; ++dn) {
+        o[dn][0] *= alpha;
+        o[dn][1] *= alpha;
+      }
+      // P enters the tensor core as bf16; a second, residual term (p - bf16(p)) keeps 16 significant
+      // bits so the result does not depend on bf16's 8-bit rounding of the probabilities.
+      float ph[4], pl[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ph[i] = __bfloat162float(__float2bfloat16_rn(pr[i]));
+        pl[i] = pr[i] - ph[i];
+      }
+      const uint32_t pa0 = pack_bf16(ph[0], ph[1]);  // row g, positions 2t, 2t+1
+      const uint32_t pa2 = pack_bf16(ph[2], ph[3]);  // row g, positions 2t+8, 2t+9
+      const uint32_t pb0 = pack_bf16(pl[0], pl[1]);
+      const uint32_t pb2 = pack_bf16(pl[2], pl[3]);
+      // V fragments, two d-tiles per ldmatrix.x4.trans
+      const uint8_t* vrow = vt + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * kRowBytes + 16 * (lane >> 4);
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, vrow + 32 * dp);
+        float acc0[4] = {o[2 * dp][0], o[2 * dp][1], 0.f, 0.f};
+        float acc1[4] = {o[2 * dp + 1][0], o[2 * dp + 1][1], 0.f, 0.f};
+        mma_bf16_16816(acc0, pa0, 0u, pa2, 0u, vb[0], vb[1]);
+        mma_bf16_16816(acc1, pa0, 0u, pa2, 0u, vb[2], vb[3]);
+        mma_bf16_16816(acc0, pb0, 0u, pb2, 0u, vb[0], vb[1]);
+        mma_bf16_16816(acc1, pb0, 0u, pb2, 0u, vb[2], vb[3]);
+        o[2 * dp][0] = acc0[0];
+        o[2 * dp][1] = acc0[1];
+        o[2 * dp + 1][0] = acc1[0];
+        o[2 * dp + 1][1] = acc1[1];
+      }
+    }
+    __syncthreads();  // everyone is done with `buf` before it is refilled
+  }
+
+  // ---- merge the four warps (rows g < group only)
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  float* mo = reinterpret_cast<float*>(smem);                   // [4 warps][8 rows][128]
+  float* mml = mo + 4 * 8 * kHD;                                // [4 warps][8 rows][2]
+#pragma unroll
+  for (int dn = 0; dn < 16; ++dn) {
+    mo[((size_t)warp * 8 + g) * kHD + 8 * dn + 2 * t] = o[dn][0];
+    mo[((size_t)warp * 8 + g) * kHD + 8 * dn + 2 * t + 1] = o[dn][1];
+  }
+  if (t == 0) {
+    mml[(warp * 8 + g) * 2] = m_run;
+    mml[(warp * 8 + g) * 2 + 1] = l_run;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < p.group * kHD; idx += kAttnThreads) {
+    const int r = idx / kHD, d = idx % kHD;
+    float M = -FLT_MAX;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 8 + r) * 2]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wgt = exp2f((mml[(w * 8 + r) * 2] - M) * kLog2e);
+      L += mml[(w * 8 + r) * 2 + 1] * wgt;
+      O += mo[((size_t)w * 8 + r) * kHD + d] * wgt;
+    }
+    const int head = kvh * p.group + r;
+    if (p.n_splits == 1) {
+      const float v = L > 0.f ? O / L : 0.f;
+      const size_t oi = ((size_t)b * p.n_heads + head) * kHD + d;
+      if (p.out_f32) reinterpret_cast<float*>(p.out)[oi] = v;
+      else reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(v);
+    } else {
+      const size_t pi = ((size_t)b * p.n_heads + head) * p.n_splits + split;
+      p.part_o[pi * kHD + d] = O;
+      if (d == 0) {
+        p.part_ml[pi * 2] = M;
+        p.part_ml[pi * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kHD) gqa_combine_kernel(const float* part_o, const float* part_ml, int n_splits,
+                                                          void* out, int out_f32) {
+  const size_t bh = blockIdx.x;  // b * n_heads + head
+  const int d = threadIdx.x;
+  float M = -FLT_MAX;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(bh * n_splits + s) * 2]);
+  float L = 0.f, O = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float wgt = exp2f((part_ml[(bh * n_splits + s) * 2] - M) * kLog2e);
+    L += part_ml[(bh * n_splits + s) * 2 + 1] * wgt;
+    O += part_o[(bh * n_splits + s) * kHD + d] * wgt;
+  }
+  const float v = L > 0.f ? O / L : 0.f;
+  if (out_f32) reinterpret_cast<float*>(out)[bh * kHD + d] = v;
+  else reinterpret_cast<__nv_bfloat16*>(out)[bh * kHD + d] = __float2bfloat16_rn(v);
+}
+
+// ComputeDevice::kv_attention on f32 buffers (cpu.rs:257-315): one warp per (query, head); each
+// lane owns head_dim/32 output columns; positions are visited in order with the reference's
+// running-max update, dot products reduced across the warp.
+__global__ void kv_attention_f32_kernel(const float* q, const float* k_cache, const float* v_cache, float* out,
+                                        int cache_start, int q_len, int n_heads, int n_kv, int head_dim) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (gw >= q_len * n_heads) return;
+  const int qi = gw / n_heads, h = gw % n_heads;
+  const int kv_h = h / (n_heads / n_kv);
+  const int kv_dim = n_kv * head_dim;
+  const float scale = 1.0f / sqrtf((float)head_dim);
+  const float* qp = q + ((size_t)qi * n_heads + h) * head_dim;
+  const int attend = cache_start + qi + 1;
+  constexpr int kMaxPer = 8;  // head_dim <= 256
+  float acc[kMaxPer];
+#pragma unroll
+  for (int i = 0; i < kMaxPer; ++i) acc[i] = 0.f;
+  float run_max = -INFINITY, run_sum = 0.f;
+  for (int j = 0; j < attend; ++j) {
+    const float* kp = k_cache + (size_t)j * kv_dim + (size_t)kv_h * head_dim;
+    float dot = 0.f;
+    for (int d = lane; d < head_dim; d += 32) dot += qp[d] * kp[d];
+    dot = warp_sum(dot);
+    const float score = dot * scale;
+    const float new_max = fmaxf(run_max, score);
+    const float e = expf(score - new_max), rescale = expf(run_max - new_max);
+    run_sum = run_sum * rescale + e;
+    const float* vp = v_cache + (size_t)j * kv_dim + (size_t)kv_h * head_dim;
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i) {
+      const int d = lane + 32 * i;
+      if (d < head_dim) acc[i] = acc[i] * rescale + e * vp[d];
+    }
+    run_max = new_max;
+  }
+  const float inv = 1.0f / run_sum;
+#pragma unroll
+  for (int i = 0; i < kMaxPer; ++i) {
+    const int d = lane + 32 * i;
+    if (d < head_dim) out[((size_t)qi * n_heads + h) * head_dim + d] = acc[i] * inv;
+  }
+}
+
+int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, const int* lens, int B,
+                      int n_heads, int n_kv, int head_dim, size_t seq_stride, int max_len, void* out, int out_dtype) {
+  TQ_REQUIRE(ctx, head_dim == kHD, "tq_gqa_decode: head_dim must be %d", kHD);
+  TQ_REQUIRE(ctx, n_kv > 0 && n_heads % n_kv == 0 && n_heads / n_kv <= 8, "tq_gqa_decode: n_heads/n_kv_heads must be 1..8");
+  TQ_REQUIRE(ctx, out_dtype == TQ_BF16 || out_dtype == TQ_F32, "tq_gqa_decode: out must be bf16 or f32");
+  if (B == 0) return TQ_OK;
+  GqaParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.lens = lens;
+  p.seq_stride = seq_stride;
+  p.n_heads = n_heads;
+  p.n_kv = n_kv;
+  p.group = n_heads / n_kv;
+  p.scale = 1.0f / sqrtf((float)head_dim);
+  p.out = out;
+  p.out_f32 = out_dtype == TQ_F32;
+  // enough CTAs for ~4 per SM, at least 128 positions per split
+  const int tiles = (max_len + kTileKeys - 1) / kTileKeys;
+  int want = (4 * ctx->sm_count + B * n_kv - 1) / (B * n_kv);
+  int max_splits = (tiles + 1) / 2;
+  if (max_splits < 1) max_splits = 1;
+  int n_splits = want < 1 ? 1 : (want > max_splits ? max_splits : want);
+  const int tiles_per_split = (tiles + n_splits - 1) / n_splits;
+  n_splits = (tiles + tiles_per_split - 1) / tiles_per_split;
+  if (n_splits < 1) n_splits = 1;
+  p.n_splits = n_splits;
+  p.chunk = (tiles_per_split > 0 ? tiles_per_split : 1) * kTileKeys;
+  p.part_o = nullptr;
+  p.part_ml = nullptr;
+  if (n_splits > 1) {
+    const size_t n_part = (size_t)B * n_heads * n_splits;
+    const size_t bytes = n_part * (kHD + 2) * sizeof(float);
+    if (int st = ensure_scratch(ctx, bytes)) return st;
+    p.part_o = static_cast<float*>(ctx->scratch);
+    p.part_ml = p.part_o + n_part * kHD;
+  }
+  const size_t smem = 4 * (size_t)kTileKeys * kRowBytes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    TQ_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set = true;
+  }
+  dim3 grid((unsigned)n_splits, (unsigned)n_kv, (unsigned)B);
+  gqa_decode_kernel<<<grid, kAttnThreads, smem, ctx->stream>>>(p);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
+  if (n_splits > 1) {
+    gqa_combine_kernel<<<(unsigned)(B * n_heads), kHD, 0, ctx->stream>>>(p.part_o, p.part_ml, n_splits, out, p.out_f32);
+    ctx->launches++;
+    TQ_CUDA(ctx, cudaGetLastError());
+  }
+  return TQ_OK;
+}
+
+}  // namespace tq
+
+using namespace tq;
+
+extern "C" {
+
+int tq_gqa_decode(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev, const int* lens_dev,
+                  size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t seq_stride, size_t max_len,
+                  void* out_dev, int out_dtype) {
+  if (int st = bind(ctx)) return st;
+  if (batch == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && lens_dev && out_dev, "tq_gqa_decode: null pointer");
+  TQ_REQUIRE(ctx, max_len > 0, "tq_gqa_decode: max_len must bound the sequence lengths");
+  return launch_gqa_decode(ctx, q_dev, k_cache_dev, v_cache_dev, lens_dev, (int)batch, (int)n_heads, (int)n_kv_heads,
+                           (int)head_dim, seq_stride, (int)max_len, out_dev, out_dtype);
+}
+
+int tq_kv_attention(tq_ctx* ctx, const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
+                    size_t cache_start, size_t q_len, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                    float* out_dev) {
+  if (int st = bind(ctx)) return st;
+  TQ_REQUIRE(ctx, n_kv_heads > 0 && n_heads % n_kv_heads == 0, "tq_kv_attention: n_heads must be a multiple of n_kv_heads");
+  TQ_REQUIRE(ctx, head_dim > 0 && head_dim <= 256, "tq_kv_attention: head_dim must be in 1..256");
+  if (q_len == 0 || n_heads == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && out_dev, "tq_kv_attention: null pointer");
+  const size_t warps = q_len * n_heads;
+  kv_attention_f32_kernel<<<(unsigned)((warps * 32 + 127) / 128), 128, 0, ctx->stream>>>(
+      q_dev, k_cache_dev, v_cache_dev, out_dev, (int)cache_start, (int)q_len, (int)n_heads, (int)n_kv_heads, (int)head_dim);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
+  return TQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,291 @@
+// Llama-shaped decode step on the device (include/tangq.h, tq_llama_*).
+//
+// Follows the reference's one decode loop, crates/tang-train/examples/smollm.rs:215-296, op for op:
+// pre-norm -> q/k/v -> RoPE -> cache append -> GQA attention -> o_proj -> residual -> pre-norm ->
+// SwiGLU -> down -> residual; final norm; LM head.  Differences are scheduling only:
+//   * q/k/v and gate/up are single fused quantised GEMVs (weights concatenated along rows);
+//   * the residual add is folded into the next RMSNorm (the reference's own fused operator,
+//     rms_norm_residual, crates/tang-compute/src/device.rs:546-575), so under tensor parallelism
+//     the row-parallel o_proj / down partial sums are all-reduced in place and consumed directly;
+//   * the KV cache lives in HBM as bf16 [sequence][position][kv_dim] and is appended in place.
+// Sharding (crates/tang-mesh/src/placement.rs:12-31 names Split{axis}; nothing executes it there):
+// q/k/v, gate/up and the LM head are split by output rows, o_proj and down by input columns;
+// attention heads follow their KV head.
+#include <cuda_bf16.h>
+
+#include <new>
+#include <vector>
+
+#include "internal.h"
+#include "qlayout.cuh"
+
+struct tq_comm;
+extern "C" int tq_all_reduce_f32(tq_ctx*, tq_comm*, float*, size_t);
+extern "C" int tq_all_gather(tq_ctx*, tq_comm*, const void*, void*, size_t);
+extern "C" int tq_comm_world(const tq_comm*);
+extern "C" int tq_comm_rank(const tq_comm*);
+
+namespace tq {
+int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const float* sin_t, const int* positions, int B,
+                    int n_heads, int n_kv, int hd, int max_seq, void* q_out, void* k_cache, void* v_cache,
+                    size_t seq_stride);
+int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, const int* lens, int B,
+                      int n_heads, int n_kv, int head_dim, size_t seq_stride, int max_len, void* out, int out_dtype);
+
+__global__ void lens_kernel(const int* positions, int* lens, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) lens[i] = positions[i] + 1;
+}
+}  // namespace tq
+
+struct LlamaLayerW {
+  const tq_qweight *wqkv = nullptr, *wo = nullptr, *wgu = nullptr, *wdown = nullptr;
+  const void *attn_norm = nullptr, *ffn_norm = nullptr;  // bf16 [d_model]
+  __nv_bfloat16 *k_cache = nullptr, *v_cache = nullptr;  // [max_batch][max_seq][kv_dim_local]
+};
+
+struct tq_llama {
+  tq_ctx* ctx = nullptr;
+  tq_llama_config cfg{};
+  int tp = 1, rank = 0;
+  int heads_l = 0, kv_l = 0, ffn_l = 0, vocab_l = 0;  // per-rank shard sizes
+  std::vector<LlamaLayerW> layers;
+  const void* embed = nullptr;       // bf16 [vocab, d_model] (replicated)
+  const void* final_norm = nullptr;  // bf16 [d_model]
+  const tq_qweight* lm_head = nullptr;
+  tq_comm* comm = nullptr;
+  float *cos_t = nullptr, *sin_t = nullptr;
+  // activations
+  float *h = nullptr, *delta = nullptr, *qkv = nullptr, *gu = nullptr, *logits_l = nullptr;
+  __nv_bfloat16 *xn = nullptr, *qb = nullptr, *attn = nullptr, *act = nullptr;
+  int* lens = nullptr;
+  std::vector<void*> owned;
+};
+
+using namespace tq;
+
+static int dev_alloc(tq_llama* m, void** p, size_t bytes) {
+  TQ_CUDA(m->ctx, cudaMalloc(p, bytes ? bytes : 16));
+  m->owned.push_back(*p);
+  return TQ_OK;
+}
+
+extern "C" {
+
+int tq_qweight_concat_rows(tq_ctx* ctx, const tq_qweight* const* parts, size_t n_parts, tq_qweight** out) {
+  if (int st = bind(ctx)) return st;
+  TQ_REQUIRE(ctx, parts && n_parts > 0 && out, "tq_qweight_concat_rows: null argument");
+  *out = nullptr;
+  size_t rows = 0;
+  for (size_t i = 0; i < n_parts; ++i) {
+    TQ_REQUIRE(ctx, parts[i] != nullptr, "tq_qweight_concat_rows: null part");
+    TQ_REQUIRE(ctx, parts[i]->kind == parts[0]->kind && parts[i]->cols == parts[0]->cols,
+               "tq_qweight_concat_rows: parts must share kind and column count");
+    TQ_REQUIRE(ctx, i + 1 == n_parts || parts[i]->rows % kTileRows == 0,
+               "tq_qweight_concat_rows: every part but the last needs a row count that is a multiple of 16");
+    rows += parts[i]->rows;
+  }
+  tq_qweight* w = new (std::nothrow) tq_qweight();
+  if (!w) return fail(ctx, TQ_ENOMEM, "out of host memory");
+  *w = *parts[0];
+  w->rows = rows;
+  w->n_rb = (int)((rows + kTileRows - 1) / kTileRows);
+  w->tile_bytes = (size_t)w->n_rb * w->n_kc * qk_tile_bytes(w->kind);
+  w->tiles = nullptr;
+  w->row_scales = nullptr;
+  cudaError_t e = cudaMalloc(&w->tiles, w->tile_bytes);
+  if (e == cudaSuccess && w->kind == TQ_I8_ROW) e = cudaMalloc(&w->row_scales, rows * sizeof(float));
+  size_t off = 0, roff = 0;
+  for (size_t i = 0; i < n_parts && e == cudaSuccess; ++i) {
+    e = cudaMemcpyAsync(w->tiles + off, parts[i]->tiles, parts[i]->tile_bytes, cudaMemcpyDeviceToDevice, ctx->stream);
+    if (e == cudaSuccess && w->kind == TQ_I8_ROW)
+      e = cudaMemcpyAsync(w->row_scales + roff, parts[i]->row_scales, parts[i]->rows * sizeof(float),
+                          cudaMemcpyDeviceToDevice, ctx->stream);
+    off += parts[i]->tile_bytes;
+    roff += parts[i]->rows;
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) {
+    if (w->tiles) cudaFree(w->tiles);
+    if (w->row_scales) cudaFree(w->row_scales);
+    delete w;
+    cudaGetLastError();
+    return fail(ctx, TQ_ECUDA, "tq_qweight_concat_rows: %s", cudaGetErrorString(e));
+  }
+  *out = w;
+  return TQ_OK;
+}
+
+int tq_llama_create(tq_ctx* ctx, const tq_llama_config* cfg, tq_comm* comm, tq_llama** out) {
+  if (int st = bind(ctx)) return st;
+  TQ_REQUIRE(ctx, cfg && out, "tq_llama_create: null argument");
+  *out = nullptr;
+  const int tp = comm ? tq_comm_world(comm) : 1;
+  TQ_REQUIRE(ctx, cfg->n_layers > 0 && cfg->d_model > 0 && cfg->head_dim == 128, "tq_llama_create: head_dim must be 128");
+  TQ_REQUIRE(ctx, cfg->n_kv_heads > 0 && cfg->n_heads % cfg->n_kv_heads == 0 && cfg->n_heads / cfg->n_kv_heads <= 8,
+             "tq_llama_create: n_heads / n_kv_heads must be 1..8");
+  TQ_REQUIRE(ctx, cfg->n_kv_heads % tp == 0 && cfg->ffn % (32 * tp) == 0 && cfg->vocab % tp == 0,
+             "tq_llama_create: kv heads, ffn/32 and vocab must divide by the tensor-parallel size %d", tp);
+  TQ_REQUIRE(ctx, cfg->max_batch > 0 && cfg->max_batch <= 64 && cfg->max_seq > 0, "tq_llama_create: max_batch must be 1..64");
+  tq_llama* m = new (std::nothrow) tq_llama();
+  if (!m) return fail(ctx, TQ_ENOMEM, "out of host memory");
+  m->ctx = ctx;
+  m->cfg = *cfg;
+  m->comm = comm;
+  m->tp = tp;
+  m->rank = comm ? tq_comm_rank(comm) : 0;
+  m->heads_l = cfg->n_heads / tp;
+  m->kv_l = cfg->n_kv_heads / tp;
+  m->ffn_l = cfg->ffn / tp;
+  m->vocab_l = cfg->vocab / tp;
+  m->layers.resize(cfg->n_layers);
+  const size_t B = cfg->max_batch, d = cfg->d_model, hd = cfg->head_dim;
+  const size_t kv_dim = (size_t)m->kv_l * hd, q_dim = (size_t)m->heads_l * hd;
+  int st = TQ_OK;
+  auto A = [&](void** p, size_t bytes) {
+    if (st == TQ_OK) st = dev_alloc(m, p, bytes);
+  };
+  A((void**)&m->cos_t, (size_t)cfg->max_seq * (hd / 2) * 4);
+  A((void**)&m->sin_t, (size_t)cfg->max_seq * (hd / 2) * 4);
+  A((void**)&m->h, B * d * 4);
+  A((void**)&m->delta, B * d * 4);
+  A((void**)&m->qkv, B * (q_dim + 2 * kv_dim) * 4);
+  A((void**)&m->gu, B * 2 * m->ffn_l * 4);
+  A((void**)&m->logits_l, B * m->vocab_l * 4);
+  A((void**)&m->xn, B * d * 2);
+  A((void**)&m->qb, B * q_dim * 2);
+  A((void**)&m->attn, B * q_dim * 2);
+  A((void**)&m->act, B * m->ffn_l * 2);
+  A((void**)&m->lens, B * 4);
+  for (auto& L : m->layers) {
+    A((void**)&L.k_cache, B * cfg->max_seq * kv_dim * 2);
+    A((void**)&L.v_cache, B * cfg->max_seq * kv_dim * 2);
+  }
+  if (st == TQ_OK) st = tq_rope_tables(ctx, hd, cfg->max_seq, cfg->rope_base, m->cos_t, m->sin_t);
+  if (st != TQ_OK) {
+    for (void* p : m->owned) cudaFree(p);
+    delete m;
+    cudaGetLastError();
+    return st;
+  }
+  *out = m;
+  return TQ_OK;
+}
+
+int tq_llama_destroy(tq_llama* m) {
+  if (!m) return TQ_OK;
+  bind(m->ctx);
+  cudaStreamSynchronize(m->ctx->stream);
+  for (void* p : m->owned) cudaFree(p);
+  delete m;
+  return TQ_OK;
+}
+
+int tq_llama_set_layer(tq_llama* m, size_t layer, const tq_qweight* wqkv, const tq_qweight* wo, const tq_qweight* wgate_up,
+                       const tq_qweight* wdown, const void* attn_norm_bf16_dev, const void* ffn_norm_bf16_dev) {
+  if (!m) return TQ_EINVAL;
+  tq_ctx* ctx = m->ctx;
+  TQ_REQUIRE(ctx, layer < m->layers.size(), "tq_llama_set_layer: layer %zu out of range", layer);
+  TQ_REQUIRE(ctx, wqkv && wo && wgate_up && wdown && attn_norm_bf16_dev && ffn_norm_bf16_dev, "tq_llama_set_layer: null weight");
+  const size_t d = m->cfg.d_model, hd = m->cfg.head_dim;
+  const size_t q_dim = (size_t)m->heads_l * hd, kv_dim = (size_t)m->kv_l * hd;
+  TQ_REQUIRE(ctx, wqkv->rows == q_dim + 2 * kv_dim && wqkv->cols == d, "tq_llama_set_layer: wqkv must be [%zu, %zu]", q_dim + 2 * kv_dim, d);
+  TQ_REQUIRE(ctx, wo->rows == d && wo->cols == q_dim, "tq_llama_set_layer: wo must be [%zu, %zu]", d, q_dim);
+  TQ_REQUIRE(ctx, wgate_up->rows == 2 * (size_t)m->ffn_l && wgate_up->cols == d, "tq_llama_set_layer: wgate_up must be [%zu, %zu]", 2 * (size_t)m->ffn_l, d);
+  TQ_REQUIRE(ctx, wdown->rows == d && wdown->cols == (size_t)m->ffn_l, "tq_llama_set_layer: wdown must be [%zu, %zu]", d, (size_t)m->ffn_l);
+  LlamaLayerW& L = m->layers[layer];
+  L.wqkv = wqkv;
+  L.wo = wo;
+  L.wgu = wgate_up;
+  L.wdown = wdown;
+  L.attn_norm = attn_norm_bf16_dev;
+  L.ffn_norm = ffn_norm_bf16_dev;
+  return TQ_OK;
+}
+
+int tq_llama_set_head(tq_llama* m, const void* embed_bf16_dev, const void* final_norm_bf16_dev, const tq_qweight* lm_head) {
+  if (!m) return TQ_EINVAL;
+  tq_ctx* ctx = m->ctx;
+  TQ_REQUIRE(ctx, embed_bf16_dev && final_norm_bf16_dev && lm_head, "tq_llama_set_head: null argument");
+  TQ_REQUIRE(ctx, lm_head->rows == (size_t)m->vocab_l && lm_head->cols == m->cfg.d_model, "tq_llama_set_head: lm_head must be [%d, %u]",
+             m->vocab_l, m->cfg.d_model);
+  m->embed = embed_bf16_dev;
+  m->final_norm = final_norm_bf16_dev;
+  m->lm_head = lm_head;
+  return TQ_OK;
+}
+
+int tq_llama_kv_cache(tq_llama* m, size_t layer, void** k_cache_dev, void** v_cache_dev, size_t* seq_stride_elems) {
+  if (!m || layer >= m->layers.size()) return TQ_EINVAL;
+  if (k_cache_dev) *k_cache_dev = m->layers[layer].k_cache;
+  if (v_cache_dev) *v_cache_dev = m->layers[layer].v_cache;
+  if (seq_stride_elems) *seq_stride_elems = (size_t)m->cfg.max_seq * m->kv_l * m->cfg.head_dim;
+  return TQ_OK;
+}
+
+int tq_llama_hidden(tq_llama* m, float** hidden_dev) {
+  if (!m || !hidden_dev) return TQ_EINVAL;
+  *hidden_dev = m->h;
+  return TQ_OK;
+}
+
+int tq_llama_decode(tq_llama* m, const int* token_ids_dev, const int* positions_dev, size_t batch, size_t max_len,
+                    float* logits_dev) {
+  if (!m) return TQ_EINVAL;
+  tq_ctx* ctx = m->ctx;
+  if (int st = bind(ctx)) return st;
+  const tq_llama_config& c = m->cfg;
+  TQ_REQUIRE(ctx, batch > 0 && batch <= c.max_batch, "tq_llama_decode: batch must be 1..%u", c.max_batch);
+  TQ_REQUIRE(ctx, token_ids_dev && positions_dev && logits_dev, "tq_llama_decode: null pointer");
+  TQ_REQUIRE(ctx, max_len > 0 && max_len <= c.max_seq, "tq_llama_decode: max_len must be 1..max_seq");
+  TQ_REQUIRE(ctx, m->lm_head != nullptr, "tq_llama_decode: head weights not set");
+  for (auto& L : m->layers) TQ_REQUIRE(ctx, L.wqkv != nullptr, "tq_llama_decode: a layer has no weights");
+  const int B = (int)batch;
+  const size_t d = c.d_model, hd = c.head_dim;
+  const size_t q_dim = (size_t)m->heads_l * hd, kv_dim = (size_t)m->kv_l * hd;
+  const size_t seq_stride = (size_t)c.max_seq * kv_dim;
+  int st;
+#define TQ_STEP(expr) \
+  if ((st = (expr)) != TQ_OK) return st;
+
+  lens_kernel<<<(B + 63) / 64, 64, 0, ctx->stream>>>(positions_dev, m->lens, B);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
+  TQ_STEP(tq_embedding(ctx, m->embed, TQ_BF16, token_ids_dev, B, d, c.vocab, m->h, TQ_F32));
+
+  bool have_delta = false;  // true once `delta` holds a projection output not yet added to h
+  for (size_t l = 0; l < m->layers.size(); ++l) {
+    const LlamaLayerW& L = m->layers[l];
+    // pre-norm (+ the residual add of the previous block's MLP output)
+    TQ_STEP(tq_rms_norm(ctx, have_delta ? (const void*)m->delta : (const void*)m->h, TQ_F32, have_delta ? m->h : nullptr,
+                        L.attn_norm, TQ_BF16, B, d, c.eps, m->xn, TQ_BF16, have_delta ? m->h : nullptr));
+    TQ_STEP(tq_qlinear(ctx, L.wqkv, m->xn, TQ_BF16, d, B, m->qkv, TQ_F32, q_dim + 2 * kv_dim, nullptr));
+    TQ_STEP(launch_qkv_post(ctx, m->qkv, m->cos_t, m->sin_t, positions_dev, B, m->heads_l, m->kv_l, (int)hd, (int)c.max_seq,
+                            m->qb, L.k_cache, L.v_cache, seq_stride));
+    TQ_STEP(launch_gqa_decode(ctx, m->qb, L.k_cache, L.v_cache, m->lens, B, m->heads_l, m->kv_l, (int)hd, seq_stride,
+                              (int)max_len, m->attn, TQ_BF16));
+    TQ_STEP(tq_qlinear(ctx, L.wo, m->attn, TQ_BF16, q_dim, B, m->delta, TQ_F32, d, nullptr));
+    TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->delta, (size_t)B * d));
+    // h += attention output; pre-norm of the MLP
+    TQ_STEP(tq_rms_norm(ctx, m->delta, TQ_F32, m->h, L.ffn_norm, TQ_BF16, B, d, c.eps, m->xn, TQ_BF16, m->h));
+    TQ_STEP(tq_qlinear(ctx, L.wgu, m->xn, TQ_BF16, d, B, m->gu, TQ_F32, 2 * (size_t)m->ffn_l, nullptr));
+    TQ_STEP(tq_swiglu(ctx, m->gu, m->gu + m->ffn_l, TQ_F32, 2 * (size_t)m->ffn_l, B, m->ffn_l, m->act, TQ_BF16));
+    TQ_STEP(tq_qlinear(ctx, L.wdown, m->act, TQ_BF16, m->ffn_l, B, m->delta, TQ_F32, d, nullptr));
+    TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->delta, (size_t)B * d));
+    have_delta = true;
+  }
+  // final norm (adds the last MLP output), LM head on every row (each row is a sequence's last token)
+  TQ_STEP(tq_rms_norm(ctx, m->delta, TQ_F32, m->h, m->final_norm, TQ_BF16, B, d, c.eps, m->xn, TQ_BF16, m->h));
+  if (m->tp == 1) {
+    TQ_STEP(tq_qlinear(ctx, m->lm_head, m->xn, TQ_BF16, d, B, logits_dev, TQ_F32, c.vocab, nullptr));
+  } else {
+    // column-parallel head: this rank's vocabulary slice, gathered rank-major: logits_dev is
+    // [tp][B][vocab/tp]
+    TQ_STEP(tq_qlinear(ctx, m->lm_head, m->xn, TQ_BF16, d, B, m->logits_l, TQ_F32, m->vocab_l, nullptr));
+    TQ_STEP(tq_all_gather(ctx, m->comm, m->logits_l, logits_dev, (size_t)B * m->vocab_l * sizeof(float)));
+  }
+#undef TQ_STEP
+  return TQ_OK;
+}
+
+}  // extern "C"

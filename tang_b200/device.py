@@ -310,3 +310,93 @@ class Graph:
         if self.handle:
             self.dev._L.tq_graph_free(self.dev._ctx, C.c_void_p(self.handle))
             self.handle = 0
+
+
+# ---------------------------------------------------------------------- operators of the decode step
+def _opt_ptr(buf) -> C.c_void_p:
+    return C.c_void_p(buf.ptr if buf is not None else 0)
+
+
+def _add_ops(cls):
+    def rms_norm(self, data: Buffer, weight: Buffer, n_groups: int, dim: int, eps: float, out_dtype: int = F32) -> Buffer:
+        """``ComputeDevice::rms_norm(data, weight, n_groups, dim, eps)`` (device.rs:121-128)."""
+        out = self.alloc(n_groups * dim, out_dtype)
+        self._check(self._L.tq_rms_norm(self._ctx, C.c_void_p(data.ptr), data.dtype, None, C.c_void_p(weight.ptr),
+                                        weight.dtype, n_groups, dim, eps, C.c_void_p(out.ptr), out_dtype, None))
+        return out
+
+    def rms_norm_residual(self, inp: Buffer, residual: Buffer, weight: Buffer, n_groups: int, dim: int, eps: float,
+                          out_dtype: int = F32):
+        """``rms_norm_residual`` (device.rs:546-575): returns (normed, input + residual)."""
+        out = self.alloc(n_groups * dim, out_dtype)
+        s = self.alloc(n_groups * dim, F32)
+        self._check(self._L.tq_rms_norm(self._ctx, C.c_void_p(inp.ptr), inp.dtype, C.c_void_p(residual.ptr),
+                                        C.c_void_p(weight.ptr), weight.dtype, n_groups, dim, eps, C.c_void_p(out.ptr),
+                                        out_dtype, C.c_void_p(s.ptr)))
+        return out, s
+
+    def rope_tables(self, head_dim: int, max_seq_len: int, base: float):
+        """``InterleavedRoPE::new`` (modules.rs:495-510): device cos / sin tables."""
+        half = head_dim // 2
+        cos, sin = self.alloc(max_seq_len * half, F32), self.alloc(max_seq_len * half, F32)
+        self._check(self._L.tq_rope_tables(self._ctx, head_dim, max_seq_len, base, C.c_void_p(cos.ptr), C.c_void_p(sin.ptr)))
+        return cos, sin
+
+    def rope_forward(self, x: Buffer, cos: Buffer, sin: Buffer, seq_len: int, n_heads: int, head_dim: int,
+                     start_pos: int = 0, positions: Buffer | None = None, out_dtype: int | None = None) -> Buffer:
+        """``rope_forward`` (device.rs:582-610)."""
+        out = self.alloc(x.n, x.dtype if out_dtype is None else out_dtype)
+        self._check(self._L.tq_rope_forward(self._ctx, C.c_void_p(x.ptr), x.dtype, C.c_void_p(cos.ptr), C.c_void_p(sin.ptr),
+                                            _opt_ptr(positions), seq_len, n_heads, head_dim, start_pos, C.c_void_p(out.ptr),
+                                            out.dtype))
+        return out
+
+    def swiglu_fused(self, gate: Buffer, up: Buffer, out_dtype: int = F32) -> Buffer:
+        """``swiglu_fused_buf`` (device.rs:727-736)."""
+        out = self.alloc(gate.n, out_dtype)
+        self._check(self._L.tq_swiglu(self._ctx, C.c_void_p(gate.ptr), C.c_void_p(up.ptr), gate.dtype, 0, 1, gate.n,
+                                      C.c_void_p(out.ptr), out_dtype))
+        return out
+
+    def embedding(self, weight: Buffer, ids, seq_len: int, dim: int, out_dtype: int = F32) -> Buffer:
+        """``embedding(weight, ids, seq_len, dim)`` (device.rs:131-138); ids: int array or I32 Buffer."""
+        idb = ids if isinstance(ids, Buffer) else self.upload(np.asarray(ids, np.int32), _lib.I32)
+        out = self.alloc(seq_len * dim, out_dtype)
+        self._check(self._L.tq_embedding(self._ctx, C.c_void_p(weight.ptr), weight.dtype, C.c_void_p(idb.ptr), seq_len, dim,
+                                         weight.n // dim, C.c_void_p(out.ptr), out_dtype))
+        return out
+
+    def kv_attention(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, cache_start: int, q_len: int, n_heads: int,
+                     n_kv_heads: int, head_dim: int) -> Buffer:
+        """``ComputeDevice::kv_attention`` (device.rs:161-180), f32 buffers."""
+        if q.dtype != F32 or k_cache.dtype != F32 or v_cache.dtype != F32:
+            raise TangqError(_lib.TQ_EINVAL, "kv_attention takes f32 buffers; use gqa_decode for the bf16 cache")
+        if q.n != q_len * n_heads * head_dim or k_cache.n < (cache_start + q_len) * n_kv_heads * head_dim:
+            raise TangqError(_lib.TQ_EINVAL, "kv_attention: buffer sizes do not match the shapes")
+        out = self.alloc(q.n, F32)
+        self._check(self._L.tq_kv_attention(self._ctx, C.c_void_p(q.ptr), C.c_void_p(k_cache.ptr), C.c_void_p(v_cache.ptr),
+                                            cache_start, q_len, n_heads, n_kv_heads, head_dim, C.c_void_p(out.ptr)))
+        return out
+
+    def gqa_decode(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, lens, batch: int, n_heads: int, n_kv_heads: int,
+                   head_dim: int, seq_stride: int, max_len: int, out_dtype: int = BF16) -> Buffer:
+        """Batched single-token decode attention over bf16 caches (``tq_gqa_decode``)."""
+        lb = lens if isinstance(lens, Buffer) else self.upload(np.asarray(lens, np.int32), _lib.I32)
+        out = self.alloc(batch * n_heads * head_dim, out_dtype)
+        self._check(self._L.tq_gqa_decode(self._ctx, C.c_void_p(q.ptr), C.c_void_p(k_cache.ptr), C.c_void_p(v_cache.ptr),
+                                          C.c_void_p(lb.ptr), batch, n_heads, n_kv_heads, head_dim, seq_stride, max_len,
+                                          C.c_void_p(out.ptr), out_dtype))
+        return out
+
+    def concat_rows(self, parts) -> QBuffer:
+        arr = (C.c_void_p * len(parts))(*[p.handle for p in parts])
+        h = C.c_void_p()
+        self._check(self._L.tq_qweight_concat_rows(self._ctx, arr, len(parts), C.byref(h)))
+        return self._wrap_q(h)
+
+    for f in (rms_norm, rms_norm_residual, rope_tables, rope_forward, swiglu_fused, embedding, kv_attention, gqa_decode,
+              concat_rows):
+        setattr(cls, f.__name__, f)
+
+
+_add_ops(QuantComputeDevice)

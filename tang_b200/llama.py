@@ -1,0 +1,98 @@
+"""Host-side driver of the Llama-shaped decode step (``tq_llama_*`` in include/tangq.h), mirroring
+the reference's decode loop, crates/tang-train/examples/smollm.rs:255-296 (``LlamaModel::forward``
+for one new token per sequence) and its use of ``tang_infer::KVCache``."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from .device import Buffer, QBuffer, QuantComputeDevice
+
+
+class LlamaConfig(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab",
+                                          "max_seq", "max_batch")] + [("eps", C.c_float), ("rope_base", C.c_double)]
+
+
+class Comm:
+    """NCCL communicator bound to a device context (``tq_comm_*``)."""
+
+    def __init__(self, dev: QuantComputeDevice, unique_id: bytes, rank: int, world: int):
+        self.dev = dev
+        h = C.c_void_p()
+        buf = C.create_string_buffer(unique_id, 128)
+        dev._check(dev._L.tq_comm_create(dev._ctx, buf, rank, world, C.byref(h)))
+        self.handle, self.rank, self.world = h.value, rank, world
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        st = _lib.load().tq_comm_unique_id(buf)
+        if st != _lib.TQ_OK:
+            raise _lib.TangqError(st, "tq_comm_unique_id failed (NCCL not loadable?)")
+        return buf.raw
+
+    def all_reduce(self, buf: Buffer) -> None:
+        self.dev._check(self.dev._L.tq_all_reduce_f32(self.dev._ctx, C.c_void_p(self.handle), C.c_void_p(buf.ptr), buf.n))
+
+    def destroy(self) -> None:
+        if self.handle:
+            self.dev._L.tq_comm_destroy(self.dev._ctx, C.c_void_p(self.handle))
+            self.handle = 0
+
+
+@dataclass
+class LlamaLayerWeights:
+    """One block's device weights in the fused form the kernels take (shard shapes under TP)."""
+    wqkv: QBuffer
+    wo: QBuffer
+    wgate_up: QBuffer
+    wdown: QBuffer
+    attn_norm: Buffer   # bf16 [d_model]
+    ffn_norm: Buffer    # bf16 [d_model]
+
+
+class LlamaModel:
+    def __init__(self, dev: QuantComputeDevice, cfg: LlamaConfig, comm: Comm | None = None):
+        self.dev, self.cfg, self.comm = dev, cfg, comm
+        self.tp = comm.world if comm else 1
+        h = C.c_void_p()
+        dev._check(dev._L.tq_llama_create(dev._ctx, C.byref(cfg), C.c_void_p(comm.handle if comm else 0), C.byref(h)))
+        self.handle = h.value
+        self._keep = []
+
+    def set_layer(self, layer: int, w: LlamaLayerWeights) -> None:
+        self._keep.append(w)
+        self.dev._check(self.dev._L.tq_llama_set_layer(
+            C.c_void_p(self.handle), layer, C.c_void_p(w.wqkv.handle), C.c_void_p(w.wo.handle),
+            C.c_void_p(w.wgate_up.handle), C.c_void_p(w.wdown.handle), C.c_void_p(w.attn_norm.ptr),
+            C.c_void_p(w.ffn_norm.ptr)))
+
+    def set_head(self, embed: Buffer, final_norm: Buffer, lm_head: QBuffer) -> None:
+        self._keep.append((embed, final_norm, lm_head))
+        self.dev._check(self.dev._L.tq_llama_set_head(C.c_void_p(self.handle), C.c_void_p(embed.ptr),
+                                                      C.c_void_p(final_norm.ptr), C.c_void_p(lm_head.handle)))
+
+    def kv_cache(self, layer: int):
+        """(k_ptr, v_ptr, seq_stride_elems) of this rank's bf16 cache for `layer`."""
+        k, v, s = C.c_void_p(), C.c_void_p(), C.c_size_t()
+        self.dev._check(self.dev._L.tq_llama_kv_cache(C.c_void_p(self.handle), layer, C.byref(k), C.byref(v), C.byref(s)))
+        return k.value, v.value, s.value
+
+    def kv_buffers(self, layer: int):
+        k, v, s = self.kv_cache(layer)
+        n = self.cfg.max_batch * s
+        return (Buffer(self.dev, k, n, _lib.BF16, owns=False), Buffer(self.dev, v, n, _lib.BF16, owns=False), s)
+
+    def decode(self, token_ids: Buffer, positions: Buffer, batch: int, max_len: int, logits: Buffer) -> None:
+        """``model.forward(&[tok], cache, pos)`` for `batch` sequences (smollm.rs:535); asynchronous."""
+        self.dev._check(self.dev._L.tq_llama_decode(C.c_void_p(self.handle), C.c_void_p(token_ids.ptr),
+                                                    C.c_void_p(positions.ptr), batch, max_len, C.c_void_p(logits.ptr)))
+
+    def destroy(self) -> None:
+        if self.handle:
+            self.dev._L.tq_llama_destroy(C.c_void_p(self.handle))
+            self.handle = 0
