@@ -179,6 +179,18 @@ TQ_API int tq_gqa_decode(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev
                          const int* lens_dev, size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
                          size_t seq_stride, size_t max_len, void* out_dev, int out_dtype);
 
+/* No counterpart in the reference.  tq_gqa_decode for callers that may not allocate device memory
+ * (a serving loop that froze its allocator after start-up, a callback that only owns a stream):
+ * same arguments and results, but the per-split partial results live in a fixed 3 MiB array inside
+ * the library instead of the context's growable workspace, and the call never reaches cudaMalloc
+ * or cudaFree.  It fails with TQ_EINVAL when batch x heads x splits needs more than that.  The
+ * first call on a device looks the array's address up and sets a kernel attribute: make it before
+ * any stream capture.  All calls on a device share the array — keep them ordered; two that overlap
+ * on the GPU corrupt each other's partials. */
+TQ_API int tq_gqa_decode_noalloc(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev,
+                                 const int* lens_dev, size_t batch, size_t n_heads, size_t n_kv_heads,
+                                 size_t head_dim, size_t seq_stride, size_t max_len, void* out_dev, int out_dtype);
+
 /* ---- collectives -----------------------------------------------------------------------------
  * NCCL over NVLink at the shard boundaries (the reference's only collective is a star sum over
  * QUIC, crates/tang-mesh/src/allreduce.rs:43-70).  One communicator per context; calls are

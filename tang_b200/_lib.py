@@ -57,6 +57,7 @@ PROTOTYPES = {
     "tq_embedding": (_i, [_p, _p, _i, _p, _sz, _sz, _sz, _p, _i]),
     "tq_kv_attention": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p]),
     "tq_gqa_decode": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),
+    "tq_gqa_decode_noalloc": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),
     "tq_comm_unique_id": (_i, [_p]),
     "tq_comm_create": (_i, [_p, _p, _i, _i, _pp]),
     "tq_comm_destroy": (_i, [_p, _p]),

@@ -395,4 +395,98 @@ int tq_kv_attention(tq_ctx* ctx, const float* q_dev, const float* k_cache_dev, c
   return TQ_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// tq_gqa_decode_noalloc: the same split-KV decode attention, for callers that must not allocate.
+//
+// Who that is: code running where cudaMalloc is off limits — inside a latency-critical serving loop
+// that has promised its host not to touch the allocator after start-up, inside a library callback
+// that is only handed a stream, or in a process whose memory pool was sized once and is owned by
+// someone else.  tq_gqa_decode keeps the per-split partial results in the context's workspace, which
+// it grows with cudaFree/cudaMalloc when a call needs more; this variant never does.  Its partials
+// live in the fixed array below, which every GPU that loads the library holds until the process
+// exits.
+//
+// The array's name is only a host-side stand-in for the device object: host code cannot pass it to a
+// kernel.  The device address is fetched once per device with cudaGetSymbolAddress while that device
+// is current (first call on the device), checked, cached, and handed to the kernels.  Because that
+// first call also sets the kernel's shared-memory attribute, make it before starting any stream
+// capture.
+//
+// All calls on a device share the one array and it keeps whatever the last call left there.  Nothing
+// in it has to start at zero: every (sequence, head, split) slot a call reads is written by that call
+// first, including the splits that turn out empty.  Two calls that overlap on the GPU (different
+// streams, or a graph replay racing a plain call) would overwrite each other's partials; the caller
+// has to keep calls on one device ordered.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchBytes = 3u << 20;  // 3 MiB: e.g. 64 sequences x 32 heads x 2 splits = 2.1 MB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+constexpr int kNoAllocMaxDevices = 64;
+static void* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+
+int tq_gqa_decode_noalloc(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev,
+                          const int* lens_dev, size_t batch, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                          size_t seq_stride, size_t max_len, void* out_dev, int out_dtype) {
+  if (int st = bind(ctx)) return st;  // makes ctx->device current
+  if (batch == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && lens_dev && out_dev, "tq_gqa_decode_noalloc: null pointer");
+  TQ_REQUIRE(ctx, max_len > 0, "tq_gqa_decode_noalloc: max_len must bound the sequence lengths");
+  TQ_REQUIRE(ctx, head_dim == (size_t)kHD, "tq_gqa_decode_noalloc: head_dim must be %d", kHD);
+  TQ_REQUIRE(ctx, n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_heads / n_kv_heads <= 8,
+             "tq_gqa_decode_noalloc: n_heads/n_kv_heads must be 1..8");
+  TQ_REQUIRE(ctx, out_dtype == TQ_BF16 || out_dtype == TQ_F32, "tq_gqa_decode_noalloc: out must be bf16 or f32");
+  TQ_REQUIRE(ctx, ctx->device >= 0 && ctx->device < kNoAllocMaxDevices, "tq_gqa_decode_noalloc: device index out of range");
+  const size_t smem = 4 * (size_t)kTileKeys * kRowBytes;
+  if (g_noalloc_ptr[ctx->device] == nullptr) {  // set-up, once per device, with that device current
+    void* ptr = nullptr;
+    TQ_CUDA(ctx, cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    TQ_REQUIRE(ctx, ptr != nullptr, "tq_gqa_decode_noalloc: the static scratch array has no device address");
+    TQ_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    g_noalloc_ptr[ctx->device] = ptr;
+  }
+  const int B = (int)batch, n_kv = (int)n_kv_heads, nh = (int)n_heads;
+  // same split rule as tq_gqa_decode
+  const int tiles = ((int)max_len + kTileKeys - 1) / kTileKeys;
+  const int want = (4 * ctx->sm_count + B * n_kv - 1) / (B * n_kv);
+  int max_splits = (tiles + 1) / 2;
+  if (max_splits < 1) max_splits = 1;
+  int n_splits = want < 1 ? 1 : (want > max_splits ? max_splits : want);
+  const int tiles_per_split = (tiles + n_splits - 1) / n_splits;
+  n_splits = (tiles + tiles_per_split - 1) / tiles_per_split;
+  if (n_splits < 1) n_splits = 1;
+  const size_t n_part = (size_t)B * nh * n_splits;
+  const size_t need = n_part * (kHD + 2) * sizeof(float);
+  if (n_splits > 1 && need > kNoAllocScratchBytes)
+    return fail(ctx, TQ_EINVAL,
+                "tq_gqa_decode_noalloc: %zu sequences x %zu heads x %d splits need %zu bytes of partials; the static "
+                "scratch holds %zu (use tq_gqa_decode, or a smaller batch)",
+                batch, n_heads, n_splits, need, kNoAllocScratchBytes);
+  GqaParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q_dev);
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache_dev);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache_dev);
+  p.lens = lens_dev;
+  p.seq_stride = seq_stride;
+  p.n_heads = nh;
+  p.n_kv = n_kv;
+  p.group = nh / n_kv;
+  p.scale = 1.0f / sqrtf((float)head_dim);
+  p.out = out_dev;
+  p.out_f32 = out_dtype == TQ_F32;
+  p.n_splits = n_splits;
+  p.chunk = (tiles_per_split > 0 ? tiles_per_split : 1) * kTileKeys;
+  p.part_o = n_splits > 1 ? static_cast<float*>(g_noalloc_ptr[ctx->device]) : nullptr;
+  p.part_ml = n_splits > 1 ? p.part_o + n_part * kHD : nullptr;
+  dim3 grid((unsigned)n_splits, (unsigned)n_kv, (unsigned)B);
+  gqa_decode_kernel<<<grid, kAttnThreads, smem, ctx->stream>>>(p);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
+  if (n_splits > 1) {
+    gqa_combine_kernel<<<(unsigned)(B * nh), kHD, 0, ctx->stream>>>(p.part_o, p.part_ml, n_splits, out_dev, p.out_f32);
+    ctx->launches++;
+    TQ_CUDA(ctx, cudaGetLastError());
+  }
+  return TQ_OK;
+}
+
 }  // extern "C"
