@@ -284,6 +284,30 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
 
+    host_w = None   # layer 0 on the host, for the CPU baseline leg
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        host_w = (scales[0].cpu().numpy().view(np.uint16), packed[0].cpu().numpy(), x.float().cpu().numpy())
+
+    # ---- Llama-3-8B-shaped decode step, tensor parallel over the ranks of this job
+    decode = None
+    if not args.no_decode:
+        graph.free()
+        graph = None
+        for h in handles:
+            L_.tq_qweight_free(dev._ctx, h)
+        del packed, scales, y
+        torch.cuda.empty_cache()
+        comm = None
+        if world > 1:
+            import torch.distributed as dist
+
+            ids = [tb.Comm.unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            comm = tb.Comm(dev, ids[0], rank, world)
+        decode = run_decode(dev, tb, torch, stream, comm, rank, world, args, barrier)
+        if comm:
+            comm.destroy()
+
     if rank == 0:
         bytes_launch = algorithmic_bytes(m)
         ms_per_step = ms / args.steps
@@ -296,9 +320,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             import oracle
 
             threads = oracle.max_threads()
-            sc_h = scales[0].cpu().numpy().view(np.uint16)
-            pk_h = packed[0].cpu().numpy()
-            v, reps, dt = cpu_matvec_rate(sc_h, pk_h, x.float().cpu().numpy(), threads, args.cpu_budget)
+            v, reps, dt = cpu_matvec_rate(host_w[0], host_w[1], host_w[2], threads, args.cpu_budget)
             cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                    "sample": f"{reps} matvecs of one K={K_IN} N={N_OUT} matrix, M={m}, in {dt:.1f} s"}
         out = {
@@ -316,13 +338,129 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                     "call": "tq_q_matvec_host (q4_matvec with host vectors), weights resident"},
             "cpu_baseline": cpu, "gpu_launches": int(gpu_launches), "clocks": clocks,
             "parity_max_rel_err_vs_oracle": parity,
+            "decode": None if decode is None else {
+                "metric": "llama3_8b_shape_decode_tokens_per_s", "peak_gbs": peak,
+                "results": [dict(r, frac_of_hbm_peak=r["gbs_per_gpu"] / peak) for r in decode]},
         }
         print(json.dumps(out))
-    graph.free()
+    if graph is not None:
+        graph.free()
     if world > 1:
         import torch.distributed as dist
 
         dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------
+# Llama-3-8B-shaped decode step (BASELINE configs[2]): 32 layers, d 4096, 32/8 heads of 128, FFN
+# 14336, vocab 128256, int4-g32/f16 weights, bf16 KV cache prefilled to 2048 positions; tensor
+# parallel over the ranks of this job.  Random-init weights generated on the device.
+# ----------------------------------------------------------------------------------------------
+LLAMA = dict(n_layers=32, d=4096, n_heads=32, n_kv=8, hd=128, ffn=14336, vocab=128256, ctx=2048)
+
+
+def decode_bytes_per_gpu(batch: int, tp: int, n_layers: int) -> int:
+    """Algorithmic bytes one GPU streams per step: its weight shards (nibbles + f16 scales) + its KV heads."""
+    c = LLAMA
+    per_layer_w = (c["d"] * (c["n_heads"] + 2 * c["n_kv"]) * c["hd"] + c["d"] * c["n_heads"] * c["hd"] + 3 * c["d"] * c["ffn"])
+    w = n_layers * per_layer_w + c["vocab"] * c["d"]
+    wbytes = w // 2 + w // 32 * 2
+    kv = n_layers * 2 * batch * (c["ctx"] + 1) * c["n_kv"] * c["hd"] * 2
+    return (wbytes + kv) // tp
+
+
+def build_llama(dev, tb, torch, stream, comm, rank, world, n_layers, max_batch):
+    import ctypes as C
+
+    c = LLAMA
+    tp = world
+    hl, kl, fl, vl = c["n_heads"] // tp, c["n_kv"] // tp, c["ffn"] // tp, c["vocab"] // tp
+    d, hd = c["d"], c["hd"]
+    cfg = tb.LlamaConfig(n_layers, d, c["n_heads"], c["n_kv"], hd, c["ffn"], c["vocab"], c["ctx"] + 1, max_batch, 1e-5, 500000.0)
+    model = tb.LlamaModel(dev, cfg, comm)
+    gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    keep = []
+
+    def qw(rows, cols):
+        with torch.cuda.stream(stream):
+            pay = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device="cuda", generator=gen)
+            sc = (torch.rand((rows, cols // 32), device="cuda", generator=gen) * 0.018 + 0.002).half()
+        stream.synchronize()
+        w = dev.qweight_from_device(tb.Q4_F16, pay.data_ptr(), sc.data_ptr(), rows, cols)
+        dev.sync()
+        return w
+
+    def bf16_vec(n, std=0.02):
+        with torch.cuda.stream(stream):
+            t = (torch.randn(n, device="cuda", generator=gen) * std).bfloat16()
+        stream.synchronize()
+        keep.append(t)
+        return tb.Buffer(dev, t.data_ptr(), t.numel(), tb.BF16, owns=False)
+
+    for l in range(n_layers):
+        model.set_layer(l, tb.LlamaLayerWeights(qw((hl + 2 * kl) * hd, d), qw(d, hl * hd), qw(2 * fl, d), qw(d, fl),
+                                                bf16_vec(d), bf16_vec(d)))
+        kbuf, vbuf, _ = model.kv_buffers(l)
+        with torch.cuda.stream(stream):     # prefill the cache with bf16 N(0,1), in slices to bound the temporary
+            step = 1 << 26
+            for buf in (kbuf, vbuf):
+                for off in range(0, buf.n, step):
+                    n = min(step, buf.n - off)
+                    t = torch.randn(n, device="cuda", generator=gen).bfloat16()
+                    dev._check(dev._L.tq_convert(dev._ctx, C.c_void_p(t.data_ptr()), tb.BF16, C.c_void_p(buf.ptr + 2 * off), tb.BF16, n))
+                    stream.synchronize()
+    model.set_head(bf16_vec(c["vocab"] * d), bf16_vec(d), qw(vl, d))
+    model._bench_keep = keep
+    return model
+
+
+def run_decode(dev, tb, torch, stream, comm, rank, world, args, barrier):
+    """Times the decode step at each batch size; returns a list of result dicts (rank 0 uses them)."""
+    c = LLAMA
+    batches = [int(b) for b in args.decode_batches.split(",") if b]
+    model = build_llama(dev, tb, torch, stream, comm, rank, world, args.decode_layers, max(batches))
+    out = []
+    for B in batches:
+        with torch.cuda.stream(stream):
+            tok = torch.randint(0, c["vocab"], (B,), dtype=torch.int32, device="cuda")
+            pos = torch.full((B,), c["ctx"], dtype=torch.int32, device="cuda")
+            logits = torch.empty((world, B, c["vocab"] // world), dtype=torch.float32, device="cuda")
+        stream.synchronize()
+        tbuf = tb.Buffer(dev, tok.data_ptr(), B, tb.I32, owns=False)
+        pbuf = tb.Buffer(dev, pos.data_ptr(), B, tb.I32, owns=False)
+        lbuf = tb.Buffer(dev, logits.data_ptr(), logits.numel(), tb.F32, owns=False)
+        model.decode(tbuf, pbuf, B, c["ctx"] + 1, lbuf)      # eager once (workspaces, attributes, NCCL warm-up)
+        dev.sync()
+        l0 = dev.launch_count
+        dev.begin_capture()
+        model.decode(tbuf, pbuf, B, c["ctx"] + 1, lbuf)
+        graph = dev.end_capture()
+        for _ in range(max(args.warmup, 3)):
+            graph.launch()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = args.decode_steps
+        with torch.cuda.stream(stream):
+            ev0.record(stream)
+            for _ in range(steps):
+                graph.launch()
+            ev1.record(stream)
+        barrier()
+        ms = ev0.elapsed_time(ev1) / steps
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        finite = bool(torch.isfinite(logits).all().item())
+        graph.free()
+        byt = decode_bytes_per_gpu(B, world, args.decode_layers)
+        out.append({"batch": B, "tp": world, "layers": args.decode_layers, "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3),
+                    "bytes_per_gpu": byt, "gbs_per_gpu": byt / (ms * 1e-3) / 1e9, "logits_finite": finite,
+                    "kernels_per_step": int((dev.launch_count - l0) // (steps + max(args.warmup, 3)))})
+    model.destroy()
+    return out
 
 
 def main() -> None:
@@ -336,6 +474,10 @@ def main() -> None:
     ap.add_argument("--cpu-budget", type=float, default=8.0, help="seconds of CPU baseline timing")
     ap.add_argument("--ref-sample", type=int, default=4, help="matvecs per step of the reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode step")
+    ap.add_argument("--decode-batches", default="1,16,64")
+    ap.add_argument("--decode-layers", type=int, default=32)
+    ap.add_argument("--decode-steps", type=int, default=10)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
