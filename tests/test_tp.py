@@ -1,0 +1,38 @@
+"""Tensor-parallel decode: sharding + collectives against the unsharded oracle.
+
+CPU: two gloo ranks run the oracle's arithmetic over HostLlama.shard's shards with the same
+all-reduce / all-gather pattern as the device path (exercises the N>1 host logic without a GPU).
+GPU: the same case through libtangq and NCCL on two GPUs (skipped when fewer are visible)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(mode, n, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "tp_worker.py"), mode]
+    env = dict(os.environ)
+    env.setdefault("OMP_NUM_THREADS", "2")
+    if mode == "gpu":
+        env["NCCL_NVLS_ENABLE"] = "0"
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+
+
+def test_tp2_sharding_with_gloo_on_cpu():
+    r = _run("cpu", 2, 29631)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "max err" in r.stdout
+
+
+@pytest.mark.gpu
+def test_tp2_decode_on_two_gpus():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = _run("gpu", 2, 29632)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
