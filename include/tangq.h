@@ -248,6 +248,36 @@ TQ_API int tq_llama_hidden(tq_llama* model, float** hidden_dev);
 TQ_API int tq_llama_decode(tq_llama* model, const int* token_ids_dev, const int* positions_dev, size_t batch,
                            size_t max_len, float* logits_dev);
 
+/* ---- mixture-of-experts FFN -------------------------------------------------------------------
+ * No counterpart in the reference (it has no MoE); composed from its primitives.  Router: logits =
+ * h . Wg^T in f64 (ascending k), top_k experts by (logit descending, index ascending), weights =
+ * softmax over ALL experts (optionally renormalised over the chosen ones).  Expert: down(bf16(
+ * silu(gate h) * (up h))) with int4/int8 block weights.  out = sum_chosen w_e expert_e(h) + sum
+ * shared experts. */
+TQ_API int tq_moe_router(tq_ctx* ctx, const void* h_bf16_dev, const void* wg_bf16_dev, size_t n_tokens, size_t d_model,
+                         size_t n_experts, size_t top_k, int renormalize, int* idx_out_dev, float* weight_out_dev,
+                         double* logits_out_dev);
+typedef struct tq_moe tq_moe;
+typedef struct tq_moe_config {
+  uint32_t d_model, ffn, n_experts, top_k, n_shared;
+  uint32_t renormalize;      /* 1: divide the chosen weights by their sum */
+  uint32_t ep_rank, ep_size; /* this rank holds experts [ep_rank, ep_rank+1) * n_experts / ep_size */
+} tq_moe_config;
+/* Stacked weights: this rank's experts concatenated by rows (tq_qweight_concat_rows): gate|up
+ * [n_local * 2*ffn, d_model] (per expert: gate rows then up rows) and down [n_local * d_model, ffn].
+ * Shared experts: n_shared pairs of fused gate|up [2*ffn, d_model] and down [d_model, ffn],
+ * replicated.  Handles are borrowed. */
+TQ_API int tq_moe_create(tq_ctx* ctx, const tq_moe_config* cfg, const void* wg_bf16_dev, const tq_qweight* w_gate_up_stacked,
+                         const tq_qweight* w_down_stacked, const tq_qweight* const* shared_gate_up,
+                         const tq_qweight* const* shared_down, tq_moe** out);
+TQ_API int tq_moe_destroy(tq_moe* moe);
+/* h bf16 [n_tokens, d_model] (the same on every rank) -> out f32 [n_tokens, d_model].  With a
+ * communicator each rank adds its own experts' terms (and the shared experts for its slice of the
+ * tokens) and the result is all-reduced.  idx_out / weight_out (optional): the router's choices,
+ * [n_tokens, top_k]. */
+TQ_API int tq_moe_ffn(tq_moe* moe, const void* h_bf16_dev, size_t n_tokens, float* out_dev, tq_comm* comm_or_null,
+                      int* idx_out_dev, float* weight_out_dev);
+
 /* ---- CUDA graphs ------------------------------------------------------------------------------
  * CudaComputeDevice::begin_capture / end_capture (crates/tang-compute/src/cuda.rs:344-356): every
  * asynchronous call made on the context between begin and end is recorded instead of run, and

@@ -74,6 +74,10 @@ PROTOTYPES = {
     "tq_llama_kv_cache": (_i, [_p, _sz, _pp, _pp, C.POINTER(_sz)]),
     "tq_llama_hidden": (_i, [_p, _pp]),
     "tq_llama_decode": (_i, [_p, _p, _p, _sz, _sz, _p]),
+    "tq_moe_router": (_i, [_p, _p, _p, _sz, _sz, _sz, _sz, _i, _p, _p, _p]),
+    "tq_moe_create": (_i, [_p, _p, _p, _p, _p, _p, _p, _pp]),
+    "tq_moe_destroy": (_i, [_p]),
+    "tq_moe_ffn": (_i, [_p, _p, _sz, _p, _p, _p, _p]),
     "tq_graph_begin": (_i, [_p]),
     "tq_graph_end": (_i, [_p, _pp]),
     "tq_graph_launch": (_i, [_p, _p]),

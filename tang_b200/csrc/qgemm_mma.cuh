@@ -40,6 +40,14 @@ struct QGemmParams {
   int y_bf16;               // 0: f32 output, 1: bf16 output
   int wr, wk, stages;       // consumer grid inside the CTA and ring depth
   int tpw;                  // 128-k tiles each consumer warp handles per stage
+  // Grouped launches (blockIdx.y = group): every group has its own weight of the same shape, `g_tile_stride`
+  // bytes apart (row scales n_rows apart).  With g_counts, group e owns activation rows
+  // g_offsets[e] .. +g_counts[e] of x / y and blockIdx.z walks them in chunks of 8*NT (expert batches);
+  // without, group e's rows start g_x_stride / g_y_stride elements into x / y (one matrix per head).
+  int grouped;
+  const int* g_counts;
+  const int* g_offsets;
+  long long g_tile_stride, g_x_stride, g_y_stride;
   int debug;                // tuning aid: 1 = consumers skip the math, 2 = producer re-reads the first K chunk
   int* err;
 };
@@ -87,6 +95,31 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
   uint8_t* zero_row = smem + kQgHeaderBytes;          // x_stride bytes of zeros: the "token" of idle lanes
   uint8_t* body = zero_row + x_stride;
 
+  // per-launch or per-group operands
+  int mx = p.mx;
+  const uint8_t* tiles = p.tiles;
+  const __nv_bfloat16* xg = p.x;
+  const float* row_scales = p.row_scales;
+  size_t y_off = 0;
+  if (p.grouped) {
+    const int e = blockIdx.y;
+    tiles += (size_t)e * p.g_tile_stride;
+    if (row_scales) row_scales += (size_t)e * p.n_rows;
+    if (p.g_counts) {
+      const int cnt = p.g_counts[e];
+      const int m0 = blockIdx.z * 8 * NT;
+      if (m0 >= cnt) return;              // whole CTA: nothing routed to this chunk
+      mx = min(8 * NT, cnt - m0);
+      const size_t row = (size_t)p.g_offsets[e] + m0;
+      xg += row * p.ldx;
+      y_off = row * p.ldy;
+    } else {
+      xg += (size_t)e * p.g_x_stride;
+      y_off = (size_t)e * p.g_y_stride;
+    }
+  }
+  const int m_out = p.grouped ? mx / p.combine : p.m_out;
+
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_consumers = WR * WK;
   const int rb0 = blockIdx.x * WR;                       // first 16-row block of this CTA
@@ -127,15 +160,15 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
       const uint32_t xbytes = (uint32_t)kxv * 2u;
       uint8_t* st = body + (size_t)s * stage_bytes;
       if (lane == 0)
-        mbar_arrive_expect_tx(&full_bar[s], wbytes * (uint32_t)rbs_valid + (xbytes ? xbytes * (uint32_t)p.mx : 0u));
+        mbar_arrive_expect_tx(&full_bar[s], wbytes * (uint32_t)rbs_valid + (xbytes ? xbytes * (uint32_t)mx : 0u));
       __syncwarp();
-      for (int i = lane; i < rbs_valid + p.mx; i += 32) {
+      for (int i = lane; i < rbs_valid + mx; i += 32) {
         if (i < rbs_valid) {
-          bulk_g2s(st + (size_t)i * KT * TB, p.tiles + ((size_t)(rb0 + i) * p.kc_total + kc0) * TB, wbytes, &full_bar[s],
+          bulk_g2s(st + (size_t)i * KT * TB, tiles + ((size_t)(rb0 + i) * p.kc_total + kc0) * TB, wbytes, &full_bar[s],
                    pol_w);
         } else if (xbytes) {
           const int m = i - rbs_valid;
-          bulk_g2s(st + x_region + (size_t)m * x_stride, p.x + (size_t)m * p.ldx + (size_t)kc0 * kTileK, xbytes,
+          bulk_g2s(st + x_region + (size_t)m * x_stride, xg + (size_t)m * p.ldx + (size_t)kc0 * kTileK, xbytes,
                    &full_bar[s], pol_x);
         }
       }
@@ -156,7 +189,7 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
     const int x_lane = 2 * (wk_i * TPW * kTileK + 8 * t);            // this lane's k offset in an activation row
     int x_off[NT];                                                // stage-relative; < 0: idle lane (reads zeros)
 #pragma unroll
-    for (int i = 0; i < NT; ++i) x_off[i] = (8 * i + g < p.mx) ? x_region + (8 * i + g) * x_stride + x_lane : -1;
+    for (int i = 0; i < NT; ++i) x_off[i] = (8 * i + g < mx) ? x_region + (8 * i + g) * x_stride + x_lane : -1;
     const int zero_off = kQgHeaderBytes + x_lane;
     const bool lane0 = lane == 0;
 
@@ -222,6 +255,7 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
           }
 #pragma unroll
           for (int i = 0; i < NT; ++i) {
+            if (NT > 1 && 8 * i >= mx) break;   // token tiles beyond this launch's (or group's) rows: nothing to do
             const uint4 xv = *reinterpret_cast<const uint4*>(smem + xo[i] + 64 * j);
             float part[4];
             mma_bf16_16816_z(part, a_lo[0], a_hi[0], a_lo[1], a_hi[1], xv.x, xv.y);
@@ -251,8 +285,8 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
     }
     if constexpr (KIND == I8_ROW) {
       const int r_lo = row0 + wr_i * 16 + g;
-      const float rs0 = r_lo < p.n_rows ? p.row_scales[r_lo] : 0.f;
-      const float rs1 = r_lo + 8 < p.n_rows ? p.row_scales[r_lo + 8] : 0.f;
+      const float rs0 = r_lo < p.n_rows ? row_scales[r_lo] : 0.f;
+      const float rs1 = r_lo + 8 < p.n_rows ? row_scales[r_lo + 8] : 0.f;
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
         acc[i][0] *= rs0;
@@ -281,7 +315,7 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
   }
   __syncthreads();
   const int rows_valid = min(R, p.n_rows - row0);
-  for (int idx = threadIdx.x; idx < p.m_out * R; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < m_out * R; idx += blockDim.x) {
     const int r = idx % R, m = idx / R;
     if (r >= rows_valid) continue;
     float v = 0.f;
@@ -289,7 +323,7 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
       const int col = m * p.combine + c;
       for (int w = 0; w < WK; ++w) v += red[((size_t)w * (8 * NT) + col) * RS + r];
     }
-    const size_t o = (size_t)m * p.ldy + row0 + r;
+    const size_t o = y_off + (size_t)m * p.ldy + row0 + r;
     if (p.residual) v += p.residual[o];
     if (p.y_bf16)
       reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(v);

@@ -170,11 +170,11 @@ struct QgConfig {
 // Launch shape: enough CTAs to cover the SMs about twice with every CTA resident at once (the
 // HBM stream is then shared evenly and no tail wave forms), eight consumer warps per CTA, and a
 // ring deep enough to keep tens of KB per SM in flight.
-static QgConfig choose_config(const tq_ctx* ctx, const tq_qweight* w, int mx) {
+static QgConfig choose_config(const tq_ctx* ctx, const tq_qweight* w, int mx, int n_rb, int n_groups) {
   QgConfig c;
   c.nt = mx <= 8 ? 1 : mx <= 16 ? 2 : mx <= 32 ? 4 : 8;
   int wr = c.nt >= 4 ? 4 : 2;
-  while (wr > 1 && (long long)((w->n_rb + wr - 1) / wr) < 2LL * ctx->sm_count) wr >>= 1;
+  while (wr > 1 && (long long)((n_rb + wr - 1) / wr) * n_groups < 2LL * ctx->sm_count) wr >>= 1;
   c.wr = wr;
   c.wk = 8 / wr;
   if (c.nt == 8 && c.wk > 2) c.wk = 2;
@@ -195,10 +195,21 @@ static QgConfig choose_config(const tq_ctx* ctx, const tq_qweight* w, int mx) {
   return c;
 }
 
-// One GEMM launch over <= 64 staged activation rows.
+struct QgGroup {
+  int n_groups = 1;
+  const int* counts = nullptr;    // device: rows routed to each group (expert batches)
+  const int* offsets = nullptr;   // device: first row of each group in x / y
+  long long x_stride = 0, y_stride = 0;  // elements between groups when counts == nullptr
+  int max_rows = 0;               // upper bound of counts[e] (sizes gridDim.z)
+};
+
+// One GEMM launch over <= 64 staged activation rows (per group, for grouped launches).
 static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
-                        void* y, int y_dtype, size_t ldy, const float* residual) {
-  QgConfig c = choose_config(ctx, w, mx);
+                        void* y, int y_dtype, size_t ldy, const float* residual, const QgGroup* grp = nullptr) {
+  const int n_groups = grp ? grp->n_groups : 1;
+  const int n_rb = w->n_rb / n_groups;
+  const size_t rows_g = w->rows / n_groups;
+  QgConfig c = choose_config(ctx, w, mx, n_rb, n_groups);
   QGemmParams p;
   p.tiles = w->tiles;
   p.row_scales = w->row_scales;
@@ -207,8 +218,8 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   p.residual = residual;
   p.ldx = (long long)ldxs;
   p.ldy = (long long)ldy;
-  p.n_rows = (int)w->rows;
-  p.n_row_blocks = w->n_rb;
+  p.n_rows = (int)rows_g;
+  p.n_row_blocks = n_rb;
   p.kc_total = w->n_kc;
   p.kx = w->n_kc * kTileK;
   p.mx = mx;
@@ -220,13 +231,21 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   p.stages = c.stages;
   p.tpw = c.tpw;
   p.err = ctx->dev_err;
+  p.grouped = grp ? 1 : 0;
+  p.g_counts = grp ? grp->counts : nullptr;
+  p.g_offsets = grp ? grp->offsets : nullptr;
+  p.g_tile_stride = (long long)n_rb * w->n_kc * qk_tile_bytes(w->kind);
+  p.g_x_stride = grp ? grp->x_stride : 0;
+  p.g_y_stride = grp ? grp->y_stride : 0;
   {
     static const char* dbg = std::getenv("TQ_QGEMM_DEBUG");
     p.debug = dbg ? std::atoi(dbg) : 0;
   }
   const size_t smem = qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.tpw, c.stages, mx);
   if (smem > 227 * 1024) return fail(ctx, TQ_EUNSUPPORTED, "tq_qlinear: launch needs %zu bytes of shared memory", smem);
-  dim3 grid((unsigned)((w->n_rb + c.wr - 1) / c.wr));
+  const int chunk = 8 * c.nt;
+  const unsigned gz = (grp && grp->counts) ? (unsigned)((grp->max_rows + chunk - 1) / chunk) : 1u;
+  dim3 grid((unsigned)((n_rb + c.wr - 1) / c.wr), (unsigned)n_groups, gz ? gz : 1u);
   dim3 block((unsigned)(32 * (c.wr * c.wk + 1)));
   cudaError_t e;
   switch (w->kind) {
@@ -238,6 +257,24 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   ctx->launches++;
   TQ_CUDA(ctx, e);
   return TQ_OK;
+}
+
+// Grouped launch entry for the other translation units (MoE experts, per-head MLA projections).
+int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, int mx,
+                         const int* counts, const int* offsets, int max_rows, long long x_stride, long long y_stride,
+                         void* y, int y_dtype, size_t ldy) {
+  TQ_REQUIRE(ctx, w && n_groups > 0 && w->rows % n_groups == 0 && (w->rows / n_groups) % kTileRows == 0,
+             "grouped qlinear: rows per group must be a multiple of 16");
+  TQ_REQUIRE(ctx, w->cols == (size_t)w->n_kc * kTileK && ldx % 8 == 0 && ((uintptr_t)x_bf16 & 15) == 0 && (x_stride % 8) == 0,
+             "grouped qlinear: K must be a multiple of 128 and activation rows 16-byte aligned");
+  QgGroup g;
+  g.n_groups = n_groups;
+  g.counts = counts;
+  g.offsets = offsets;
+  g.x_stride = x_stride;
+  g.y_stride = y_stride;
+  g.max_rows = max_rows;
+  return launch_qgemm(ctx, w, static_cast<const __nv_bfloat16*>(x_bf16), ldx, mx, 1, y, y_dtype, ldy, nullptr, &g);
 }
 
 }  // namespace tq

@@ -1,0 +1,72 @@
+"""GPU parity of the MoE FFN layer against the oracle composition (parity unpinned: the reference has
+no MoE).  Expert selection must be bit-exact; outputs are f32-accumulated."""
+import numpy as np
+import pytest
+
+from moe_util import HostMoe
+from util import bf16_round, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import tang_b200
+
+    d = tang_b200.QuantComputeDevice(0)
+    yield d
+    d.close()
+
+
+def check(dev, orc, host, T, seed):
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(seed)
+    hb, hf = bf16_round(rng.standard_normal((T, host.d)).astype(np.float32))
+    want, idx_o, w_o, lg_o = host.oracle(orc, hf)
+    hbuf = dev.upload(hb, tb.BF16)
+    idx_d, w_d, lg_d = tb.moe_router(dev, hbuf, dev.upload(host.wg_bits, tb.BF16), T, host.d, host.E, host.k, host.renorm)
+    assert np.array_equal(lg_d, lg_o)                 # f64, same order of additions: bit-identical logits
+    assert np.array_equal(idx_d, idx_o)               # so the selection (and its order) is identical
+    assert rel_err(w_d, w_o) < 1e-6
+    layer = host.to_device(dev)
+    out, idx, w = layer.forward(hbuf, T, want_routing=True)
+    dev.sync()
+    assert np.array_equal(idx.to_vec().reshape(T, host.k), idx_o)
+    got = out.to_vec().reshape(T, host.d)
+    # the SwiGLU output is rounded to bf16 on both sides; an f32-vs-f64 difference ahead of that rounding can
+    # flip single elements by one bf16 ulp, so the bar is taken against max(|ref|, rms(ref))
+    assert rel_err(got, want, floor_frac=1.0) < 1e-3, T
+    layer.destroy()
+
+
+@pytest.mark.parametrize("T", [1, 5, 70, 200])
+def test_small_moe(dev, orc, T):
+    host = HostMoe(np.random.default_rng(5), d=256, ffn=256, n_experts=8, top_k=2, n_shared=1)
+    check(dev, orc, host, T, seed=T)
+
+
+def test_router_ties_pick_lower_index(dev, orc):
+    import tang_b200 as tb
+
+    d, E, k = 128, 8, 3
+    wg = np.zeros((E, d), np.float32)
+    wg[[1, 4, 6], 0] = 1.0            # experts 1, 4, 6 tie exactly; the rest tie at zero
+    wg[2, 0] = 2.0
+    h = np.zeros((1, d), np.float32)
+    h[0, 0] = 1.0
+    idx, w, lg = tb.moe_router(dev, dev.upload(bf16_round(h)[0], tb.BF16), dev.upload(bf16_round(wg)[0], tb.BF16), 1, d, E, k)
+    oi, ow, _ = orc.router_f64(h[0].astype(np.float64), wg.astype(np.float64), E, k)
+    assert list(idx[0]) == [2, 1, 4] == list(oi)
+
+
+def test_renormalised_weights(dev, orc):
+    host = HostMoe(np.random.default_rng(6), d=256, ffn=128, n_experts=16, top_k=4, n_shared=0, renorm=True)
+    check(dev, orc, host, 9, seed=3)
+
+
+@pytest.mark.parametrize("T", [1, 64])
+def test_deepseek_v2_lite_shape(dev, orc, T):
+    """d_model 2048, 64 routed + 2 shared experts of width 1408, top-6 (BASELINE configs[3])."""
+    host = HostMoe(np.random.default_rng(7), d=2048, ffn=1408, n_experts=64, top_k=6, n_shared=2)
+    check(dev, orc, host, T, seed=100 + T)
