@@ -278,6 +278,25 @@ TQ_API int tq_moe_destroy(tq_moe* moe);
 TQ_API int tq_moe_ffn(tq_moe* moe, const void* h_bf16_dev, size_t n_tokens, float* out_dev, tq_comm* comm_or_null,
                       int* idx_out_dev, float* weight_out_dev);
 
+/* ---- multi-head latent attention, decode ------------------------------------------------------
+ * No counterpart in the reference (it has no MLA).  Absorbed form: the bf16 cache row of position j
+ * is [c_j (kv_lora = 512) | r_j (rope = 64)], sequence b starting at element b*seq_stride;
+ *   s_j = (q_lat . c_j + q_rope . r_j) * softmax_scale,   o_lat = sum_j softmax(s)_j c_j.
+ * q_full [batch, n_heads, 576] bf16 holds q_lat | q_rope per head; o_lat [batch, n_heads, 512] bf16.
+ * n_heads (per rank, when heads are sharded) must be a multiple of 16. */
+TQ_API int tq_mla_decode(tq_ctx* ctx, const void* q_full_bf16_dev, const void* cache_bf16_dev, const int* lens_dev,
+                         size_t batch, size_t n_heads, size_t kv_lora, size_t rope_dim, size_t seq_stride, size_t max_len,
+                         float softmax_scale, void* o_lat_bf16_dev);
+/* q_lat = W_qk[h] q_nope[h] for every head (int8 per-row weights stacked by rows,
+ * [n_heads*512, nope_dim]) written as bf16 into q_full, with q_rope copied behind it.
+ * q_nope [batch, n_heads, nope_dim], q_rope [batch, n_heads, 64] bf16; batch <= 64. */
+TQ_API int tq_mla_absorb_q(tq_ctx* ctx, const tq_qweight* w_qk_stacked, const void* q_nope_bf16_dev,
+                           const void* q_rope_bf16_dev, size_t batch, size_t n_heads, size_t nope_dim,
+                           void* q_full_bf16_dev);
+/* o[h] = W_uv[h] o_lat[h] (stacked [n_heads*v_dim, 512]); out [batch, n_heads, v_dim] f32 or bf16. */
+TQ_API int tq_mla_unabsorb(tq_ctx* ctx, const tq_qweight* w_uv_stacked, const void* o_lat_bf16_dev, size_t batch,
+                           size_t n_heads, size_t v_dim, void* out_dev, int out_dtype);
+
 /* ---- CUDA graphs ------------------------------------------------------------------------------
  * CudaComputeDevice::begin_capture / end_capture (crates/tang-compute/src/cuda.rs:344-356): every
  * asynchronous call made on the context between begin and end is recorded instead of run, and

@@ -391,14 +391,14 @@ def expert_ffn_f64(gate: QWeight, up: QWeight, down: QWeight, x, threads: int = 
     return out
 
 
-def mla_decode_f64(dims: MlaDims, q_nope, q_rope, cache_bf16, ctx, w_uk, w_uk_scale, w_uv, w_uv_scale,
+def mla_decode_f64(dims: MlaDims, q_nope, q_rope, cache_bf16, ctx, w_qk, w_qk_scale, w_uv, w_uv_scale,
                    absorbed=True, threads: int = 0) -> np.ndarray:
     q_nope, q_rope = _c(q_nope, np.float64), _c(q_rope, np.float64)
     cache_bf16 = _c(cache_bf16, np.uint16)
-    w_uk, w_uv = _c(w_uk, np.int8), _c(w_uv, np.int8)
-    w_uk_scale, w_uv_scale = _c(w_uk_scale, np.float32), _c(w_uv_scale, np.float32)
+    w_qk, w_uv = _c(w_qk, np.int8), _c(w_uv, np.int8)
+    w_qk_scale, w_uv_scale = _c(w_qk_scale, np.float32), _c(w_uv_scale, np.float32)
     out = np.empty(int(dims.n_heads * dims.v_dim), np.float64)
-    lib().orc_mla_decode_f64(C.byref(dims), _ptr(q_nope), _ptr(q_rope), _ptr(cache_bf16), C.c_uint64(ctx), _ptr(w_uk),
-                             _ptr(w_uk_scale), _ptr(w_uv), _ptr(w_uv_scale), C.c_int(int(absorbed)), _ptr(out),
+    lib().orc_mla_decode_f64(C.byref(dims), _ptr(q_nope), _ptr(q_rope), _ptr(cache_bf16), C.c_uint64(ctx), _ptr(w_qk),
+                             _ptr(w_qk_scale), _ptr(w_uv), _ptr(w_uv_scale), C.c_int(int(absorbed)), _ptr(out),
                              C.c_int(threads))
     return out

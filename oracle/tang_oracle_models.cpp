@@ -183,16 +183,20 @@ ORC_API void orc_expert_ffn_f64(const OrcQWeight* gate, const OrcQWeight* up, co
 // ---------------------------------------------------------------------------------------------
 // Multi-head latent attention, decode step (no reference counterpart; parity unpinned)
 //
-// Per sequence the cache row of position j is [c_j (kv_lora) | r_j (rope_dim)] in bf16.
-// Per head h with W_UK[h] : [nope, kv_lora] and W_UV[h] : [v_dim, kv_lora] (int8 with a per-row
-// f32 scale, dequantised as crates/tang-infer/src/quantize.rs:73-81 does: v as f32 * scale):
+// Per sequence the cache row of position j is [c_j (kv_lora) | r_j (rope_dim)] in bf16.  The
+// projections are stored ABSORBED and quantised per output row (int8 with one f32 scale per row,
+// dequantised as crates/tang-infer/src/quantize.rs:73-81 does: v as f32 * scale; matvec order as
+// quantize.rs:227-253):
+//   W_qk[h] : [kv_lora, nope]   q_lat = W_qk[h] q_nope          (= W_UK[h]^T of the unabsorbed model)
+//   W_uv[h] : [v_dim, kv_lora]  o     = W_uv[h] o_lat
 //
-//   naive:    k_j = W_UK[h] c_j ,  s_j = (q_nope·k_j + q_rope·r_j) / sqrt(nope+rope_dim)
-//             v_j = W_UV[h] c_j ,  o = sum_j softmax(s)_j v_j
-//   absorbed: q_lat = bf16(W_UK[h]^T q_nope) ,  s_j = (q_lat·c_j + q_rope·r_j) / sqrt(nope+rope_dim)
-//             o_lat = bf16(sum_j softmax(s)_j c_j) ,  o = W_UV[h] o_lat
-// The two agree exactly in real arithmetic; the absorbed form (what the device runs) adds the two
-// bf16 roundings marked above.  `absorbed` selects the form, so a test can bound their gap.
+//   absorbed: q_lat = bf16(W_qk[h] q_nope),  s_j = (q_lat.c_j + q_rope.r_j) * scale,
+//             o_lat = bf16(sum_j softmax(s)_j c_j),  o = W_uv[h] o_lat
+//   naive:    k_j = W_qk[h]^T c_j,  s_j = (q_nope.k_j + q_rope.r_j) * scale,
+//             v_j = W_uv[h] c_j,    o = sum_j softmax(s)_j v_j
+// with scale = 1/sqrt(nope + rope_dim).  The two agree exactly in real arithmetic; the absorbed
+// form (what the device runs) adds the two bf16 roundings marked above.  `absorbed` selects the
+// form, so a test can bound their gap.
 // ---------------------------------------------------------------------------------------------
 
 struct OrcMlaDims {
@@ -200,8 +204,8 @@ struct OrcMlaDims {
 };
 
 ORC_API void orc_mla_decode_f64(const OrcMlaDims* dm, const double* q_nope, const double* q_rope,
-                                const uint16_t* cache_bf16, uint64_t ctx, const int8_t* w_uk,
-                                const float* w_uk_scale, const int8_t* w_uv, const float* w_uv_scale,
+                                const uint16_t* cache_bf16, uint64_t ctx, const int8_t* w_qk,
+                                const float* w_qk_scale, const int8_t* w_uv, const float* w_uv_scale,
                                 int absorbed, double* out, int threads) {
   const size_t H = dm->n_heads, C = dm->kv_lora, Dn = dm->nope, Dr = dm->rope_dim, Dv = dm->v_dim;
   const size_t row = C + Dr;
@@ -210,8 +214,8 @@ ORC_API void orc_mla_decode_f64(const OrcMlaDims* dm, const double* q_nope, cons
 #pragma omp parallel for schedule(static)
   for (long long hh = 0; hh < (long long)H; ++hh) {
     size_t h = (size_t)hh;
-    const int8_t* uk = w_uk + h * Dn * C;
-    const float* uks = w_uk_scale + h * Dn;
+    const int8_t* qk = w_qk + h * C * Dn;
+    const float* qks = w_qk_scale + h * C;
     const int8_t* uv = w_uv + h * Dv * C;
     const float* uvs = w_uv_scale + h * Dv;
     const double* qn = q_nope + h * Dn;
@@ -221,7 +225,8 @@ ORC_API void orc_mla_decode_f64(const OrcMlaDims* dm, const double* q_nope, cons
     if (absorbed) {
       for (size_t c = 0; c < C; ++c) {
         double acc = 0.0;
-        for (size_t dd = 0; dd < Dn; ++dd) acc += qn[dd] * (double)((float)uk[dd * C + c] * uks[dd]);
+        const double sc = (double)qks[c];
+        for (size_t dd = 0; dd < Dn; ++dd) acc += (double)qk[c * Dn + dd] * sc * qn[dd];
         q_lat[c] = round_bf16(acc);
       }
     }
@@ -232,10 +237,10 @@ ORC_API void orc_mla_decode_f64(const OrcMlaDims* dm, const double* q_nope, cons
       if (absorbed) {
         for (size_t c = 0; c < C; ++c) dot += q_lat[c] * (double)orc_bf16_to_f32(cr[c]);
       } else {
-        for (size_t dd = 0; dd < Dn; ++dd) {
-          double acc = 0.0;
-          for (size_t c = 0; c < C; ++c) acc += (double)((float)uk[dd * C + c] * uks[dd]) * (double)orc_bf16_to_f32(cr[c]);
-          kj[dd] = acc;
+        for (size_t dd = 0; dd < Dn; ++dd) kj[dd] = 0.0;
+        for (size_t c = 0; c < C; ++c) {
+          const double cv = (double)orc_bf16_to_f32(cr[c]) * (double)qks[c];
+          for (size_t dd = 0; dd < Dn; ++dd) kj[dd] += (double)qk[c * Dn + dd] * cv;
         }
         for (size_t dd = 0; dd < Dn; ++dd) dot += qn[dd] * kj[dd];
       }
@@ -250,17 +255,32 @@ ORC_API void orc_mla_decode_f64(const OrcMlaDims* dm, const double* q_nope, cons
       sum += s[j];
     }
     for (size_t j = 0; j < ctx; ++j) s[j] /= sum;
-    std::vector<double> o_lat(C, 0.0);
-    for (size_t j = 0; j < ctx; ++j) {
-      const uint16_t* cr = cache_bf16 + j * row;
-      for (size_t c = 0; c < C; ++c) o_lat[c] += s[j] * (double)orc_bf16_to_f32(cr[c]);
-    }
-    if (absorbed)
+    if (absorbed) {
+      std::vector<double> o_lat(C, 0.0);
+      for (size_t j = 0; j < ctx; ++j) {
+        const uint16_t* cr = cache_bf16 + j * row;
+        for (size_t c = 0; c < C; ++c) o_lat[c] += s[j] * (double)orc_bf16_to_f32(cr[c]);
+      }
       for (size_t c = 0; c < C; ++c) o_lat[c] = round_bf16(o_lat[c]);
-    for (size_t dv = 0; dv < Dv; ++dv) {
-      double acc = 0.0;
-      for (size_t c = 0; c < C; ++c) acc += (double)((float)uv[dv * C + c] * uvs[dv]) * o_lat[c];
-      out[h * Dv + dv] = acc;
+      for (size_t dv = 0; dv < Dv; ++dv) {
+        double acc = 0.0;
+        const double sc = (double)uvs[dv];
+        for (size_t c = 0; c < C; ++c) acc += (double)uv[dv * C + c] * sc * o_lat[c];
+        out[h * Dv + dv] = acc;
+      }
+    } else {
+      for (size_t dv = 0; dv < Dv; ++dv) out[h * Dv + dv] = 0.0;
+      std::vector<double> vj(Dv);
+      for (size_t j = 0; j < ctx; ++j) {
+        const uint16_t* cr = cache_bf16 + j * row;
+        for (size_t dv = 0; dv < Dv; ++dv) {
+          double acc = 0.0;
+          const double sc = (double)uvs[dv];
+          for (size_t c = 0; c < C; ++c) acc += (double)uv[dv * C + c] * sc * (double)orc_bf16_to_f32(cr[c]);
+          vj[dv] = acc;
+        }
+        for (size_t dv = 0; dv < Dv; ++dv) out[h * Dv + dv] += s[j] * vj[dv];
+      }
     }
   }
 }
