@@ -1,6 +1,7 @@
 // Context, raw buffers and dtype conversion of the C ABI (include/tangq.h).
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -76,6 +77,7 @@ int tq_ctx_create(int device, void* stream, tq_ctx** out) {
   if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return bail(TQ_ECUDA);
   if (prop.major != 10) return bail(TQ_EUNSUPPORTED);  // kernels are built for sm_100a only
   ctx->sm_count = prop.multiProcessorCount;
+  if (const char* e = std::getenv("TQ_PDL")) ctx->pdl = std::atoi(e) != 0;
   if (stream) {
     ctx->stream = reinterpret_cast<cudaStream_t>(stream);
   } else {

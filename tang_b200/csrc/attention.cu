@@ -70,6 +70,8 @@ __global__ void __launch_bounds__(kAttnThreads) gqa_decode_kernel(const GqaParam
   uint8_t* k_s = smem;
   uint8_t* v_s = smem + 2 * kTileKeys * kRowBytes;
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int len = p.lens[b];
@@ -248,6 +250,8 @@ __global__ void __launch_bounds__(kAttnThreads) gqa_decode_kernel(const GqaParam
 
 __global__ void __launch_bounds__(kHD) gqa_combine_kernel(const float* part_o, const float* part_ml, int n_splits,
                                                           void* out, int out_f32) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t bh = blockIdx.x;  // b * n_heads + head
   const int d = threadIdx.x;
   float M = -FLT_MAX;
@@ -351,14 +355,10 @@ int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const voi
     attr_set = true;
   }
   dim3 grid((unsigned)n_splits, (unsigned)n_kv, (unsigned)B);
-  gqa_decode_kernel<<<grid, kAttnThreads, smem, ctx->stream>>>(p);
-  ctx->launches++;
-  TQ_CUDA(ctx, cudaGetLastError());
-  if (n_splits > 1) {
-    gqa_combine_kernel<<<(unsigned)(B * n_heads), kHD, 0, ctx->stream>>>(p.part_o, p.part_ml, n_splits, out, p.out_f32);
-    ctx->launches++;
-    TQ_CUDA(ctx, cudaGetLastError());
-  }
+  TQ_CUDA(ctx, launch_k(ctx, gqa_decode_kernel, grid, dim3(kAttnThreads), smem, p));
+  if (n_splits > 1)
+    TQ_CUDA(ctx, launch_k(ctx, gqa_combine_kernel, dim3((unsigned)(B * n_heads)), dim3(kHD), 0, (const float*)p.part_o,
+                          (const float*)p.part_ml, n_splits, out, p.out_f32));
   return TQ_OK;
 }
 

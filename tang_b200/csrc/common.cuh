@@ -25,6 +25,12 @@ enum DeviceErr : int {
 // microseconds; it only exists so that a logic error can never hang the GPU.
 constexpr uint32_t kMaxPolls = 1u << 22;
 
+// Programmatic dependent launch: wait until every kernel this one depends on has completed and its
+// writes are visible (no-op when the kernel was launched without the attribute) / allow the next
+// kernel in the stream to begin launching.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -22,6 +22,7 @@ struct tq_ctx {
   int sm_count = 148;
   int cfg_wr = 0, cfg_wk = 0, cfg_stages = 0, cfg_tpw = 0;  // tq_qlinear_set_config override
   unsigned long long launches = 0;             // kernels launched through this context
+  bool pdl = true;                             // programmatic dependent launch for the decode-path kernels
   bool capturing = false;                      // between tq_graph_begin and tq_graph_end
   unsigned long long launches_at_capture = 0;
   std::string last_error = "";
@@ -70,6 +71,26 @@ inline int bind(tq_ctx* ctx) {
 
 int ensure_xprep(tq_ctx* ctx, size_t bytes);
 int ensure_scratch(tq_ctx* ctx, size_t bytes);
+
+// Launches `kern` on the context's stream.  With programmatic dependent launch enabled (default;
+// TQ_PDL=0 turns it off) the launch carries the programmatic-stream-serialization attribute, so the
+// kernel may start while its predecessor drains; every kernel launched this way executes
+// `griddepcontrol.wait` before it touches memory another kernel wrote or still reads.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(tq_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  ctx->launches++;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 inline size_t dtype_size(int dt) {
   switch (dt) {

@@ -33,6 +33,8 @@ int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const voi
                       int n_heads, int n_kv, int head_dim, size_t seq_stride, int max_len, void* out, int out_dtype);
 
 __global__ void lens_kernel(const int* positions, int* lens, int n) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) lens[i] = positions[i] + 1;
 }
@@ -248,9 +250,7 @@ int tq_llama_decode(tq_llama* m, const int* token_ids_dev, const int* positions_
 #define TQ_STEP(expr) \
   if ((st = (expr)) != TQ_OK) return st;
 
-  lens_kernel<<<(B + 63) / 64, 64, 0, ctx->stream>>>(positions_dev, m->lens, B);
-  ctx->launches++;
-  TQ_CUDA(ctx, cudaGetLastError());
+  TQ_CUDA(ctx, launch_k(ctx, lens_kernel, dim3((B + 63) / 64), dim3(64), 0, positions_dev, m->lens, B));
   TQ_STEP(tq_embedding(ctx, m->embed, TQ_BF16, token_ids_dev, B, d, c.vocab, m->h, TQ_F32));
 
   bool have_delta = false;  // true once `delta` holds a projection output not yet added to h

@@ -35,37 +35,93 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 // rms_norm / rms_norm_residual (crates/tang-compute/src/cpu.rs:126-149, device.rs:546-575):
 //   v = x (+ residual);  out = v * (1/sqrt(mean(v^2) + eps)) * w;  sum_out = v (optional).
-// One CTA per row; the row is read once into registers (dim <= 256*32).
+// One CTA per row.  The row is read once, four elements per load, ALL loads issued before any of
+// them is used (the row lives in registers), so the kernel costs one memory round trip per phase.
 constexpr int kNormThreads = 256;
-constexpr int kNormMaxPerThread = 32;
+constexpr int kNormVecs = 8;  // float4 chunks per thread: dim <= 256 * 8 * 4 = 8192
 
-__global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const void* x, int x_dt, const float* residual,
-                                                                const void* w, int w_dt, int dim, float eps, void* out,
-                                                                int out_dt, float* sum_out) {
+template <typename T>
+__device__ __forceinline__ float4 load4(const T* p, size_t i);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p, size_t i) {
+  return *reinterpret_cast<const float4*>(p + i);
+}
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p, size_t i) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p + i);
+  return make_float4(bf16_bits_to_float(u.x & 0xFFFFu), bf16_bits_to_float(u.x >> 16), bf16_bits_to_float(u.y & 0xFFFFu),
+                     bf16_bits_to_float(u.y >> 16));
+}
+__device__ __forceinline__ void store4(float* p, size_t i, float4 v) { *reinterpret_cast<float4*>(p + i) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, size_t i, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p + i) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+
+// dim % 4 == 0 and 16-byte aligned rows.
+template <typename XT, typename WT, typename OT>
+__global__ void __launch_bounds__(kNormThreads) rms_norm_vec_kernel(const XT* x, const float* residual, const WT* w, int dim,
+                                                                    float eps, OT* out, float* sum_out) {
   __shared__ float red[kNormThreads / 32];
-  const size_t row = blockIdx.x;
-  float v[kNormMaxPerThread];
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t base = (size_t)blockIdx.x * dim;
+  const bool has_res = residual != nullptr;
+  float4 v[kNormVecs], r[kNormVecs], g[kNormVecs];
+#pragma unroll
+  for (int i = 0; i < kNormVecs; ++i) {
+    const int d = 4 * (threadIdx.x + i * kNormThreads);
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    r[i] = v[i];
+    g[i] = v[i];
+    if (d < dim) {
+      v[i] = load4<XT>(x, base + d);
+      if (has_res) r[i] = load4<float>(residual, base + d);
+      g[i] = load4<WT>(w, d);
+    }
+  }
   float sq = 0.f;
 #pragma unroll
-  for (int i = 0; i < kNormMaxPerThread; ++i) {
-    const int d = threadIdx.x + i * kNormThreads;
-    v[i] = 0.f;
-    if (d < dim) {
-      float t = load_as_float(x, x_dt, row * dim + d);
-      if (residual) t += residual[row * dim + d];
-      v[i] = t;
-      sq += t * t;
-    }
+  for (int i = 0; i < kNormVecs; ++i) {
+    v[i].x += r[i].x;
+    v[i].y += r[i].y;
+    v[i].z += r[i].z;
+    v[i].w += r[i].w;
+    sq += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
   }
   const float total = block_sum(sq, red);
   const float inv = 1.0f / sqrtf(total / (float)dim + eps);
 #pragma unroll
-  for (int i = 0; i < kNormMaxPerThread; ++i) {
-    const int d = threadIdx.x + i * kNormThreads;
+  for (int i = 0; i < kNormVecs; ++i) {
+    const int d = 4 * (threadIdx.x + i * kNormThreads);
     if (d < dim) {
-      store_from_float(out, out_dt, row * dim + d, v[i] * inv * load_as_float(w, w_dt, d));
-      if (sum_out) sum_out[row * dim + d] = v[i];
+      store4(out, base + d, make_float4(v[i].x * inv * g[i].x, v[i].y * inv * g[i].y, v[i].z * inv * g[i].z, v[i].w * inv * g[i].w));
+      if (sum_out) store4(sum_out, base + d, v[i]);
     }
+  }
+}
+
+// Any dim <= 8192, any alignment: one element per step (the rarely used fallback).
+__global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const void* x, int x_dt, const float* residual,
+                                                                const void* w, int w_dt, int dim, float eps, void* out,
+                                                                int out_dt, float* sum_out) {
+  __shared__ float red[kNormThreads / 32];
+  __shared__ float row_s[8192];
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t base = (size_t)blockIdx.x * dim;
+  float sq = 0.f;
+  for (int d = threadIdx.x; d < dim; d += kNormThreads) {
+    float t = load_as_float(x, x_dt, base + d);
+    if (residual) t += residual[base + d];
+    row_s[d] = t;
+    sq += t * t;
+  }
+  const float total = block_sum(sq, red);
+  const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+  for (int d = threadIdx.x; d < dim; d += kNormThreads) {
+    store_from_float(out, out_dt, base + d, row_s[d] * inv * load_as_float(w, w_dt, d));
+    if (sum_out) sum_out[base + d] = row_s[d];
   }
 }
 
@@ -92,6 +148,8 @@ __global__ void rope_kernel(const void* x, int x_dt, void* out, int out_dt, cons
 // halves of one fused projection: element (row, i) of gate sits at gate[row*ld + i].
 __global__ void swiglu_kernel(const void* gate, const void* up, int in_dt, size_t ld, size_t rows, size_t n, void* out,
                               int out_dt) {
+  pdl_wait();
+  pdl_launch_dependents();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * n) return;
   const size_t row = idx / n, i = idx % n;
@@ -103,6 +161,8 @@ __global__ void swiglu_kernel(const void* gate, const void* up, int in_dt, size_
 // embedding (cpu.rs:151-167): out[i, :] = weight[ids[i], :].
 __global__ void embedding_kernel(const void* weight, int w_dt, const int* ids, size_t n_ids, size_t dim, size_t vocab,
                                  void* out, int out_dt) {
+  pdl_wait();
+  pdl_launch_dependents();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_ids * dim) return;
   const size_t r = idx / dim, d = idx % dim;
@@ -119,6 +179,8 @@ __global__ void embedding_kernel(const void* weight, int w_dt, const int* ids, s
 __global__ void qkv_post_kernel(const float* qkv, const float* cos_t, const float* sin_t, const int* positions, int B,
                                 int n_heads, int n_kv, int hd, int max_seq, __nv_bfloat16* q_out,
                                 __nv_bfloat16* k_cache, __nv_bfloat16* v_cache, size_t seq_stride) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int half = hd / 2;
   const int pairs_per_row = (n_heads + 2 * n_kv) * half;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -150,11 +212,9 @@ int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const flo
                     int n_heads, int n_kv, int hd, int max_seq, void* q_out, void* k_cache, void* v_cache,
                     size_t seq_stride) {
   const size_t n = (size_t)B * (n_heads + 2 * n_kv) * (hd / 2);
-  qkv_post_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(
-      qkv, cos_t, sin_t, positions, B, n_heads, n_kv, hd, max_seq, static_cast<__nv_bfloat16*>(q_out),
-      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), seq_stride);
-  ctx->launches++;
-  TQ_CUDA(ctx, cudaGetLastError());
+  TQ_CUDA(ctx, launch_k(ctx, qkv_post_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, qkv, cos_t, sin_t, positions, B,
+                        n_heads, n_kv, hd, max_seq, static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+                        static_cast<__nv_bfloat16*>(v_cache), seq_stride));
   return TQ_OK;
 }
 
@@ -170,14 +230,33 @@ int tq_rms_norm(tq_ctx* ctx, const void* x_dev, int x_dtype, const float* residu
                 int w_dtype, size_t n_groups, size_t dim, float eps, void* out_dev, int out_dtype, float* sum_out_dev) {
   if (int st = bind(ctx)) return st;
   TQ_REQUIRE(ctx, io_dtype(x_dtype) && io_dtype(w_dtype) && io_dtype(out_dtype), "tq_rms_norm: dtypes must be f32 or bf16");
-  TQ_REQUIRE(ctx, dim > 0 && dim <= (size_t)kNormThreads * kNormMaxPerThread, "tq_rms_norm: dim must be in 1..%d",
-             kNormThreads * kNormMaxPerThread);
+  TQ_REQUIRE(ctx, dim > 0 && dim <= 8192, "tq_rms_norm: dim must be in 1..8192");
   if (n_groups == 0) return TQ_OK;
   TQ_REQUIRE(ctx, x_dev && weight_dev && out_dev, "tq_rms_norm: null pointer");
-  rms_norm_kernel<<<(unsigned)n_groups, kNormThreads, 0, ctx->stream>>>(x_dev, x_dtype, residual_dev, weight_dev, w_dtype,
-                                                                       (int)dim, eps, out_dev, out_dtype, sum_out_dev);
-  ctx->launches++;
-  TQ_CUDA(ctx, cudaGetLastError());
+  const dim3 grid((unsigned)n_groups), block(kNormThreads);
+  const bool vec = dim % 4 == 0 && (((uintptr_t)x_dev | (uintptr_t)weight_dev | (uintptr_t)out_dev | (uintptr_t)residual_dev |
+                                     (uintptr_t)sum_out_dev) & 15) == 0;
+  using bf = __nv_bfloat16;
+#define TQ_NORM(XT, WT, OT)                                                                                           \
+  TQ_CUDA(ctx, launch_k(ctx, rms_norm_vec_kernel<XT, WT, OT>, grid, block, 0, static_cast<const XT*>(x_dev), residual_dev, \
+                        static_cast<const WT*>(weight_dev), (int)dim, eps, static_cast<OT*>(out_dev), sum_out_dev))
+  const int key = (x_dtype == TQ_BF16) * 4 + (w_dtype == TQ_BF16) * 2 + (out_dtype == TQ_BF16);
+  if (!vec) {
+    TQ_CUDA(ctx, launch_k(ctx, rms_norm_kernel, grid, block, 0, x_dev, x_dtype, residual_dev, weight_dev, w_dtype, (int)dim, eps,
+                          out_dev, out_dtype, sum_out_dev));
+  } else {
+    switch (key) {
+      case 0: TQ_NORM(float, float, float); break;
+      case 1: TQ_NORM(float, float, bf); break;
+      case 2: TQ_NORM(float, bf, float); break;
+      case 3: TQ_NORM(float, bf, bf); break;
+      case 4: TQ_NORM(bf, float, float); break;
+      case 5: TQ_NORM(bf, float, bf); break;
+      case 6: TQ_NORM(bf, bf, float); break;
+      default: TQ_NORM(bf, bf, bf); break;
+    }
+  }
+#undef TQ_NORM
   return TQ_OK;
 }
 
@@ -226,10 +305,8 @@ int tq_swiglu(tq_ctx* ctx, const void* gate_dev, const void* up_dev, int in_dtyp
   if (rows * n == 0) return TQ_OK;
   TQ_REQUIRE(ctx, gate_dev && up_dev && out_dev, "tq_swiglu: null pointer");
   if (ld == 0) ld = n;
-  swiglu_kernel<<<(unsigned)((rows * n + 255) / 256), 256, 0, ctx->stream>>>(gate_dev, up_dev, in_dtype, ld, rows, n, out_dev,
-                                                                            out_dtype);
-  ctx->launches++;
-  TQ_CUDA(ctx, cudaGetLastError());
+  TQ_CUDA(ctx, launch_k(ctx, swiglu_kernel, dim3((unsigned)((rows * n + 255) / 256)), dim3(256), 0, gate_dev, up_dev, in_dtype,
+                        ld, rows, n, out_dev, out_dtype));
   return TQ_OK;
 }
 
@@ -239,10 +316,8 @@ int tq_embedding(tq_ctx* ctx, const void* weight_dev, int w_dtype, const int* id
   TQ_REQUIRE(ctx, io_dtype(w_dtype) && io_dtype(out_dtype), "tq_embedding: dtypes must be f32 or bf16");
   if (seq_len * dim == 0) return TQ_OK;
   TQ_REQUIRE(ctx, weight_dev && ids_dev && out_dev, "tq_embedding: null pointer");
-  embedding_kernel<<<(unsigned)((seq_len * dim + 255) / 256), 256, 0, ctx->stream>>>(weight_dev, w_dtype, ids_dev, seq_len,
-                                                                                    dim, vocab, out_dev, out_dtype);
-  ctx->launches++;
-  TQ_CUDA(ctx, cudaGetLastError());
+  TQ_CUDA(ctx, launch_k(ctx, embedding_kernel, dim3((unsigned)((seq_len * dim + 255) / 256)), dim3(256), 0, weight_dev, w_dtype,
+                        ids_dev, seq_len, dim, vocab, out_dev, out_dtype));
   return TQ_OK;
 }
 

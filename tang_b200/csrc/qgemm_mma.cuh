@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
   const float* row_scales = p.row_scales;
   size_t y_off = 0;
   if (p.grouped) {
+    pdl_wait();   // group tables and row offsets come from earlier kernels of the stream
     const int e = blockIdx.y;
     tiles += (size_t)e * p.g_tile_stride;
     if (row_scales) row_scales += (size_t)e * p.n_rows;
@@ -149,29 +150,37 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
     // ------------------------------------------------------------------ producer warp
     const uint64_t pol_w = l2_policy_evict_first();
     const uint64_t pol_x = l2_policy_evict_last();
-    int s = 0;
-    uint32_t ph = 0;
-    for (int it = 0; it < n_iters; ++it) {
-      if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, failed, p.err, DERR_EMPTY_WAIT)) break;
+    // The weights do not depend on the previous kernel of the stream, the activations do: the first
+    // ring-full of weight tiles is requested before griddepcontrol.wait, the activation rows after.
+    auto issue = [&](int it, int s, bool weights, bool acts) {
       const int kc0 = (p.debug == 2) ? 0 : it * KT;
       const int kcs = min(KT, p.kc_total - kc0);                 // tiles along K in this stage
       const int kxv = max(0, min(KB, p.kx - kc0 * kTileK));       // activation elements in this stage
       const uint32_t wbytes = (uint32_t)(kcs * TB);
       const uint32_t xbytes = (uint32_t)kxv * 2u;
       uint8_t* st = body + (size_t)s * stage_bytes;
-      if (lane == 0)
-        mbar_arrive_expect_tx(&full_bar[s], wbytes * (uint32_t)rbs_valid + (xbytes ? xbytes * (uint32_t)mx : 0u));
-      __syncwarp();
-      for (int i = lane; i < rbs_valid + mx; i += 32) {
-        if (i < rbs_valid) {
-          bulk_g2s(st + (size_t)i * KT * TB, tiles + ((size_t)(rb0 + i) * p.kc_total + kc0) * TB, wbytes, &full_bar[s],
-                   pol_w);
-        } else if (xbytes) {
-          const int m = i - rbs_valid;
-          bulk_g2s(st + x_region + (size_t)m * x_stride, xg + (size_t)m * p.ldx + (size_t)kc0 * kTileK, xbytes,
-                   &full_bar[s], pol_x);
-        }
+      if (weights) {
+        if (lane == 0)
+          mbar_arrive_expect_tx(&full_bar[s], wbytes * (uint32_t)rbs_valid + (xbytes ? xbytes * (uint32_t)mx : 0u));
+        __syncwarp();
+        for (int i = lane; i < rbs_valid; i += 32)
+          bulk_g2s(st + (size_t)i * KT * TB, tiles + ((size_t)(rb0 + i) * p.kc_total + kc0) * TB, wbytes, &full_bar[s], pol_w);
       }
+      if (acts && xbytes)
+        for (int m = lane; m < mx; m += 32)
+          bulk_g2s(st + x_region + (size_t)m * x_stride, xg + (size_t)m * p.ldx + (size_t)kc0 * kTileK, xbytes, &full_bar[s],
+                   pol_x);
+    };
+    const int n_pre = min(S, n_iters);
+    for (int it = 0; it < n_pre; ++it) issue(it, it, true, false);
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int it = 0; it < n_pre; ++it) issue(it, it, false, true);
+    int s = n_pre == S ? 0 : n_pre;
+    uint32_t ph = n_pre == S ? 1u : 0u;
+    for (int it = n_pre; it < n_iters; ++it) {
+      if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, failed, p.err, DERR_EMPTY_WAIT)) break;
+      issue(it, s, true, true);
       if (++s == S) {
         s = 0;
         ph ^= 1u;
@@ -298,6 +307,7 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
   }
 
   // ------------------------------------------------------------------ split-K meet + store
+  pdl_wait();       // results (and the residual) touch memory the previous kernel may still own
   __syncthreads();  // every stage consumed (or the CTA has failed and no copy is awaited)
   const int RS = R + 4;
   float* red = reinterpret_cast<float*>(body);  // [WK][8*NT cols][RS]

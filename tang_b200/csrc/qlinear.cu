@@ -146,14 +146,13 @@ __global__ void prep_x_kernel(const void* x, int x_dtype, size_t ldx, size_t m, 
 }
 
 template <int KIND>
-static cudaError_t launch_nt(int nt, const QGemmParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+static cudaError_t launch_nt(tq_ctx* ctx, int nt, const QGemmParams& p, dim3 grid, dim3 block, size_t smem) {
   auto go = [&](auto kern) -> cudaError_t {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
     }
-    kern<<<grid, block, smem, st>>>(p);
-    return cudaGetLastError();
+    return launch_k(ctx, kern, grid, block, smem, p);
   };
   switch (nt) {
     case 1: return go(qgemm_mma_kernel<KIND, 1>);
@@ -249,12 +248,11 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   dim3 block((unsigned)(32 * (c.wr * c.wk + 1)));
   cudaError_t e;
   switch (w->kind) {
-    case TQ_Q4_F32: e = launch_nt<Q4_F32>(c.nt, p, grid, block, smem, ctx->stream); break;
-    case TQ_Q4_F16: e = launch_nt<Q4_F16>(c.nt, p, grid, block, smem, ctx->stream); break;
-    case TQ_Q8_F32: e = launch_nt<Q8_F32>(c.nt, p, grid, block, smem, ctx->stream); break;
-    default: e = launch_nt<I8_ROW>(c.nt, p, grid, block, smem, ctx->stream); break;
+    case TQ_Q4_F32: e = launch_nt<Q4_F32>(ctx, c.nt, p, grid, block, smem); break;
+    case TQ_Q4_F16: e = launch_nt<Q4_F16>(ctx, c.nt, p, grid, block, smem); break;
+    case TQ_Q8_F32: e = launch_nt<Q8_F32>(ctx, c.nt, p, grid, block, smem); break;
+    default: e = launch_nt<I8_ROW>(ctx, c.nt, p, grid, block, smem); break;
   }
-  ctx->launches++;
   TQ_CUDA(ctx, e);
   return TQ_OK;
 }
