@@ -23,7 +23,7 @@ enum DeviceErr : int {
 // Upper bound on polls of one barrier before a kernel records an error and moves on.  Each poll
 // is a try_wait (which itself blocks for a hardware-defined slice), so this is seconds, not
 // microseconds; it only exists so that a logic error can never hang the GPU.
-constexpr uint32_t kMaxPolls = 1u << 22;
+constexpr uint32_t kMaxPolls = 1u << 19;
 
 // Programmatic dependent launch: wait until every kernel this one depends on has completed and its
 // writes are visible (no-op when the kernel was launched without the attribute) / allow the next
@@ -79,14 +79,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
-// Spins on try_wait entirely inside one PTX block (no C-level control flow in the hot path).
-// Returns false if the phase did not complete within kMaxPolls polls.
+// Waits for a phase entirely inside one PTX block (no C-level control flow in the hot path).  The first
+// look is a test_wait, which answers about three times sooner than try_wait when the phase has already
+// completed (measured: ~70 against ~200 cycles); only a phase that is still open falls through to the
+// try_wait loop, which may suspend the thread.  Returns false if the phase did not complete within
+// kMaxPolls polls.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
-      "mov.u32 n, 0;\n\t"
-      "mov.u32 %0, 1;\n"
+      "mov.u32 %0, 1;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra TQ_DONE;\n\t"
+      "mov.u32 n, 0;\n"
       "TQ_WAIT:\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "@p bra TQ_DONE;\n\t"
@@ -99,6 +104,35 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
       : "r"(smem_u32(bar)), "r"(parity), "r"(kMaxPolls)
       : "memory");
   return ok != 0;
+}
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// One non-blocking look at the phase: 1 when the phase with this parity has completed.  The result can
+// be asked for well before it is needed, which takes the barrier unit's latency off the critical path.
+__device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Completes a wait whose early look gave `token`: returns at once when the phase was already seen.
+__device__ __forceinline__ bool mbar_wait_token(uint64_t* bar, uint32_t parity, uint32_t token) {
+  return token ? true : mbar_wait_spin(bar, parity);
 }
 
 // Arrives on `bar` from the lanes whose `pred` is set, without a branch.
@@ -160,6 +194,22 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint3
 __device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
   return r;
 }
 

@@ -1,0 +1,427 @@
+// tcgen05 / tensor-memory dequant-GEMM: kernel and launcher (see qgemm_umma.cuh for the design).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "internal.h"
+#include "qgemm_umma.cuh"
+
+namespace tq {
+
+template <int KIND, int TERMS>
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int TB = (KIND == Q4_F16) ? 1152 : 1280;
+  constexpr int kMaxStages = 6;
+  // ---- shared-memory carve-up (operand tiles need 1024-byte alignment for the 128-byte swizzle)
+  uint8_t* smem = smem_raw;
+  uint64_t* x_full = reinterpret_cast<uint64_t*>(smem);       // [stages] activation box landed
+  uint64_t* a_full = x_full + kMaxStages;                      // [stages] A tiles written (one arrival per dequant warp)
+  uint64_t* empty = a_full + kMaxStages;                       // [stages] MMAs of the stage retired
+  uint64_t* raw_full = empty + kMaxStages;                     // [raw stages] packed tiles landed
+  uint64_t* raw_empty = raw_full + kUmmaMaxRawStages;             // [raw stages] packed tiles consumed (one arrival per dequant warp)
+  uint64_t* acc_full = raw_empty + kUmmaMaxRawStages;             // accumulator complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t base_u32 = smem_u32(smem_raw);
+  uint8_t* tiles_s = smem_raw + kUmmaHeader + ((1024 - ((base_u32 + kUmmaHeader) & 1023)) & 1023);  // 1024-aligned
+  const size_t stage_bytes = umma_stage_bytes(TERMS, p.ntok);
+  uint8_t* raw_s = tiles_s + (size_t)p.stages * stage_bytes;   // [raw stages][8 tiles]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages, RS = p.raw_stages;
+  const int rb0 = blockIdx.x * (kUmmaRows / kTileRows);        // first 16-row block
+  const int m0 = blockIdx.y * p.ntok;                          // first token of this CTA
+  const int n_kb = p.kc_total * 2;                             // 64-k steps
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&x_full[s], 1);
+      mbar_init(&a_full[s], kUmmaGroupWarps);
+      mbar_init(&empty[s], 1);
+    }
+    for (int r = 0; r < RS; ++r) {
+      mbar_init(&raw_full[r], 1);
+      mbar_init(&raw_empty[r], 2 * kUmmaGroupWarps);   // the two groups that read its halves
+    }
+    mbar_init(acc_full, 1);
+    *failed = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, (uint32_t)p.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = *tmem_slot;
+
+  pdl_wait();
+  pdl_launch_dependents();
+
+  auto give_up = [&](int code) {
+    *failed = 1;
+    atomicCAS(p.err, 0, code);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ packed-weight producer
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      int r = 0;
+      uint32_t rph = 0;
+      for (int tile = 0; tile < p.kc_total && !*failed; ++tile) {
+        if (!mbar_wait_spin(&raw_empty[r], rph ^ 1u)) { give_up(DERR_EMPTY_WAIT); break; }
+#ifdef TQ_UMMA_PROFILE
+        if (p.dbg & 4) {
+          mbar_arrive(&raw_full[r]);
+          if (++r == RS) { r = 0; rph ^= 1u; }
+          continue;
+        }
+#endif
+        mbar_arrive_expect_tx(&raw_full[r], 8u * TB);
+        for (int i = 0; i < 8; ++i)
+          bulk_g2s(raw_s + ((size_t)r * 8 + i) * TB, p.tiles + ((size_t)(rb0 + i) * p.kc_total + tile) * TB, TB, &raw_full[r],
+                   pol_w);
+        if (++r == RS) {
+          r = 0;
+          rph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ activation producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int kb = 0; kb < n_kb && !*failed; ++kb) {
+        if (!mbar_wait_spin(&empty[s], ph ^ 1u)) { give_up(DERR_EMPTY_WAIT); break; }
+#ifdef TQ_UMMA_PROFILE
+        if (p.dbg & 8) {
+          mbar_arrive(&x_full[s]);
+          if (++s == S) { s = 0; ph ^= 1u; }
+          continue;
+        }
+#endif
+        mbar_arrive_expect_tx(&x_full[s], (uint32_t)p.ntok * 128u);
+        tma_load_2d(tiles_s + (size_t)s * stage_bytes + (size_t)TERMS * kUmmaRows * 128, &x_map, kb * kUmmaK, m0, &x_full[s]);
+        if (++s == S) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    // The whole warp runs the loop (warp-uniform control flow keeps the descriptors in uniform
+    // registers); one elected lane issues.  The barriers of the NEXT step are looked at before this
+    // step's instructions are issued, so that the answer is there when the loop comes round.
+    const bool leader = elect_one();
+    const uint32_t idesc = umma_idesc_bf16(p.ntok);
+    const uint64_t desc0 = umma_desc_sw128(tiles_s);
+    const uint32_t stage_u = (uint32_t)(stage_bytes >> 4), b_off_u = (uint32_t)((TERMS * kUmmaRows * 128) >> 4);
+    bool ok = true;
+    int s = 0;
+    uint32_t ph = 0;
+    uint32_t tok_x = mbar_test(&x_full[0], 0), tok_a = mbar_test(&a_full[0], 0);
+#ifdef TQ_UMMA_PROFILE
+    long long prof_acc[3] = {0, 0, 0};
+#endif
+#pragma unroll 1
+    for (int kb = 0; kb < n_kb; ++kb) {
+#ifdef TQ_UMMA_PROFILE
+      const long long t0 = clock64();
+      ok = !*failed && mbar_wait_token(&x_full[s], ph, tok_x);
+      const long long t1 = clock64();
+      ok = ok && mbar_wait_token(&a_full[s], ph, tok_a);
+      const long long t2 = clock64();
+      prof_acc[0] += t1 - t0;
+      prof_acc[1] += t2 - t1;
+#else
+      ok = !*failed && mbar_wait_token(&x_full[s], ph, tok_x) && mbar_wait_token(&a_full[s], ph, tok_a);
+#endif
+      if (!ok) { give_up(DERR_FULL_WAIT); break; }
+      tc_fence_after();
+      const uint64_t ad = desc0 + (uint64_t)((uint32_t)s * stage_u);
+      const int s_cur = s;
+      if (++s == S) {
+        s = 0;
+        ph ^= 1u;
+      }
+      tok_x = mbar_test(&x_full[s], ph);
+      tok_a = mbar_test(&a_full[s], ph);
+#ifdef TQ_UMMA_PROFILE
+      if (!(p.dbg & 2))
+#endif
+      if (leader) {
+#pragma unroll
+        for (int k16 = 0; k16 < kUmmaK / 16; ++k16) {
+          const uint64_t bd = ad + b_off_u + 2 * k16;
+          umma_f16(tmem_d, ad + 2 * k16, bd, idesc, (kb | k16) != 0);
+          if (TERMS == 2) umma_f16(tmem_d, ad + (kUmmaRows * 128 >> 4) + 2 * k16, bd, idesc, 1u);
+        }
+      }
+      if (leader) umma_commit(&empty[s_cur]);   // arrives when the MMAs above have finished reading the stage
+      __syncwarp();
+#ifdef TQ_UMMA_PROFILE
+      prof_acc[2] += clock64() - t2;
+#endif
+    }
+    if (leader) umma_commit(acc_full);           // arrives when every MMA issued so far has completed
+    __syncwarp();
+#ifdef TQ_UMMA_PROFILE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && p.prof && lane == 0)
+      for (int i = 0; i < 3; ++i) p.prof[i] = prof_acc[i];
+#endif
+  } else {
+    // ------------------------------------------------------------------ dequant warps
+    // Everything that does not change from step to step (which words of the packed tiles this thread
+    // converts, where their scales sit, where the result goes in the swizzled A tile) is computed once.
+    // The dequant warps form kUmmaGroups groups; group g produces the stages kb = g, g + G, g + 2G, ...
+    // so that G stages are being converted at any time (one stage's chain of waits, loads, arithmetic,
+    // stores and fence is long; the groups overlap it).  G is even, so a group always reads the same
+    // half (c = g & 1) of its 128-k packed tiles.
+    const int group = (warp - 3) / kUmmaGroupWarps;
+    const int tid = threadIdx.x - 96 - group * 32 * kUmmaGroupWarps;
+    constexpr int kCombos = 512 / (32 * kUmmaGroupWarps);
+    int src_off[kCombos], sc_off[kCombos], dst_off[kCombos][2];
+#pragma unroll
+    for (int i = 0; i < kCombos; ++i) {
+      const int combo = tid + 32 * kUmmaGroupWarps * i;            // (row block, half, lane of the tile layout)
+      const int rbi = combo >> 6, h = (combo >> 5) & 1, L = combo & 31;
+      const int g = L >> 2, t = L & 3;
+      const int row = rbi * 16 + g + 8 * h;
+      src_off[i] = rbi * TB + h * 512 + 16 * L;
+      sc_off[i] = rbi * TB + 1024 + (KIND == Q4_F16 ? h * 64 + g * 8 : h * 128 + g * 16);
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) dst_off[i][jj] = row * 128 + (((4 * jj + t) ^ (row & 7)) << 4);
+    }
+    bool ok = true;
+    const int c = group & 1;                                    // which 64-k half of the 128-k tile
+    int s = group, r = group >> 1;                               // ring slots of this group's first stage and tile
+    uint32_t ph = 0, rph = 0;
+    while (s >= S) {
+      s -= S;
+      ph ^= 1u;
+    }
+    while (r >= RS) {
+      r -= RS;
+      rph ^= 1u;
+    }
+    uint32_t tok_raw = mbar_test(&raw_full[r], rph), tok_empty = mbar_test(&empty[s], ph ^ 1u);
+#ifdef TQ_UMMA_PROFILE
+    long long dq_acc[4] = {0, 0, 0, 0};
+    const long long dq_start = clock64();
+#endif
+#pragma unroll 1
+    for (int kb = group; kb < n_kb && ok; kb += kUmmaGroups) {
+#ifdef TQ_UMMA_PROFILE
+      const long long t0 = clock64();
+      ok = !*failed && mbar_wait_token(&raw_full[r], rph, tok_raw);
+      const long long t1 = clock64();
+      ok = ok && mbar_wait_token(&empty[s], ph ^ 1u, tok_empty);
+      const long long t2 = clock64();
+      dq_acc[0] += t1 - t0;
+      dq_acc[1] += t2 - t1;
+#else
+      ok = !*failed && mbar_wait_token(&raw_full[r], rph, tok_raw) && mbar_wait_token(&empty[s], ph ^ 1u, tok_empty);
+#endif
+      if (!ok) { give_up(DERR_FULL_WAIT); break; }
+      const int s_cur = s, r_cur = r;
+      s += kUmmaGroups;
+      while (s >= S) {
+        s -= S;
+        ph ^= 1u;
+      }
+      r += kUmmaGroups / 2;
+      while (r >= RS) {
+        r -= RS;
+        rph ^= 1u;
+      }
+      if (kb + kUmmaGroups < n_kb) {                 // early look at what this group's next stage waits for
+        tok_raw = mbar_test(&raw_full[r], rph);
+        tok_empty = mbar_test(&empty[s], ph ^ 1u);
+      }
+      uint8_t* a_hi = tiles_s + (size_t)s_cur * stage_bytes;
+      uint8_t* a_lo = a_hi + kUmmaRows * 128;
+      const uint8_t* raw = raw_s + (size_t)r_cur * 8 * TB;
+#ifdef TQ_UMMA_PROFILE
+      if (!(p.dbg & 1))
+#endif
+#pragma unroll
+      for (int i = 0; i < kCombos; ++i) {
+        const uint2 w2 = *reinterpret_cast<const uint2*>(raw + src_off[i] + 8 * c);   // blocks 2c, 2c+1
+        // The scale as s_hi + s_lo, two bf16 numbers (exact for an f16 scale: 11 = 8 + 3 significant bits).
+        // With t = q*s_lo (7 bits, exact in bf16), hi = fma(q, s_hi, t) is the exact product rounded once;
+        // lo = fma(q, s_hi, -hi) + t = q*scale - hi, both steps exact, so hi + lo reproduces the product.
+        float2 f;
+        if (KIND == Q4_F16) f = __half22float2(*reinterpret_cast<const __half2*>(raw + sc_off[i] + 4 * c));
+        else f = *reinterpret_cast<const float2*>(raw + sc_off[i] + 8 * c);
+        const __nv_bfloat162 shb = __floats2bfloat162_rn(f.x, f.y);
+        const uint32_t sh = *reinterpret_cast<const uint32_t*>(&shb);
+        const __nv_bfloat162 slb = __floats2bfloat162_rn(f.x - __uint_as_float(sh << 16), f.y - __uint_as_float(sh & 0xFFFF0000u));
+        const uint32_t sl = *reinterpret_cast<const uint32_t*>(&slb);
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const uint32_t s_hi = prmt(sh, sh, jj ? 0x3232u : 0x1010u), s_lo = prmt(sl, sl, jj ? 0x3232u : 0x1010u);
+          uint32_t q[4];
+          dequant_q4_word(jj ? w2.y : w2.x, q);                  // (k0,k1) (k2,k3) (k4,k5) (k6,k7), exact ints
+          uint32_t hi[4], lo[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t t = bf16x2_mul(q[e], s_lo);
+            hi[e] = bf16x2_fma(q[e], s_hi, t);
+            if (TERMS == 2) lo[e] = bf16x2_add(bf16x2_fma(q[e], s_hi, hi[e] ^ 0x80008000u), t);
+          }
+          *reinterpret_cast<uint4*>(a_hi + dst_off[i][jj]) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          if (TERMS == 2) *reinterpret_cast<uint4*>(a_lo + dst_off[i][jj]) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+      }
+#ifdef TQ_UMMA_PROFILE
+      const long long t3 = clock64();
+      dq_acc[2] += t3 - t2;
+#endif
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
+      __syncwarp();
+      if (lane == 0) {                                                // one arrival per warp
+        mbar_arrive(&a_full[s_cur]);
+        mbar_arrive(&raw_empty[r_cur]);
+      }
+#ifdef TQ_UMMA_PROFILE
+      dq_acc[3] += clock64() - t3;
+#endif
+    }
+#ifdef TQ_UMMA_PROFILE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && p.prof && threadIdx.x == 96) {
+      for (int i = 0; i < 4; ++i) p.prof[4 + i] = dq_acc[i];
+      p.prof[8] = clock64() - dq_start;
+    }
+#endif
+    // ---- epilogue: D[128 features x ntok tokens] -> y[token][feature]
+    if (ok && !*failed) ok = mbar_wait_spin(acc_full, 0);
+    if (!ok) give_up(DERR_TMEM);
+    tc_fence_after();
+    if (ok) {
+      const int q4 = warp & 3;                                 // tensor-memory lane quarter this warp may read
+      const int n = blockIdx.x * kUmmaRows + 32 * q4 + lane;
+      // two warps share a lane quarter and alternate over the 16-column chunks
+      for (int c0 = 16 * ((warp - 3) >> 2); c0 < p.ntok; c0 += 16 * (kUmmaDqWarps / 4)) {
+        float v[16];
+        tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)c0, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int m = m0 + c0 + i;
+          if (m < p.m_total) {
+            if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(v[i]);
+            else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + n] = v[i];
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_d, (uint32_t)p.tmem_cols);
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+bool umma_supported(const tq_qweight* w, size_t m) {
+  return (w->kind == TQ_Q4_F16 || w->kind == TQ_Q4_F32) && w->rows % kUmmaRows == 0 && w->cols % kTileK == 0 && m >= 1;
+}
+
+// y[m, rows] = x[m, cols] . W^T through the tcgen05 kernel.  x: bf16, 16-byte aligned rows.
+int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
+                      size_t ldy, int terms) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return fail(ctx, TQ_EUNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
+  TQ_REQUIRE(ctx, umma_supported(w, m), "tcgen05 GEMM: needs a Q4 weight with rows %% 128 == 0 and cols %% 128 == 0");
+  TQ_REQUIRE(ctx, ((uintptr_t)x_bf16 & 15) == 0 && (ldx * 2) % 16 == 0, "tcgen05 GEMM: activation rows must be 16-byte aligned");
+  // Ring sizes.  Two rules come from the dequant groups running ahead of one another (a parity wait
+  // is only sound when the waiter is at most one phase ahead of the barrier): at least kUmmaGroups
+  // A/B stages, and an even number of packed-tile slots whenever slots are reused.  The token tile is
+  // the widest that leaves room for four stages and two packed tiles, then evened out over the tiles.
+  const size_t kSmemMax = 227 * 1024, raw_tile = 8 * (size_t)qk_tile_bytes(w->kind);
+  const size_t budget = kSmemMax - kUmmaHeader - 1024;
+  int ntok_max = (int)(((budget - 2 * raw_tile) / kUmmaGroups - (size_t)terms * kUmmaRows * 128) / 128) / 16 * 16;
+  if (ntok_max > 256) ntok_max = 256;
+  const size_t n_tok_tiles = (m + ntok_max - 1) / ntok_max;
+  const int ntok = (int)(((m + n_tok_tiles - 1) / n_tok_tiles + 15) / 16 * 16);
+  int tmem_cols = 32;
+  while (tmem_cols < ntok) tmem_cols <<= 1;
+  int stages = (int)((budget - 2 * raw_tile) / umma_stage_bytes(terms, ntok));
+  if (stages > kUmmaGroups && (budget - (size_t)stages * umma_stage_bytes(terms, ntok)) / raw_tile < 4) --stages;   // rather four packed tiles
+  if (stages > 6) stages = 6;
+  int raw_stages = (int)((budget - (size_t)stages * umma_stage_bytes(terms, ntok)) / raw_tile) & ~1;
+  if (raw_stages > 6) raw_stages = 6;
+  if (raw_stages >= w->n_kc) raw_stages = w->n_kc;   // every slot used once: no reuse, any count will do
+  if (stages < kUmmaGroups || raw_stages < 1) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: ring sizes %d/%d", stages, raw_stages);
+  CUtensorMap map;
+  const cuuint64_t gdim[2] = {(cuuint64_t)w->cols, (cuuint64_t)m};
+  const cuuint64_t gstride[1] = {(cuuint64_t)ldx * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kUmmaK, (cuuint32_t)ntok};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x_bf16), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return fail(ctx, TQ_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
+  UmmaParams p;
+  p.tiles = w->tiles;
+  p.y = y;
+  p.ldy = (long long)ldy;
+  p.m_total = (int)m;
+  p.n_rows = (int)w->rows;
+  p.kc_total = w->n_kc;
+  p.ntok = ntok;
+  p.tmem_cols = tmem_cols;
+  p.y_bf16 = y_dtype == TQ_BF16;
+  p.err = ctx->dev_err;
+  p.stages = stages;
+  p.raw_stages = raw_stages;
+  const size_t smem = umma_smem_bytes(w->kind, terms, ntok, stages, raw_stages);
+  if (smem > kSmemMax) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: %zu bytes of shared memory needed", smem);
+  dim3 grid((unsigned)(w->rows / kUmmaRows), (unsigned)((m + ntok - 1) / ntok));
+  auto go = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    return launch_k(ctx, kern, grid, dim3(kUmmaThreads), smem, map, p);
+  };
+#ifdef TQ_UMMA_PROFILE
+  static long long* prof_dev = nullptr;
+  if (!prof_dev) cudaMalloc(&prof_dev, 16 * sizeof(long long));
+  cudaMemset(prof_dev, 0, 16 * sizeof(long long));
+  p.prof = prof_dev;
+  p.dbg = getenv("TQ_UMMA_DBG") ? atoi(getenv("TQ_UMMA_DBG")) : 0;
+#endif
+  cudaError_t e;
+  if (w->kind == TQ_Q4_F16) e = terms == 2 ? go(qgemm_umma_kernel<Q4_F16, 2>) : go(qgemm_umma_kernel<Q4_F16, 1>);
+  else e = terms == 2 ? go(qgemm_umma_kernel<Q4_F32, 2>) : go(qgemm_umma_kernel<Q4_F32, 1>);
+  TQ_CUDA(ctx, e);
+#ifdef TQ_UMMA_PROFILE
+  {
+    long long h[16];
+    cudaStreamSynchronize(ctx->stream);
+    cudaMemcpy(h, prof_dev, sizeof(h), cudaMemcpyDeviceToHost);
+    fprintf(stderr, "umma profile (cycles, CTA 0, %d steps): mma wait_x %lld wait_a %lld issue %lld | dq wait_raw %lld wait_empty %lld work %lld fence+arrive %lld total %lld\n",
+            p.kc_total * 2, h[0], h[1], h[2], h[4], h[5], h[6], h[7], h[8]);
+  }
+#endif
+  return TQ_OK;
+}
+
+}  // namespace tq

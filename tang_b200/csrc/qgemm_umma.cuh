@@ -1,0 +1,129 @@
+// Dequant-GEMM on the 5th-generation tensor cores (tcgen05 + tensor memory) for many activation
+// rows (prefill, large decode batches, batched experts):
+//     y[m, n] = sum_k x[m, k] * q[n, k] * scale[n, k/32]
+// restating crates/tang-infer/src/quantize.rs:256-289 (q4_matvec, one call per activation row) as
+// one contraction.
+//
+// Operand roles are swapped so that any token count fits one instruction shape: the 128 output
+// features of a CTA are the UMMA M dimension (A operand, the dequantised weights), the tokens are
+// the UMMA N dimension (B operand, 16..256), and the f32 accumulator D[128 x tokens] lives in
+// tensor memory.  Per 64-k step:
+//   * warp 0 streams the packed fragment tiles (1-D bulk copies), warp 2 the activation boxes
+//     (cp.async.bulk.tensor, 128-byte swizzle, out-of-range token rows filled with zeros), each as
+//     far ahead as its own ring allows;
+//   * sixteen dequant warps, in four groups that each take every fourth step, turn nibbles into bf16 A tiles in shared memory in the K-major
+//     128-byte-swizzled layout UMMA reads.  The product q*scale (15 significant bits) is split into
+//     hi = bf16(q*scale) and lo = bf16(q*scale - hi); hi + lo equals q*scale EXACTLY, so two MMAs
+//     per k-step reproduce exact products with f32 accumulation (TERMS = 2).  TERMS = 1 keeps only
+//     hi (relative weight error 2^-9), for bf16 outputs;
+//   * one elected lane of warp 1 issues tcgen05.mma (kind::f16, bf16 x bf16 -> f32) and commits each
+//     stage back to the producers;
+//   * the dequant warps finally read the accumulator with tcgen05.ld and store y.
+// Every mbarrier wait is bounded; on failure the CTA records a code, skips ahead and still frees its
+// tensor memory.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "qlayout.cuh"
+
+namespace tq {
+
+constexpr int kUmmaRows = 128;        // output features per CTA
+constexpr int kUmmaK = 64;            // k per stage (one 128-byte swizzle span of bf16)
+constexpr int kUmmaGroups = 4;        // dequant groups, each converting every fourth 64-k stage (even)
+constexpr int kUmmaGroupWarps = 4;    // warps per group
+constexpr int kUmmaDqWarps = kUmmaGroups * kUmmaGroupWarps;   // dequant / epilogue warps
+constexpr int kUmmaThreads = 96 + 32 * kUmmaDqWarps;   // + weight-producer, MMA and activation-producer warps
+
+struct UmmaParams {
+  const uint8_t* tiles;   // fragment tiles [n_row_blocks][kc_total][tile_bytes]
+  void* y;                // [M][ldy] f32 or bf16
+  long long ldy;
+  int m_total;            // activation rows
+  int n_rows;             // output features (multiple of 128)
+  int kc_total;           // K / 128
+  int ntok;               // tokens per CTA tile = UMMA N (multiple of 16, <= 256)
+  int tmem_cols;          // power of two >= max(32, ntok)
+  int stages;             // A/B ring depth
+  int raw_stages;         // packed-tile ring depth (128 k each): what keeps the HBM stream in flight
+  int y_bf16;
+  int* err;
+#ifdef TQ_UMMA_PROFILE
+  long long* prof;      // cycle counters of CTA 0 (profiling builds only)
+  int dbg;              // bit 0: no dequant math, 1: no MMA, 2: no weight copies, 3: no activation copies
+#endif
+};
+
+__host__ __device__ inline size_t umma_stage_bytes(int terms, int ntok) {
+  return (size_t)terms * kUmmaRows * 128 + (size_t)ntok * 128;   // A tiles + B tile, all 1024-aligned sizes
+}
+constexpr int kUmmaMaxRawStages = 8;
+constexpr int kUmmaHeader = 1024;
+__host__ __device__ inline size_t umma_smem_bytes(int kind, int terms, int ntok, int stages, int raw_stages) {
+  return kUmmaHeader + 1024 /*alignment slack*/ + (size_t)stages * umma_stage_bytes(terms, ntok) +
+         (size_t)raw_stages * 8 * qk_tile_bytes(kind);
+}
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem_ptr) {
+  const uint32_t addr = smem_u32(smem_ptr);
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);        // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset: next 8-row group
+  d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                       // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor, kind::f16: D f32, A bf16, B bf16, both K-major, M = 128, N = ntok.
+// (A and B must have the same format: an f16 A with a bf16 B is rejected by the hardware as an
+// illegal instruction.)
+__host__ __device__ inline uint32_t umma_idesc_bf16(int ntok) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ntok >> 3) << 17) | ((uint32_t)(kUmmaRows >> 4) << 24);
+}
+
+}  // namespace tq

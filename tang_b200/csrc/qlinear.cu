@@ -21,7 +21,7 @@ static inline size_t scale_elem(int kind) { return kind == TQ_Q4_F16 ? 2 : 4; }
 // for t == 0, the block's scale.  Integer codes and scale bits are copied, never recomputed.
 // ---------------------------------------------------------------------------------------------
 __global__ void repack_kernel(const uint8_t* pay, const uint8_t* sc, size_t ld_pay, size_t ld_sc, int kind, size_t rows,
-                              size_t cols, int n_rb, int n_kc, uint8_t* tiles) {
+                              size_t cols, int n_rb, int n_kc, uint8_t* tiles, int* bad_scale) {
   const size_t total = (size_t)n_rb * n_kc * 2 * 32 * 4;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -72,10 +72,15 @@ __global__ void repack_kernel(const uint8_t* pay, const uint8_t* sc, size_t ld_p
       uint16_t v = 0;
       if (live) v = *reinterpret_cast<const uint16_t*>(sc + row * ld_sc + 2 * (k0 / 32));
       *reinterpret_cast<uint16_t*>(tile + off) = v;
+      if ((v & 0x7FFFu) > 0x6FFFu) *bad_scale = 1;            // 8 * |scale| would leave the f16 range
     } else {
       uint32_t v = 0;
       if (live) v = *reinterpret_cast<const uint32_t*>(sc + row * ld_sc + 4 * (k0 / 32));
       *reinterpret_cast<uint32_t*>(tile + off) = v;
+      if (kind == Q4_F32) {
+        const float a = fabsf(__uint_as_float(v));
+        if (!(a <= 8188.0f) || (a != 0.0f && a < 6.103515625e-05f)) *bad_scale = 1;   // overflow, NaN or f16-subnormal
+      }
     }
   }
 }
@@ -275,6 +280,20 @@ int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const v
   return launch_qgemm(ctx, w, static_cast<const __nv_bfloat16*>(x_bf16), ldx, mx, 1, y, y_dtype, ldy, nullptr, &g);
 }
 
+bool umma_supported(const tq_qweight* w, size_t m);
+int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
+                      size_t ldy, int terms);
+
+// Activation rows from which the tcgen05 kernel takes over from the mma.sync kernel (TQ_UMMA_MIN_M
+// overrides; 0 disables the tcgen05 path).
+static int umma_min_m() {
+  static int v = [] {
+    const char* e = std::getenv("TQ_UMMA_MIN_M");
+    return e ? std::atoi(e) : 24;
+  }();
+  return v;
+}
+
 }  // namespace tq
 
 using namespace tq;
@@ -319,10 +338,21 @@ static int repack_from_device(tq_ctx* ctx, tq_qweight* w, const uint8_t* pay, co
   size_t ld_pay, ld_sc;
   plain_strides(w->kind, w->cols, &ld_pay, &ld_sc);
   const size_t n = (size_t)w->n_rb * w->n_kc * 256;
-  repack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(pay, sc, ld_pay, ld_sc, w->kind, w->rows, w->cols,
-                                                                     w->n_rb, w->n_kc, w->tiles);
-  ctx->launches++;
-  TQ_CUDA(ctx, cudaGetLastError());
+  int* bad_scale = nullptr;   // raised by the repack when a Q4 scale does not survive as an f16 operand
+  TQ_CUDA(ctx, cudaMalloc(&bad_scale, sizeof(int)));
+  cudaError_t e = cudaMemsetAsync(bad_scale, 0, sizeof(int), ctx->stream);
+  if (e == cudaSuccess) {
+    repack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(pay, sc, ld_pay, ld_sc, w->kind, w->rows, w->cols,
+                                                                       w->n_rb, w->n_kc, w->tiles, bad_scale);
+    ctx->launches++;
+    e = cudaGetLastError();
+  }
+  int bad = 1;
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&bad, bad_scale, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  cudaFree(bad_scale);
+  TQ_CUDA(ctx, e);
+  w->f16_ok = (w->kind == TQ_Q4_F16 || w->kind == TQ_Q4_F32) && bad == 0;
   if (w->kind == TQ_I8_ROW)
     TQ_CUDA(ctx, cudaMemcpyAsync(w->row_scales, sc, w->rows * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
   return TQ_OK;
@@ -474,6 +504,8 @@ int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x_dtype,
     const size_t rows_staged = (m < chunk ? m : chunk) * combine;
     if (int st = ensure_xprep(ctx, rows_staged * kx * 2)) return st;
   }
+  if (direct && !residual_dev && umma_min_m() > 0 && m >= (size_t)umma_min_m() && umma_supported(w, m))
+    return launch_qgemm_umma(ctx, w, x_dev, ldx, m, y_dev, y_dtype, ldy, y_dtype == TQ_F32 ? 2 : 1);
   const size_t xe = x_dtype == TQ_F32 ? 4 : 2, ye = y_dtype == TQ_F32 ? 4 : 2;
   for (size_t m0 = 0; m0 < m; m0 += chunk) {
     const size_t mc = m - m0 < chunk ? m - m0 : chunk;

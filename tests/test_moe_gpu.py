@@ -35,8 +35,10 @@ def check(dev, orc, host, T, seed):
     assert np.array_equal(idx.to_vec().reshape(T, host.k), idx_o)
     got = out.to_vec().reshape(T, host.d)
     # the SwiGLU output is rounded to bf16 on both sides; an f32-vs-f64 difference ahead of that rounding can
-    # flip single elements by one bf16 ulp, so the bar is taken against max(|ref|, rms(ref))
-    assert rel_err(got, want, floor_frac=1.0) < 1e-3, T
+    # flip single elements by one bf16 ulp, so the bar is taken against max(|ref|, rms(ref)).  From 24 tokens
+    # on, the shared experts' bf16-output linears run on the tensor-memory GEMM, which rounds each product
+    # q*scale to bf16 once (relative 2^-9, the step of the bf16 output itself): observed 2.6e-3.
+    assert rel_err(got, want, floor_frac=1.0) < (1e-3 if T < 24 else 5e-3), T
     layer.destroy()
 
 
