@@ -65,11 +65,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// One non-blocking look at the phase: 1 when the phase with this parity has completed.  The result can
+// be asked for well before it is needed, which takes the barrier unit's latency off the critical path.
+__device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
 // Waits for the given phase parity.  Returns false (after recording `code` in *err and raising the
 // CTA-wide `failed` flag) if the phase does not complete within kMaxPolls polls, or at once if
 // another thread of the CTA has already failed.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* failed, int* err,
                                                   int code) {
+  if (mbar_test(bar, parity)) return true;   // a completed phase answers about three times sooner this way
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*failed) return false;
@@ -117,19 +131,6 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
-// One non-blocking look at the phase: 1 when the phase with this parity has completed.  The result can
-// be asked for well before it is needed, which takes the barrier unit's latency off the critical path.
-__device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok;
-}
 // Completes a wait whose early look gave `token`: returns at once when the phase was already seen.
 __device__ __forceinline__ bool mbar_wait_token(uint64_t* bar, uint32_t parity, uint32_t token) {
   return token ? true : mbar_wait_spin(bar, parity);
