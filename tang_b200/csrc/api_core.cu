@@ -37,6 +37,20 @@ int ensure_scratch(tq_ctx* ctx, size_t bytes) {
   return TQ_OK;
 }
 
+int ensure_splitk(tq_ctx* ctx, size_t bytes) {
+  if (ctx->splitk_bytes >= bytes) return TQ_OK;
+  if (ctx->splitk) {
+    TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    TQ_CUDA(ctx, cudaFree(ctx->splitk));
+    ctx->splitk = nullptr;
+    ctx->splitk_bytes = 0;
+  }
+  size_t want = bytes < (8u << 20) ? (8u << 20) : bytes;
+  TQ_CUDA(ctx, cudaMalloc(&ctx->splitk, want));
+  ctx->splitk_bytes = want;
+  return TQ_OK;
+}
+
 __global__ void convert_kernel(const void* src, int sdt, void* dst, int ddt, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -84,8 +98,8 @@ int tq_ctx_create(int device, void* stream, tq_ctx** out) {
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(TQ_ECUDA);
     ctx->owns_stream = true;
   }
-  if (cudaMalloc(&ctx->dev_err, sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
-  if (cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMalloc(&ctx->dev_err, (1 + kTileCounters) * sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMemsetAsync(ctx->dev_err, 0, (1 + kTileCounters) * sizeof(int), ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
   *out = ctx;
   return TQ_OK;
@@ -97,6 +111,7 @@ int tq_ctx_destroy(tq_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->xprep) cudaFree(ctx->xprep);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->splitk) cudaFree(ctx->splitk);
   if (ctx->dev_err) cudaFree(ctx->dev_err);
   if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;

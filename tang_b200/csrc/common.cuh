@@ -228,6 +228,18 @@ __device__ __forceinline__ void dequant_q4_word(uint32_t w, uint32_t (&out)[4]) 
   out[3] = bf16x2_sub(lop3_and_or(w >> 12, kMask, kMagic), kBias);
 }
 
+// The same unpacking without the bias removal: out holds 128 + n = 136 + q.  A contraction over these
+// is corrected by one more MMA whose A operand is the constant -136 (kNeg136x2 in every register):
+// sum (136 + q) x + sum (-136) x = sum q x, with every product still exact in f32.
+constexpr uint32_t kNeg136x2 = 0xC308C308u;
+__device__ __forceinline__ void dequant_q4_word_biased(uint32_t w, uint32_t (&out)[4]) {
+  constexpr uint32_t kMask = 0x000F000Fu, kMagic = 0x43004300u;
+  out[0] = lop3_and_or(w, kMask, kMagic);
+  out[1] = lop3_and_or(w >> 4, kMask, kMagic);
+  out[2] = lop3_and_or(w >> 8, kMask, kMagic);
+  out[3] = lop3_and_or(w >> 12, kMask, kMagic);
+}
+
 // Converts eight int8 (two words: bytes k0..k3 and k4..k7) to bf16x2 registers in the same
 // pairing as dequant_q4_word: out[i] = (q_i, q_{i+4}).  Each byte is biased to unsigned, dropped
 // into the mantissa of 2^23 (f32), the bias removed with one exact subtraction, and the pair is

@@ -10,15 +10,20 @@
 
 #include "../../include/tangq.h"
 
+constexpr int kTileCounters = 1024;
+
 struct tq_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
   bool owns_stream = false;
-  int* dev_err = nullptr;        // device status word written by kernels that give up a bounded wait
+  int* dev_err = nullptr;        // device status word written by kernels that give up a bounded wait,
+                                 // followed by kTileCounters zeroed tile counters (split-K meets)
   void* xprep = nullptr;         // activation staging for tq_qlinear (bf16 copy / 3-way f32 split)
   size_t xprep_bytes = 0;
   void* scratch = nullptr;       // general workspace (attention partials, host-call staging, ...)
   size_t scratch_bytes = 0;
+  void* splitk = nullptr;        // f32 partials of split-K GEMMs; separate because callers that carve
+  size_t splitk_bytes = 0;       // their own buffers out of `scratch` run linear layers in between
   int sm_count = 148;
   int cfg_wr = 0, cfg_wk = 0, cfg_stages = 0, cfg_tpw = 0;  // tq_qlinear_set_config override
   unsigned long long launches = 0;             // kernels launched through this context
@@ -72,6 +77,7 @@ inline int bind(tq_ctx* ctx) {
 
 int ensure_xprep(tq_ctx* ctx, size_t bytes);
 int ensure_scratch(tq_ctx* ctx, size_t bytes);
+int ensure_splitk(tq_ctx* ctx, size_t bytes);
 
 // Launches `kern` on the context's stream.  With programmatic dependent launch enabled (default;
 // TQ_PDL=0 turns it off) the launch carries the programmatic-stream-serialization attribute, so the

@@ -32,7 +32,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
   const int S = p.stages, RS = p.raw_stages;
   const int rb0 = blockIdx.x * (kUmmaRows / kTileRows);        // first 16-row block
   const int m0 = blockIdx.y * p.ntok;                          // first token of this CTA
-  const int n_kb = p.kc_total * 2;                             // 64-k steps
+  const int kc_begin = blockIdx.z * p.kc_per_split;            // this CTA's slice of K, in 128-k tiles
+  const int kc_len = min(p.kc_per_split, p.kc_total - kc_begin);
+  const int n_kb = kc_len * 2;                                 // 64-k steps
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -68,7 +70,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       const uint64_t pol_w = l2_policy_evict_first();
       int r = 0;
       uint32_t rph = 0;
-      for (int tile = 0; tile < p.kc_total && !*failed; ++tile) {
+      for (int tile = 0; tile < kc_len && !*failed; ++tile) {
         if (!mbar_wait_spin(&raw_empty[r], rph ^ 1u)) { give_up(DERR_EMPTY_WAIT); break; }
 #ifdef TQ_UMMA_PROFILE
         if (p.dbg & 4) {
@@ -79,7 +81,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
 #endif
         mbar_arrive_expect_tx(&raw_full[r], 8u * TB);
         for (int i = 0; i < 8; ++i)
-          bulk_g2s(raw_s + ((size_t)r * 8 + i) * TB, p.tiles + ((size_t)(rb0 + i) * p.kc_total + tile) * TB, TB, &raw_full[r],
+          bulk_g2s(raw_s + ((size_t)r * 8 + i) * TB, p.tiles + ((size_t)(rb0 + i) * p.kc_total + kc_begin + tile) * TB, TB,
+                   &raw_full[r],
                    pol_w);
         if (++r == RS) {
           r = 0;
@@ -102,7 +105,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         }
 #endif
         mbar_arrive_expect_tx(&x_full[s], (uint32_t)p.ntok * 128u);
-        tma_load_2d(tiles_s + (size_t)s * stage_bytes + (size_t)TERMS * kUmmaRows * 128, &x_map, kb * kUmmaK, m0, &x_full[s]);
+        tma_load_2d(tiles_s + (size_t)s * stage_bytes + (size_t)TERMS * kUmmaRows * 128, &x_map,
+                    (kc_begin * 2 + kb) * kUmmaK, m0, &x_full[s]);
         if (++s == S) {
           s = 0;
           ph ^= 1u;
@@ -306,12 +310,22 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       for (int c0 = 16 * ((warp - 3) >> 2); c0 < p.ntok; c0 += 16 * (kUmmaDqWarps / 4)) {
         float v[16];
         tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)c0, v);
+        if (p.splits > 1) {
+          // K is split over gridDim.z CTAs: park the f32 partial; the last CTA of the tile adds them up
+          float* part = p.partial + (size_t)blockIdx.z * p.m_total * p.n_rows;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int m = m0 + c0 + i;
-          if (m < p.m_total) {
-            if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(v[i]);
-            else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + n] = v[i];
+          for (int i = 0; i < 16; ++i) {
+            const int m = m0 + c0 + i;
+            if (m < p.m_total) __stcg(part + (size_t)m * p.n_rows + n, v[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = m0 + c0 + i;
+            if (m < p.m_total) {
+              if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(v[i]);
+              else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + n] = v[i];
+            }
           }
         }
       }
@@ -320,6 +334,34 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_d, (uint32_t)p.tmem_cols);
+  if (p.splits > 1) {
+    // Deterministic split-K meet: every CTA of the tile counts in after its partial is visible; the one
+    // that counts in last sums the partials in split order (so the result does not depend on which CTA
+    // that was), writes y and leaves the counter at zero for the next launch.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    int* counter = p.counters + blockIdx.y * gridDim.x + blockIdx.x;
+    if (threadIdx.x == 0) {
+      const int seen = atomicAdd(counter, 1);
+      is_last = seen == p.splits - 1;
+      if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      const int m_hi = min(p.ntok, p.m_total - m0);
+      const size_t plane = (size_t)p.m_total * p.n_rows;
+      for (int idx = threadIdx.x; idx < m_hi * kUmmaRows; idx += blockDim.x) {
+        const int m = m0 + idx / kUmmaRows, n = blockIdx.x * kUmmaRows + idx % kUmmaRows;
+        const float* src = p.partial + (size_t)m * p.n_rows + n;
+        float sum = 0.f;
+        for (int z = 0; z < p.splits; ++z) sum += __ldcg(src + z * plane);
+        if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(sum);
+        else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + n] = sum;
+      }
+    }
+  }
 }
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -362,6 +404,20 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   if (ntok_max > 256) ntok_max = 256;
   const size_t n_tok_tiles = (m + ntok_max - 1) / ntok_max;
   const int ntok = (int)(((m + n_tok_tiles - 1) / n_tok_tiles + 15) / 16 * 16);
+  // Few output tiles (narrow layers, small batches) leave most SMs idle: split K over gridDim.z.
+  const int base_ctas = (int)(w->rows / kUmmaRows) * (int)n_tok_tiles;
+  int splits = 1;
+  if (base_ctas < (ctx->sm_count * 3) / 4) {
+    splits = ctx->sm_count / base_ctas;
+    if (splits > w->n_kc / 4) splits = w->n_kc / 4;      // at least eight 64-k steps per CTA
+    if (splits > 16) splits = 16;
+    // the f32 partials are written and read once more: keep them below the bytes of the weights themselves
+    const size_t wbytes = (size_t)w->n_rb * w->n_kc * qk_tile_bytes(w->kind), pbytes = m * w->rows * 8;
+    if ((size_t)splits > wbytes / pbytes) splits = (int)(wbytes / pbytes);
+    if (splits < 1) splits = 1;
+  }
+  const int kc_per_split = (w->n_kc + splits - 1) / splits;
+  splits = (w->n_kc + kc_per_split - 1) / kc_per_split;
   int tmem_cols = 32;
   while (tmem_cols < ntok) tmem_cols <<= 1;
   int stages = (int)((budget - 2 * raw_tile) / umma_stage_bytes(terms, ntok));
@@ -369,7 +425,7 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   if (stages > 6) stages = 6;
   int raw_stages = (int)((budget - (size_t)stages * umma_stage_bytes(terms, ntok)) / raw_tile) & ~1;
   if (raw_stages > 6) raw_stages = 6;
-  if (raw_stages >= w->n_kc) raw_stages = w->n_kc;   // every slot used once: no reuse, any count will do
+  if (raw_stages >= kc_per_split) raw_stages = kc_per_split;   // every slot used once: no reuse, any count will do
   if (stages < kUmmaGroups || raw_stages < 1) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: ring sizes %d/%d", stages, raw_stages);
   CUtensorMap map;
   const cuuint64_t gdim[2] = {(cuuint64_t)w->cols, (cuuint64_t)m};
@@ -391,11 +447,20 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.tmem_cols = tmem_cols;
   p.y_bf16 = y_dtype == TQ_BF16;
   p.err = ctx->dev_err;
+  p.splits = splits;
+  p.kc_per_split = kc_per_split;
+  p.partial = nullptr;
+  p.counters = ctx->dev_err + 1;
+  if (splits > 1) {
+    if (base_ctas > kTileCounters) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: %d output tiles with split K", base_ctas);
+    if (int st = ensure_splitk(ctx, (size_t)splits * m * w->rows * sizeof(float))) return st;
+    p.partial = static_cast<float*>(ctx->splitk);
+  }
   p.stages = stages;
   p.raw_stages = raw_stages;
   const size_t smem = umma_smem_bytes(w->kind, terms, ntok, stages, raw_stages);
   if (smem > kSmemMax) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: %zu bytes of shared memory needed", smem);
-  dim3 grid((unsigned)(w->rows / kUmmaRows), (unsigned)((m + ntok - 1) / ntok));
+  dim3 grid((unsigned)(w->rows / kUmmaRows), (unsigned)((m + ntok - 1) / ntok), (unsigned)splits);
   auto go = [&](auto kern) -> cudaError_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

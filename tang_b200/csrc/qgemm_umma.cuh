@@ -49,6 +49,10 @@ struct UmmaParams {
   int stages;             // A/B ring depth
   int raw_stages;         // packed-tile ring depth (128 k each): what keeps the HBM stream in flight
   int y_bf16;
+  int splits;             // CTAs along K per output tile (gridDim.z)
+  int kc_per_split;       // 128-k tiles per split
+  float* partial;         // [splits][m_total][n_rows] f32, only when splits > 1
+  int* counters;          // one per output tile, zero between launches
   int* err;
 #ifdef TQ_UMMA_PROFILE
   long long* prof;      // cycle counters of CTA 0 (profiling builds only)

@@ -242,6 +242,9 @@ def test_tensor_memory_gemm(dev, orc, kind, rows, cols, m):
     dev.sync()
     yb = (yb.astype(np.uint32) << 16).view(np.float32)
     assert rel_err(yb[sel], want, floor_frac=1.0) < TOL_BF16
-    # rows of the batch are independent: the first 24 rows alone give the same f32 result bit for bit
+    # rows of the batch are independent (a smaller batch may split K differently, so not bit for bit)
     y24 = dev.qlinear(dev.upload(xbits[:24], tb.BF16), w, 24, tb.F32).to_vec().reshape(24, rows)
-    assert np.array_equal(y24, y[:24])
+    assert rel_err(y24, y[:24], floor_frac=1.0) < 1e-4
+    # and the split-K meet adds its partials in a fixed order: the same call gives the same bits
+    y24b = dev.qlinear(dev.upload(xbits[:24], tb.BF16), w, 24, tb.F32).to_vec().reshape(24, rows)
+    assert np.array_equal(y24, y24b)
