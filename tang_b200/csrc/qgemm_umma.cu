@@ -46,7 +46,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       mbar_init(&raw_full[r], 1);
       mbar_init(&raw_empty[r], 2 * kUmmaGroupWarps);   // the two groups that read its halves
     }
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, 2);
     *failed = 0;
     mbar_init_fence();
   }
@@ -113,8 +113,12 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Two of them: issuing one step's MMAs from a single thread (~55 cycles each, plus the waits and the
+    // commit) is what bounds the step time, so warp 1 takes the even steps into accumulator 0 and warp 3
+    // the odd steps into accumulator 1; the epilogue adds the two (a fixed order: reproducible).  With an
+    // even ring depth each issuer only ever returns to slots it consumed itself.
     // The whole warp runs the loop (warp-uniform control flow keeps the descriptors in uniform
     // registers); one elected lane issues.  The barriers of the NEXT step are looked at before this
     // step's instructions are issued, so that the answer is there when the loop comes round.
@@ -123,14 +127,16 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     const uint64_t desc0 = umma_desc_sw128(tiles_s);
     const uint32_t stage_u = (uint32_t)(stage_bytes >> 4), b_off_u = (uint32_t)((TERMS * kUmmaRows * 128) >> 4);
     bool ok = true;
-    int s = 0;
+    const int odd = warp == 3;
+    const uint32_t acc = tmem_d + (uint32_t)(odd * p.acc_stride);
+    int s = odd;
     uint32_t ph = 0;
-    uint32_t tok_x = mbar_test(&x_full[0], 0), tok_a = mbar_test(&a_full[0], 0);
+    uint32_t tok_x = mbar_test(&x_full[s], 0), tok_a = mbar_test(&a_full[s], 0);
 #ifdef TQ_UMMA_PROFILE
     long long prof_acc[3] = {0, 0, 0};
 #endif
 #pragma unroll 1
-    for (int kb = 0; kb < n_kb; ++kb) {
+    for (int kb = odd; kb < n_kb; kb += 2) {
 #ifdef TQ_UMMA_PROFILE
       const long long t0 = clock64();
       ok = !*failed && mbar_wait_token(&x_full[s], ph, tok_x);
@@ -146,12 +152,11 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       tc_fence_after();
       const uint64_t ad = desc0 + (uint64_t)((uint32_t)s * stage_u);
       const int s_cur = s;
-      if (++s == S) {
-        s = 0;
+      s += 2;
+      if (s >= S) {
+        s -= S;
         ph ^= 1u;
       }
-      tok_x = mbar_test(&x_full[s], ph);
-      tok_a = mbar_test(&a_full[s], ph);
 #ifdef TQ_UMMA_PROFILE
       if (!(p.dbg & 2))
 #endif
@@ -159,12 +164,16 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
 #pragma unroll
         for (int k16 = 0; k16 < kUmmaK / 16; ++k16) {
           const uint64_t bd = ad + b_off_u + 2 * k16;
-          umma_f16(tmem_d, ad + 2 * k16, bd, idesc, (kb | k16) != 0);
-          if (TERMS == 2) umma_f16(tmem_d, ad + (kUmmaRows * 128 >> 4) + 2 * k16, bd, idesc, 1u);
+          umma_f16(acc, ad + 2 * k16, bd, idesc, (kb > 1) | (k16 != 0));
+          if (TERMS == 2) umma_f16(acc, ad + (kUmmaRows * 128 >> 4) + 2 * k16, bd, idesc, 1u);
         }
       }
       if (leader) umma_commit(&empty[s_cur]);   // arrives when the MMAs above have finished reading the stage
       __syncwarp();
+      // Look at the next step's barriers only now: the answer takes ~70 cycles, during which an in-order
+      // thread issues nothing, and here the tensor core already has this step's work.
+      tok_x = mbar_test(&x_full[s], ph);
+      tok_a = mbar_test(&a_full[s], ph);
 #ifdef TQ_UMMA_PROFILE
       prof_acc[2] += clock64() - t2;
 #endif
@@ -172,7 +181,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     if (leader) umma_commit(acc_full);           // arrives when every MMA issued so far has completed
     __syncwarp();
 #ifdef TQ_UMMA_PROFILE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && p.prof && lane == 0)
+    if (blockIdx.x == 0 && blockIdx.y == 0 && p.prof && lane == 0 && !odd)
       for (int i = 0; i < 3; ++i) p.prof[i] = prof_acc[i];
 #endif
   } else {
@@ -183,8 +192,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     // so that G stages are being converted at any time (one stage's chain of waits, loads, arithmetic,
     // stores and fence is long; the groups overlap it).  G is even, so a group always reads the same
     // half (c = g & 1) of its 128-k packed tiles.
-    const int group = (warp - 3) / kUmmaGroupWarps;
-    const int tid = threadIdx.x - 96 - group * 32 * kUmmaGroupWarps;
+    const int group = (warp - kUmmaFirstDqWarp) / kUmmaGroupWarps;
+    const int tid = threadIdx.x - 32 * kUmmaFirstDqWarp - group * 32 * kUmmaGroupWarps;
     constexpr int kCombos = 512 / (32 * kUmmaGroupWarps);
     int src_off[kCombos], sc_off[kCombos], dst_off[kCombos][2];
 #pragma unroll
@@ -240,10 +249,6 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         r -= RS;
         rph ^= 1u;
       }
-      if (kb + kUmmaGroups < n_kb) {                 // early look at what this group's next stage waits for
-        tok_raw = mbar_test(&raw_full[r], rph);
-        tok_empty = mbar_test(&empty[s], ph ^ 1u);
-      }
       uint8_t* a_hi = tiles_s + (size_t)s_cur * stage_bytes;
       uint8_t* a_lo = a_hi + kUmmaRows * 128;
       const uint8_t* raw = raw_s + (size_t)r_cur * 8 * TB;
@@ -289,12 +294,16 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         mbar_arrive(&a_full[s_cur]);
         mbar_arrive(&raw_empty[r_cur]);
       }
+      if (kb + kUmmaGroups < n_kb) {                 // early look at what this group's next stage waits for
+        tok_raw = mbar_test(&raw_full[r], rph);
+        tok_empty = mbar_test(&empty[s], ph ^ 1u);
+      }
 #ifdef TQ_UMMA_PROFILE
       dq_acc[3] += clock64() - t3;
 #endif
     }
 #ifdef TQ_UMMA_PROFILE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && p.prof && threadIdx.x == 96) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && p.prof && threadIdx.x == 32 * kUmmaFirstDqWarp) {
       for (int i = 0; i < 4; ++i) p.prof[4 + i] = dq_acc[i];
       p.prof[8] = clock64() - dq_start;
     }
@@ -307,9 +316,12 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       const int q4 = warp & 3;                                 // tensor-memory lane quarter this warp may read
       const int n = blockIdx.x * kUmmaRows + 32 * q4 + lane;
       // two warps share a lane quarter and alternate over the 16-column chunks
-      for (int c0 = 16 * ((warp - 3) >> 2); c0 < p.ntok; c0 += 16 * (kUmmaDqWarps / 4)) {
-        float v[16];
+      for (int c0 = 16 * ((warp - kUmmaFirstDqWarp) >> 2); c0 < p.ntok; c0 += 16 * (kUmmaDqWarps / 4)) {
+        float v[16], v1[16];
         tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)c0, v);
+        tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)(p.acc_stride + c0), v1);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] += v1[i];
         if (p.splits > 1) {
           // K is split over gridDim.z CTAs: park the f32 partial; the last CTA of the tile adds them up
           float* part = p.partial + (size_t)blockIdx.z * p.m_total * p.n_rows;
@@ -418,13 +430,16 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   }
   const int kc_per_split = (w->n_kc + splits - 1) / splits;
   splits = (w->n_kc + kc_per_split - 1) / kc_per_split;
-  int tmem_cols = 32;
-  while (tmem_cols < ntok) tmem_cols <<= 1;
-  int stages = (int)((budget - 2 * raw_tile) / umma_stage_bytes(terms, ntok));
-  if (stages > kUmmaGroups && (budget - (size_t)stages * umma_stage_bytes(terms, ntok)) / raw_tile < 4) --stages;   // rather four packed tiles
-  if (stages > 6) stages = 6;
+  int acc_stride = 32;
+  while (acc_stride < ntok) acc_stride <<= 1;
+  const int tmem_cols = 2 * acc_stride;
+  // Four A/B stages are what the dequant groups need; everything else goes to the packed-tile ring, because
+  // the bytes in flight from HBM (ring slots not being read) are what hides its latency.
+  int stages = kUmmaGroups;
+  if ((budget - 2 * raw_tile) / umma_stage_bytes(terms, ntok) < (size_t)stages)
+    return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: token tile of %d does not fit", ntok);
   int raw_stages = (int)((budget - (size_t)stages * umma_stage_bytes(terms, ntok)) / raw_tile) & ~1;
-  if (raw_stages > 6) raw_stages = 6;
+  if (raw_stages > kUmmaMaxRawStages) raw_stages = kUmmaMaxRawStages;
   if (raw_stages >= kc_per_split) raw_stages = kc_per_split;   // every slot used once: no reuse, any count will do
   if (stages < kUmmaGroups || raw_stages < 1) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: ring sizes %d/%d", stages, raw_stages);
   CUtensorMap map;
@@ -445,6 +460,7 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.kc_total = w->n_kc;
   p.ntok = ntok;
   p.tmem_cols = tmem_cols;
+  p.acc_stride = acc_stride;
   p.y_bf16 = y_dtype == TQ_BF16;
   p.err = ctx->dev_err;
   p.splits = splits;

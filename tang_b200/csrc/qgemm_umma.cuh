@@ -16,9 +16,10 @@
 //     hi = bf16(q*scale) and lo = bf16(q*scale - hi); hi + lo equals q*scale EXACTLY, so two MMAs
 //     per k-step reproduce exact products with f32 accumulation (TERMS = 2).  TERMS = 1 keeps only
 //     hi (relative weight error 2^-9), for bf16 outputs;
-//   * one elected lane of warp 1 issues tcgen05.mma (kind::f16, bf16 x bf16 -> f32) and commits each
-//     stage back to the producers;
-//   * the dequant warps finally read the accumulator with tcgen05.ld and store y.
+//   * one elected lane of warp 1 (even steps) and of warp 3 (odd steps) issues tcgen05.mma (kind::f16,
+//     bf16 x bf16 -> f32), each into an accumulator of its own, and commits each stage back to the
+//     producers;
+//   * the dequant warps finally read both accumulators with tcgen05.ld, add them and store y.
 // Every mbarrier wait is bounded; on failure the CTA records a code, skips ahead and still frees its
 // tensor memory.
 #pragma once
@@ -35,7 +36,8 @@ constexpr int kUmmaK = 64;            // k per stage (one 128-byte swizzle span 
 constexpr int kUmmaGroups = 4;        // dequant groups, each converting every fourth 64-k stage (even)
 constexpr int kUmmaGroupWarps = 4;    // warps per group
 constexpr int kUmmaDqWarps = kUmmaGroups * kUmmaGroupWarps;   // dequant / epilogue warps
-constexpr int kUmmaThreads = 96 + 32 * kUmmaDqWarps;   // + weight-producer, MMA and activation-producer warps
+constexpr int kUmmaFirstDqWarp = 4;   // warps 0..3: weight producer, MMA issuer (even steps), activation producer, MMA issuer (odd steps)
+constexpr int kUmmaThreads = 32 * (kUmmaFirstDqWarp + kUmmaDqWarps);
 
 struct UmmaParams {
   const uint8_t* tiles;   // fragment tiles [n_row_blocks][kc_total][tile_bytes]
@@ -45,7 +47,8 @@ struct UmmaParams {
   int n_rows;             // output features (multiple of 128)
   int kc_total;           // K / 128
   int ntok;               // tokens per CTA tile = UMMA N (multiple of 16, <= 256)
-  int tmem_cols;          // power of two >= max(32, ntok)
+  int tmem_cols;          // allocation: two accumulators, power of two
+  int acc_stride;         // columns between the accumulators of the even and the odd steps
   int stages;             // A/B ring depth
   int raw_stages;         // packed-tile ring depth (128 k each): what keeps the HBM stream in flight
   int y_bf16;
@@ -63,7 +66,7 @@ struct UmmaParams {
 __host__ __device__ inline size_t umma_stage_bytes(int terms, int ntok) {
   return (size_t)terms * kUmmaRows * 128 + (size_t)ntok * 128;   // A tiles + B tile, all 1024-aligned sizes
 }
-constexpr int kUmmaMaxRawStages = 8;
+constexpr int kUmmaMaxRawStages = 16;
 constexpr int kUmmaHeader = 1024;
 __host__ __device__ inline size_t umma_smem_bytes(int kind, int terms, int ntok, int stages, int raw_stages) {
   return kUmmaHeader + 1024 /*alignment slack*/ + (size_t)stages * umma_stage_bytes(terms, ntok) +
