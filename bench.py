@@ -38,7 +38,7 @@ METRIC, UNIT = "int4_gemv_hbm_tbps", "TB/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # capture summarised in profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 33_105_000   # 33.08 MB read + 28 KB written (profiles/qgemm_mma_q4f16_m1_n14336_k4096.md)
 
 
 def algorithmic_bytes(m: int) -> int:
@@ -308,6 +308,14 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         if comm:
             comm.destroy()
 
+    extras = None
+    if world == 1 and not args.no_extras:
+        if graph is not None:
+            graph.free()
+            graph = None
+        torch.cuda.empty_cache()
+        extras = run_extras(dev, tb, torch, stream, measured_peaks()[0])
+
     if rank == 0:
         bytes_launch = algorithmic_bytes(m)
         ms_per_step = ms / args.steps
@@ -341,6 +349,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "decode": None if decode is None else {
                 "metric": "llama3_8b_shape_decode_tokens_per_s", "peak_gbs": peak,
                 "results": [dict(r, frac_of_hbm_peak=r["gbs_per_gpu"] / peak) for r in decode]},
+            "extras": extras,
         }
         print(json.dumps(out))
     if graph is not None:
@@ -463,6 +472,146 @@ def run_decode(dev, tb, torch, stream, comm, rank, world, args, barrier):
     return out
 
 
+# ----------------------------------------------------------------------------------------------
+# The other BASELINE configurations, timed briefly at N=1 and reported under "extras": the M sweep of
+# configs[1], the DeepSeek-V2-Lite-shaped MoE layer (configs[3]) and the DeepSeek-V3-shaped MLA decode
+# attention (configs[4]).  Seeded synthetic inputs generated on the device.
+# ----------------------------------------------------------------------------------------------
+def _time_ms(torch, stream, dev, fn, reps, warm=2):
+    for _ in range(warm):
+        fn()
+    dev.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+    dev.sync()
+    return e0.elapsed_time(e1) / reps
+
+
+def run_extras(dev, tb, torch, stream, peak_gbs):
+    import ctypes as C
+
+    L_ = dev._L
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    out = {}
+
+    def q4(rows, cols):
+        with torch.cuda.stream(stream):
+            pay = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device="cuda", generator=gen)
+            sc = (torch.rand((rows, cols // 32), device="cuda", generator=gen) * 0.018 + 0.002).half()
+        stream.synchronize()
+        w = dev.qweight_from_device(tb.Q4_F16, pay.data_ptr(), sc.data_ptr(), rows, cols)
+        dev.sync()
+        return w
+
+    def i8(rows, cols):
+        with torch.cuda.stream(stream):
+            pay = torch.randint(-127, 128, (rows, cols), dtype=torch.int8, device="cuda", generator=gen)
+            sc = torch.rand(rows, device="cuda", generator=gen) * 0.009 + 0.001
+        stream.synchronize()
+        w = dev.qweight_from_device(tb.I8_ROW, pay.data_ptr(), sc.data_ptr(), rows, cols)
+        dev.sync()
+        return w
+
+    def bf16(shape, std=1.0):
+        with torch.cuda.stream(stream):
+            t = (torch.randn(shape, device="cuda", generator=gen) * std).bfloat16()
+        stream.synchronize()
+        return t
+
+    # ---- configs[1]: M sweep over 6 distinct matrices (198 MB > L2), bf16 results, one CUDA graph per M
+    n_mat = 6
+    ws = [q4(N_OUT, K_IN) for _ in range(n_mat)]
+    sweep = []
+    for m in (1, 8, 32, 64, 512, 2048):
+        x = bf16((m, K_IN))
+        y = torch.empty((m, N_OUT), dtype=torch.bfloat16, device="cuda")
+
+        def one():
+            for w in ws:
+                dev._check(L_.tq_qlinear(dev._ctx, C.c_void_p(w.handle), C.c_void_p(x.data_ptr()), tb.BF16, 0, m,
+                                         C.c_void_p(y.data_ptr()), tb.BF16, 0, None))
+        one()
+        dev.sync()
+        dev.begin_capture()
+        one()
+        g = dev.end_capture()
+        us = _time_ms(torch, stream, dev, g.launch, 10, 3) * 1e3 / n_mat
+        g.free()
+        byt, fl = algorithmic_bytes(m), 2.0 * m * N_OUT * K_IN
+        sweep.append({"m": m, "us_per_launch": us, "gbs": byt / us / 1e3, "tflops": fl / us / 1e6,
+                      "frac_of_hbm_peak": byt / us / 1e3 / peak_gbs})
+    out["int4_gemm_m_sweep"] = sweep
+    for w in ws:
+        w.free()
+    del ws
+    torch.cuda.empty_cache()
+
+    # ---- configs[3]: MoE layer, d 2048, 64 routed + 2 shared experts of width 1408, top-6
+    d, ffn, E, k, nsh = 2048, 1408, 64, 6, 2
+    wg = bf16((E, d), 0.02)
+    layer = tb.MoeLayer(dev, tb.MoeConfig(d, ffn, E, k, nsh, 0, 0, 1), tb.Buffer(dev, wg.data_ptr(), wg.numel(), tb.BF16, owns=False),
+                        q4(E * 2 * ffn, d), q4(E * d, ffn), [q4(2 * ffn, d) for _ in range(nsh)], [q4(d, ffn) for _ in range(nsh)])
+    per_expert = 3 * (ffn * d // 2 + ffn * d // 32 * 2)
+    moe = []
+    for T in (1, 64, 256, 4096):
+        h = bf16((T, d))
+        hb = tb.Buffer(dev, h.data_ptr(), h.numel(), tb.BF16, owns=False)
+        o, idx, _w = layer.forward(hb, T, want_routing=True)
+        dev.sync()
+        distinct = int(len(set(idx.to_vec().tolist())))
+        ob = dev.alloc(T * d, tb.F32)
+        dev.begin_capture()
+        layer.forward(hb, T, out=ob)
+        g = dev.end_capture()
+        ms = _time_ms(torch, stream, dev, g.launch, 10 if T <= 256 else 3)
+        g.free()
+        byt = (distinct + nsh) * per_expert
+        moe.append({"tokens": T, "us": ms * 1e3, "distinct_routed_experts": distinct, "weight_bytes_touched": byt,
+                    "gbs": byt / ms / 1e6, "tflops": 2.0 * T * (k + nsh) * 3 * ffn * d / ms / 1e9})
+    out["moe_dsv2_lite_layer"] = moe
+    layer.destroy()
+    torch.cuda.empty_cache()
+
+    # ---- configs[4]: MLA decode attention, 128 heads, latent 512 + rope 64, int8 per-row W_UK / W_UV
+    H, NOPE, VD, CL, RP = 128, 128, 128, 512, 64
+    wq, wu = i8(H * CL, NOPE), i8(H * VD, CL)
+    mla = []
+    for ctx, B in ((4096, 1), (16384, 16), (32768, 64)):
+        cache = torch.empty((B, ctx, CL + RP), dtype=torch.bfloat16, device="cuda")
+        with torch.cuda.stream(stream):
+            for b in range(B):
+                cache[b].copy_(torch.randn((ctx, CL + RP), device="cuda", generator=gen))
+        stream.synchronize()
+        qn, qr = bf16((B, H, NOPE)), bf16((B, H, RP))
+        lens = dev.upload(np.full(B, ctx, np.int32), tb.I32)
+        q_full, o_lat, o = dev.alloc(B * H * (CL + RP), tb.BF16), dev.alloc(B * H * CL, tb.BF16), dev.alloc(B * H * VD, tb.F32)
+
+        def fn():   # absorb W_UK into q, attend over the latent cache, un-absorb with W_UV
+            dev._check(L_.tq_mla_absorb_q(dev._ctx, C.c_void_p(wq.handle), C.c_void_p(qn.data_ptr()), C.c_void_p(qr.data_ptr()),
+                                          B, H, NOPE, C.c_void_p(q_full.ptr)))
+            dev._check(L_.tq_mla_decode(dev._ctx, C.c_void_p(q_full.ptr), C.c_void_p(cache.data_ptr()), C.c_void_p(lens.ptr), B, H,
+                                        CL, RP, ctx * (CL + RP), ctx, 1.0 / (NOPE + RP) ** 0.5, C.c_void_p(o_lat.ptr)))
+            dev._check(L_.tq_mla_unabsorb(dev._ctx, C.c_void_p(wu.handle), C.c_void_p(o_lat.ptr), B, H, VD, C.c_void_p(o.ptr), tb.F32))
+        fn()
+        dev.sync()
+        dev.begin_capture()
+        fn()
+        g = dev.end_capture()
+        ms = _time_ms(torch, stream, dev, g.launch, 5)
+        g.free()
+        byt = B * ctx * (CL + RP) * 2
+        mla.append({"ctx": ctx, "batch": B, "us": ms * 1e3, "cache_bytes": byt, "gbs": byt / ms / 1e6,
+                    "tflops": B * ctx * H * 2176.0 / ms / 1e9, "frac_of_hbm_peak": byt / ms / 1e6 / peak_gbs})
+        del cache
+        torch.cuda.empty_cache()
+    out["mla_dsv3_decode"] = mla
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -475,6 +624,7 @@ def main() -> None:
     ap.add_argument("--ref-sample", type=int, default=4, help="matvecs per step of the reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Llama-3-8B-shaped decode step")
+    ap.add_argument("--no-extras", action="store_true", help="skip the M sweep / MoE / MLA timings (N=1 only)")
     ap.add_argument("--decode-batches", default="1,16,64")
     ap.add_argument("--decode-layers", type=int, default=32)
     ap.add_argument("--decode-steps", type=int, default=10)

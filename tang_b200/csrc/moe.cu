@@ -23,44 +23,110 @@ namespace tq {
 
 int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, int mx,
                          const int* counts, const int* offsets, int max_rows, long long x_stride, long long y_stride,
-                         void* y, int y_dtype, size_t ldy);
+                         void* y, int y_dtype, size_t ldy, const int* active = nullptr,
+                         int max_active = 0);
 
 constexpr int kMaxExperts = 256;
 constexpr int kMaxTopK = 16;
 
-// One CTA per token, one thread per expert.  Logits are accumulated in f64 in ascending k, one
-// product at a time — the same sequence of additions as the CPU restatement, and bf16 x bf16
-// products are exact in f64, so the logits (hence the selection) are bit-identical to it.
-__global__ void router_kernel(const __nv_bfloat16* h, const __nv_bfloat16* wg, int T, int d, int E, int top_k,
-                              int renorm, int* idx_out, float* w_out, double* logits_out) {
-  extern __shared__ double sh[];          // [128] h chunk | [E][129] gate chunk
-  double* hs = sh;
-  double* ws = sh + 128;
+// One CTA of eight warps per token; warp w computes the logits of experts w, w + 8, ...
+// The reference order is one f64 addition per k, ascending, of products that are exact in f64 (bf16 x
+// bf16).  A warp-parallel sum gives the SAME BITS whenever no addition can round, whatever the order:
+// every product is a multiple of q = 2^qexp and the sum of |products| stays below 2^52 q, so every
+// partial sum of every subset is exactly representable.  The warp certifies this from the exponents
+// (qexp = min over non-zero products of the operands' unit-in-the-last-place exponents, sum |p| with
+// a factor two of slack); an expert that fails the test is redone by one lane in the reference order.
+__device__ __forceinline__ int bf16_ulp_exp(unsigned short bits) {   // value is a multiple of 2^this
+  const int e = (bits >> 7) & 0xFF;
+  return (e ? e : 1) - 127 - 7;
+}
+
+__global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, const __nv_bfloat16* wg, int T, int d, int E,
+                                                     int top_k, int renorm, int* idx_out, float* w_out, double* logits_out, int* counters) {
+  extern __shared__ __align__(16) unsigned short hs[];   // the token's activations (bf16 bits)
   __shared__ double lg[kMaxExperts];
-  const int t = blockIdx.x, e = threadIdx.x;
-  double acc = 0.0;
-  for (int k0 = 0; k0 < d; k0 += 128) {
-    const int kn = min(128, d - k0);
-    for (int i = threadIdx.x; i < kn; i += blockDim.x) hs[i] = (double)__bfloat162float(h[(size_t)t * d + k0 + i]);
-    for (int i = threadIdx.x; i < E * kn; i += blockDim.x) {
-      const int ee = i / kn, kk = i % kn;
-      ws[ee * 129 + kk] = (double)__bfloat162float(wg[(size_t)ee * d + k0 + kk]);
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned short* hrow = reinterpret_cast<const unsigned short*>(h) + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) hs[i] = hrow[i];
+  __syncthreads();
+  // gridDim.y CTAs share a token's experts (few tokens would otherwise occupy few SMs); the CTA that
+  // finishes last (counter) reads all logits back and makes the selection
+  for (int e = blockIdx.y * 8 + warp; e < E; e += 8 * gridDim.y) {
+    const unsigned short* wrow = reinterpret_cast<const unsigned short*>(wg) + (size_t)e * d;
+    double acc = 0.0;
+    float sabs = 0.f;
+    int qmin = 1 << 20;
+    auto term = [&](unsigned short hb, unsigned short wb) {
+      const float p = __uint_as_float((unsigned)hb << 16) * __uint_as_float((unsigned)wb << 16);   // 16 bits: exact
+      if (p != 0.f) qmin = min(qmin, bf16_ulp_exp(hb) + bf16_ulp_exp(wb));
+      acc += (double)p;
+      sabs += fabsf(p);          // a bound only (rounded f32 sum; the test below leaves a factor of two)
+    };
+    // eight consecutive k per lane and load, four loads in flight (d is a multiple of 8: checked by the host)
+    for (int k0 = 8 * lane; k0 < d; k0 += 4 * 256) {
+      uint4 wv[4], hv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int k = k0 + 256 * u;
+        wv[u] = k < d ? *reinterpret_cast<const uint4*>(wrow + k) : make_uint4(0u, 0u, 0u, 0u);
+        hv[u] = k < d ? *reinterpret_cast<const uint4*>(hs + k) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const unsigned ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w}, hh[4] = {hv[u].x, hv[u].y, hv[u].z, hv[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          term((unsigned short)(hh[j] & 0xFFFFu), (unsigned short)(ww[j] & 0xFFFFu));
+          term((unsigned short)(hh[j] >> 16), (unsigned short)(ww[j] >> 16));
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      sabs += __shfl_xor_sync(0xffffffffu, sabs, o);
+      qmin = min(qmin, __shfl_xor_sync(0xffffffffu, qmin, o));
+    }
+    // NaN or infinity anywhere fails the comparison and takes the reference order as well
+    const bool exact = qmin == (1 << 20) || ((double)sabs < ldexp(1.0, 50 + qmin));
+    if (!exact && lane == 0) {
+      acc = 0.0;
+      for (int k = 0; k < d; ++k)
+        acc += (double)__uint_as_float((unsigned)hs[k] << 16) * (double)__uint_as_float((unsigned)wrow[k] << 16);
+    }
+    if (lane == 0) {
+      lg[e] = acc;
+      if (logits_out) logits_out[(size_t)t * E + e] = acc;
+    }
+  }
+  if (gridDim.y > 1) {
+    __shared__ int last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      last = atomicAdd(&counters[t], 1) == (int)gridDim.y - 1;
+      if (last) counters[t] = 0;
     }
     __syncthreads();
-    if (e < E)
-      for (int kk = 0; kk < kn; ++kk) acc += hs[kk] * ws[e * 129 + kk];
-    __syncthreads();
-  }
-  if (e < E) {
-    lg[e] = acc;
-    if (logits_out) logits_out[(size_t)t * E + e] = acc;
+    if (!last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < E; i += blockDim.x) lg[i] = __ldcg(logits_out + (size_t)t * E + i);
   }
   __syncthreads();
+  // softmax terms in parallel (one f64 exp per thread), their sum in index order by one thread
+  __shared__ double ex[kMaxExperts];
+  __shared__ double mx_s;
   if (threadIdx.x == 0) {
     double mx = lg[0];
     for (int i = 1; i < E; ++i) mx = fmax(mx, lg[i]);
+    mx_s = mx;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < E; i += blockDim.x) ex[i] = exp(lg[i] - mx_s);
+  __syncthreads();
+  if (threadIdx.x == 0) {
     double sum = 0.0;
-    for (int i = 0; i < E; ++i) sum += exp(lg[i] - mx);
+    for (int i = 0; i < E; ++i) sum += ex[i];
     unsigned long long taken[kMaxExperts / 64] = {0, 0, 0, 0};
     double chosen = 0.0;
     double pw[kMaxTopK];
@@ -73,7 +139,7 @@ __global__ void router_kernel(const __nv_bfloat16* h, const __nv_bfloat16* wg, i
       }
       taken[best >> 6] |= 1ull << (best & 63);
       pi[s] = best;
-      pw[s] = exp(lg[best] - mx) / sum;
+      pw[s] = ex[best] / sum;
       chosen += pw[s];
     }
     for (int s = 0; s < top_k; ++s) {
@@ -84,7 +150,8 @@ __global__ void router_kernel(const __nv_bfloat16* h, const __nv_bfloat16* wg, i
 }
 
 // counts[e] = rows routed to expert e (a single CTA; T*top_k entries).
-__global__ void moe_count_kernel(const int* idx, int n, int E, int* counts, int* offsets, int* cursor) {
+__global__ void moe_count_kernel(const int* idx, int n, int E, int* counts, int* offsets, int* cursor, int* active,
+                                 int n_listed) {
   __shared__ int c[kMaxExperts];
   for (int i = threadIdx.x; i < E; i += blockDim.x) c[i] = 0;
   __syncthreads();
@@ -98,6 +165,10 @@ __global__ void moe_count_kernel(const int* idx, int n, int E, int* counts, int*
       cursor[e] = run;
       run += c[e];
     }
+    int j = 0;                                   // ids of the first n_listed groups that received rows, then -1s
+    for (int e = 0; e < n_listed; ++e)
+      if (c[e] > 0) active[j++] = e;
+    for (; j < n_listed; ++j) active[j] = -1;
   }
 }
 
@@ -143,27 +214,34 @@ using namespace tq;
 
 extern "C" {
 
-int tq_moe_router(tq_ctx* ctx, const void* h_bf16_dev, const void* wg_bf16_dev, size_t n_tokens, size_t d_model,
-                  size_t n_experts, size_t top_k, int renormalize, int* idx_out_dev, float* weight_out_dev,
-                  double* logits_out_dev) {
-  if (int st = bind(ctx)) return st;
+// logits_ws: [n_tokens][n_experts] f64 that the kernel may use to share logits between the CTAs of a token
+// (null: one CTA per token).
+static int launch_router(tq_ctx* ctx, const void* h_bf16_dev, const void* wg_bf16_dev, size_t n_tokens, size_t d_model,
+                         size_t n_experts, size_t top_k, int renormalize, int* idx_out_dev, float* weight_out_dev,
+                         double* logits_ws) {
   TQ_REQUIRE(ctx, n_experts > 0 && n_experts <= kMaxExperts && top_k > 0 && top_k <= kMaxTopK && top_k <= n_experts,
              "tq_moe_router: need 1 <= top_k <= n_experts <= %d and top_k <= %d", kMaxExperts, kMaxTopK);
   if (n_tokens == 0) return TQ_OK;
   TQ_REQUIRE(ctx, h_bf16_dev && wg_bf16_dev && idx_out_dev && weight_out_dev, "tq_moe_router: null pointer");
-  const int threads = (int)((n_experts + 31) / 32 * 32);
-  const size_t smem = (128 + n_experts * 129) * sizeof(double);
-  static size_t smem_set = 0;
-  if (smem > 48 * 1024 && smem > smem_set) {
-    TQ_CUDA(ctx, cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    smem_set = smem;
-  }
-  router_kernel<<<(unsigned)n_tokens, threads, smem, ctx->stream>>>(
+  const size_t smem = d_model * sizeof(unsigned short);
+  TQ_REQUIRE(ctx, smem <= 48 * 1024 && d_model % 8 == 0 && ((uintptr_t)h_bf16_dev & 15) == 0 && ((uintptr_t)wg_bf16_dev & 15) == 0,
+             "tq_moe_router: d_model must be a multiple of 8 and at most 24576, arrays 16-byte aligned");
+  unsigned gy = 1;
+  if (logits_ws && n_tokens <= 64 && n_tokens <= (size_t)kTileCounters) gy = (unsigned)((n_experts + 7) / 8);
+  router_kernel<<<dim3((unsigned)n_tokens, gy), 256, smem, ctx->stream>>>(
       static_cast<const __nv_bfloat16*>(h_bf16_dev), static_cast<const __nv_bfloat16*>(wg_bf16_dev), (int)n_tokens,
-      (int)d_model, (int)n_experts, (int)top_k, renormalize, idx_out_dev, weight_out_dev, logits_out_dev);
+      (int)d_model, (int)n_experts, (int)top_k, renormalize, idx_out_dev, weight_out_dev, logits_ws, ctx->dev_err + 1);
   ctx->launches++;
   TQ_CUDA(ctx, cudaGetLastError());
   return TQ_OK;
+}
+
+int tq_moe_router(tq_ctx* ctx, const void* h_bf16_dev, const void* wg_bf16_dev, size_t n_tokens, size_t d_model,
+                  size_t n_experts, size_t top_k, int renormalize, int* idx_out_dev, float* weight_out_dev,
+                  double* logits_out_dev) {
+  if (int st = bind(ctx)) return st;
+  return launch_router(ctx, h_bf16_dev, wg_bf16_dev, n_tokens, d_model, n_experts, top_k, renormalize, idx_out_dev,
+                       weight_out_dev, logits_out_dev);
 }
 
 int tq_moe_create(tq_ctx* ctx, const tq_moe_config* cfg, const void* wg_bf16_dev, const tq_qweight* w_gate_up_stacked,
@@ -215,15 +293,36 @@ __global__ void moe_localize_kernel(const int* idx, int n, int lo, int n_local, 
 __global__ void moe_combine_local_kernel(const float* yo, const int* slot, const int* idx_local, const float* w,
                                          const float* shared, int shared_lo, int shared_hi, int top_k, int d, int n_local,
                                          float* out) {
+  // the token's few (row, weight) pairs first, then wide independent loads over the model dimension
+  __shared__ int rows[kMaxTopK];
+  __shared__ float wts[kMaxTopK];
   const int t = blockIdx.x;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    float acc = 0.f;
+  if (threadIdx.x < top_k) {
+    const size_t i = (size_t)t * top_k + threadIdx.x;
+    const bool local = idx_local[i] < n_local;
+    rows[threadIdx.x] = local ? slot[i] : -1;
+    wts[threadIdx.x] = local ? w[i] : 0.f;
+  }
+  __syncthreads();
+  const bool add_shared = shared && t >= shared_lo && t < shared_hi;
+  for (int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x); c < d; c += 4 * gridDim.y * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < top_k; ++s) {
-      const size_t i = (size_t)t * top_k + s;
-      if (idx_local[i] < n_local) acc += w[i] * yo[(size_t)slot[i] * d + c];
+      if (rows[s] < 0) continue;
+      const float4 v = *reinterpret_cast<const float4*>(yo + (size_t)rows[s] * d + c);
+      acc.x += wts[s] * v.x;
+      acc.y += wts[s] * v.y;
+      acc.z += wts[s] * v.z;
+      acc.w += wts[s] * v.w;
     }
-    if (shared && t >= shared_lo && t < shared_hi) acc += shared[(size_t)(t - shared_lo) * d + c];
-    out[(size_t)t * d + c] = acc;
+    if (add_shared) {
+      const float4 v = *reinterpret_cast<const float4*>(shared + (size_t)(t - shared_lo) * d + c);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * d + c) = acc;
   }
 }
 
@@ -249,7 +348,7 @@ int tq_moe_ffn(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_de
     return o;
   };
   const size_t o_idx = take(n * 4), o_idl = take(n * 4), o_w = take(n * 4), o_slot = take(n * 4), o_cnt = take((nl + 1) * 4),
-               o_off = take((nl + 1) * 4), o_cur = take((nl + 1) * 4), o_xs = take(n * d * 2), o_gu = take(n * 2 * f * 4),
+               o_off = take((nl + 1) * 4), o_cur = take((nl + 1) * 4), o_act_list = take((nl + 1) * 4), o_lg = take(T * c.n_experts * 8), o_xs = take(n * d * 2), o_gu = take(n * 2 * f * 4),
                o_act = take(n * f * 2), o_yo = take(n * d * 4), o_sh = take(Ts * d * 4), o_shgu = take(Ts * 2 * f * 4),
                o_shact = take(Ts * f * 2);
   if (int st = ensure_scratch(ctx, off)) return st;
@@ -259,6 +358,7 @@ int tq_moe_ffn(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_de
   float* w = reinterpret_cast<float*>(s + o_w);
   int* slot = reinterpret_cast<int*>(s + o_slot);
   int *cnt = reinterpret_cast<int*>(s + o_cnt), *offs = reinterpret_cast<int*>(s + o_off), *cur = reinterpret_cast<int*>(s + o_cur);
+  int* active = reinterpret_cast<int*>(s + o_act_list);
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(s + o_xs);
   float* gu = reinterpret_cast<float*>(s + o_gu);
   __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(s + o_act);
@@ -274,25 +374,31 @@ int tq_moe_ffn(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_de
   ctx->launches++;      \
   TQ_CUDA(ctx, cudaGetLastError());
 
-  TQ_STEP(tq_moe_router(ctx, h, m->wg, T, d, c.n_experts, k, c.renormalize, idx, w, nullptr));
+  TQ_STEP(launch_router(ctx, h, m->wg, T, d, c.n_experts, k, c.renormalize, idx, w, reinterpret_cast<double*>(s + o_lg)));
   moe_localize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(idx, (int)n, m->expert_lo, nl, idl);
   TQ_LAUNCHED();
-  moe_count_kernel<<<1, 1024, 0, ctx->stream>>>(idl, (int)n, nl + 1, cnt, offs, cur);
+  moe_count_kernel<<<1, 1024, 0, ctx->stream>>>(idl, (int)n, nl + 1, cnt, offs, cur, active, nl);
   TQ_LAUNCHED();
   moe_slot_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(idl, (int)n, cur, slot);
   TQ_LAUNCHED();
   moe_gather_kernel<<<(unsigned)n, 128, 0, ctx->stream>>>(h, slot, (int)n, (int)k, (int)d, xs);
   TQ_LAUNCHED();
-  const int cap = (int)(T < 64 ? T : 64);   // a token picks an expert at most once: counts[e] <= T
-  TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, cap, cnt, offs, (int)T, 0, 0, gu, TQ_F32, 2 * f));
+  // a token picks an expert at most once (counts[e] <= T); the chunk of rows one CTA takes follows the
+  // expected rows per expert (T k / E), so that small batches do not pay for 64-row tiles
+  size_t want = 2 * n / (size_t)c.n_experts + 1;
+  int cap = 8;
+  while (cap < 64 && (size_t)cap < want) cap <<= 1;
+  if ((size_t)cap > T) cap = (int)T;
+  const int max_active = (int)(n < (size_t)nl ? n : (size_t)nl);   // at most one expert per (token, choice)
+  TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, cap, cnt, offs, (int)T, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
   TQ_STEP(tq_swiglu(ctx, gu, gu + f, TQ_F32, 2 * f, n, f, act, TQ_BF16));
-  TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, cap, cnt, offs, (int)T, 0, 0, yo, TQ_F32, d));
+  TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, cap, cnt, offs, (int)T, 0, 0, yo, TQ_F32, d, active, max_active));
   for (size_t i = 0; i < m->sh_gate_up.size() && Ts > 0; ++i) {
     TQ_STEP(tq_qlinear(ctx, m->sh_gate_up[i], h + sh_lo * d, TQ_BF16, d, Ts, shgu, TQ_F32, 2 * f, nullptr));
     TQ_STEP(tq_swiglu(ctx, shgu, shgu + f, TQ_F32, 2 * f, Ts, f, shact, TQ_BF16));
     TQ_STEP(tq_qlinear(ctx, m->sh_down[i], shact, TQ_BF16, f, Ts, sh, TQ_F32, d, i ? sh : nullptr));
   }
-  moe_combine_local_kernel<<<(unsigned)T, 256, 0, ctx->stream>>>(yo, slot, idl, w, (c.n_shared && Ts) ? sh : nullptr, (int)sh_lo,
+  moe_combine_local_kernel<<<dim3((unsigned)T, (unsigned)((d + 1023) / 1024)), 256, 0, ctx->stream>>>(yo, slot, idl, w, (c.n_shared && Ts) ? sh : nullptr, (int)sh_lo,
                                                                  (int)sh_hi, (int)k, (int)d, nl, out_dev);
   TQ_LAUNCHED();
   if (comm) TQ_STEP(tq_all_reduce_f32(ctx, comm, out_dev, T * d));

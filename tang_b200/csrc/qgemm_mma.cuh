@@ -47,6 +47,7 @@ struct QGemmParams {
   int grouped;
   const int* g_counts;
   const int* g_offsets;
+  const int* g_active;    // optional: blockIdx.y indexes this list of group ids (-1 = unused entry)
   long long g_tile_stride, g_x_stride, g_y_stride;
   int debug;                // tuning aid: 1 = consumers skip the math, 2 = producer re-reads the first K chunk
   int* err;
@@ -106,7 +107,11 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
   size_t y_off = 0;
   if (p.grouped) {
     pdl_wait();   // group tables and row offsets come from earlier kernels of the stream
-    const int e = blockIdx.y;
+    int e = blockIdx.y;
+    if (p.g_active) {
+      e = p.g_active[blockIdx.y];
+      if (e < 0) return;                  // fewer groups have rows than the grid allowed for
+    }
     tiles += (size_t)e * p.g_tile_stride;
     if (row_scales) row_scales += (size_t)e * p.n_rows;
     if (p.g_counts) {

@@ -205,6 +205,8 @@ struct QgGroup {
   const int* offsets = nullptr;   // device: first row of each group in x / y
   long long x_stride = 0, y_stride = 0;  // elements between groups when counts == nullptr
   int max_rows = 0;               // upper bound of counts[e] (sizes gridDim.z)
+  const int* active = nullptr;    // device: ids of the groups that have rows, then -1s
+  int max_active = 0;             // upper bound of how many groups can have rows (sizes gridDim.y)
 };
 
 // One GEMM launch over <= 64 staged activation rows (per group, for grouped launches).
@@ -238,6 +240,7 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   p.grouped = grp ? 1 : 0;
   p.g_counts = grp ? grp->counts : nullptr;
   p.g_offsets = grp ? grp->offsets : nullptr;
+  p.g_active = grp ? grp->active : nullptr;
   p.g_tile_stride = (long long)n_rb * w->n_kc * qk_tile_bytes(w->kind);
   p.g_x_stride = grp ? grp->x_stride : 0;
   p.g_y_stride = grp ? grp->y_stride : 0;
@@ -249,7 +252,8 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   if (smem > 227 * 1024) return fail(ctx, TQ_EUNSUPPORTED, "tq_qlinear: launch needs %zu bytes of shared memory", smem);
   const int chunk = 8 * c.nt;
   const unsigned gz = (grp && grp->counts) ? (unsigned)((grp->max_rows + chunk - 1) / chunk) : 1u;
-  dim3 grid((unsigned)((n_rb + c.wr - 1) / c.wr), (unsigned)n_groups, gz ? gz : 1u);
+  const int gy = (grp && grp->active && grp->max_active < n_groups) ? grp->max_active : n_groups;
+  dim3 grid((unsigned)((n_rb + c.wr - 1) / c.wr), (unsigned)gy, gz ? gz : 1u);
   dim3 block((unsigned)(32 * (c.wr * c.wk + 1)));
   cudaError_t e;
   switch (w->kind) {
@@ -265,7 +269,7 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
 // Grouped launch entry for the other translation units (MoE experts, per-head MLA projections).
 int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, int mx,
                          const int* counts, const int* offsets, int max_rows, long long x_stride, long long y_stride,
-                         void* y, int y_dtype, size_t ldy) {
+                         void* y, int y_dtype, size_t ldy, const int* active, int max_active) {
   TQ_REQUIRE(ctx, w && n_groups > 0 && w->rows % n_groups == 0 && (w->rows / n_groups) % kTileRows == 0,
              "grouped qlinear: rows per group must be a multiple of 16");
   TQ_REQUIRE(ctx, w->cols == (size_t)w->n_kc * kTileK && ldx % 8 == 0 && ((uintptr_t)x_bf16 & 15) == 0 && (x_stride % 8) == 0,
@@ -277,6 +281,8 @@ int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const v
   g.x_stride = x_stride;
   g.y_stride = y_stride;
   g.max_rows = max_rows;
+  g.active = active;
+  g.max_active = max_active;
   return launch_qgemm(ctx, w, static_cast<const __nv_bfloat16*>(x_bf16), ldx, mx, 1, y, y_dtype, ldy, nullptr, &g);
 }
 
