@@ -162,6 +162,17 @@ TQ_API int tq_swiglu(tq_ctx* ctx, const void* gate_dev, const void* up_dev, int 
  * ids are int32 (the reference smuggles u32 bit patterns through an f32 buffer, cpu.rs:51-56). */
 TQ_API int tq_embedding(tq_ctx* ctx, const void* weight_dev, int w_dtype, const int* ids_dev, size_t seq_len, size_t dim,
                         size_t vocab, void* out_dev, int out_dtype);
+/* The greedy branch of Sampler::sample (crates/tang-infer/src/sampling.rs:108-111,183-194): the index of the
+ * FIRST maximum of each row (strict '>' scan; NaN is never chosen).  x is f32 [slices][rows][cols] -- a
+ * vocabulary gathered rank-major from `slices` tensor-parallel ranks, slices = 1 for a plain matrix -- and the
+ * index written is slice * cols + column. */
+TQ_API int tq_argmax_rows(tq_ctx* ctx, const float* x_dev, size_t slices, size_t rows, size_t cols, int* idx_out_dev);
+/* The bookkeeping of `generate` (sampling.rs:229-256) between two decode steps, on the device: stores the chosen
+ * tokens in out_tokens[row][*step], makes them the next step's input, adds one to every position and to *step.
+ * With the decode step and tq_argmax_rows in front of it, one captured graph generates a token per replay and
+ * no logits leave the device.  rows <= 1024. */
+TQ_API int tq_generate_advance(tq_ctx* ctx, const int* chosen_dev, size_t rows, int* tokens_io_dev, int* positions_io_dev,
+                               int* out_tokens_dev, size_t out_ld, int* step_io_dev);
 
 /* ---- attention -------------------------------------------------------------------------------
  * ComputeDevice::kv_attention (device.rs:161-180; cpu.rs:257-315) on f32 buffers, exactly the

@@ -218,6 +218,68 @@ int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const flo
   return TQ_OK;
 }
 
+// Index of the first maximum of each row (strict '>' scan from index 0: NaN is never chosen, an all-NaN or
+// all -inf row gives 0), crates/tang-infer/src/sampling.rs:183-194.  x is [slices][rows][cols]; the index is
+// slice * cols + column.  One CTA per row; each thread scans ascending indices, then (value, index) pairs meet
+// with "larger value, else smaller index".
+__global__ void argmax_rows_kernel(const float* x, int slices, int rows, int cols, int* idx_out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  const int total = slices * cols;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int sl = i / cols, c = i - sl * cols;
+    const float v = x[((size_t)sl * rows + r) * cols + c];
+    if (v > best) {
+      best = v;
+      best_i = i;
+    }
+  }
+  auto meet = [](float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) {
+      v = ov;
+      i = oi;
+    }
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) meet(best, best_i, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, best_i, o));
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = best_i;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    best_i = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) meet(best, best_i, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, best_i, o));
+    if (lane == 0) idx_out[r] = best_i == 0x7fffffff ? 0 : best_i;
+  }
+}
+
+// Between two decode steps of a generation loop: record the chosen tokens, make them the next input, advance the
+// positions.  The step counter lives on the device so that the same captured graph can be replayed.
+__global__ void generate_advance_kernel(const int* chosen, int rows, int* tokens_io, int* positions_io, int* out_tokens,
+                                        int out_ld, int* step_io) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int step = *step_io;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows) {
+    if (step < out_ld) out_tokens[(size_t)i * out_ld + step] = chosen[i];
+    tokens_io[i] = chosen[i];
+    positions_io[i] += 1;
+  }
+  __syncthreads();                       // a single block (rows <= 1024): every thread has read `step`
+  if (threadIdx.x == 0) *step_io = step + 1;
+}
+
 }  // namespace tq
 
 using namespace tq;
@@ -318,6 +380,27 @@ int tq_embedding(tq_ctx* ctx, const void* weight_dev, int w_dtype, const int* id
   TQ_REQUIRE(ctx, weight_dev && ids_dev && out_dev, "tq_embedding: null pointer");
   TQ_CUDA(ctx, launch_k(ctx, embedding_kernel, dim3((unsigned)((seq_len * dim + 255) / 256)), dim3(256), 0, weight_dev, w_dtype,
                         ids_dev, seq_len, dim, vocab, out_dev, out_dtype));
+  return TQ_OK;
+}
+
+int tq_argmax_rows(tq_ctx* ctx, const float* x_dev, size_t slices, size_t rows, size_t cols, int* idx_out_dev) {
+  if (int st = bind(ctx)) return st;
+  if (rows == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, x_dev && idx_out_dev && slices > 0 && cols > 0, "tq_argmax_rows: null pointer or empty row");
+  TQ_REQUIRE(ctx, slices * cols < (1ull << 31), "tq_argmax_rows: row too long");
+  TQ_CUDA(ctx, launch_k(ctx, argmax_rows_kernel, dim3((unsigned)rows), dim3(1024), 0, x_dev, (int)slices, (int)rows, (int)cols,
+                        idx_out_dev));
+  return TQ_OK;
+}
+
+int tq_generate_advance(tq_ctx* ctx, const int* chosen_dev, size_t rows, int* tokens_io_dev, int* positions_io_dev,
+                        int* out_tokens_dev, size_t out_ld, int* step_io_dev) {
+  if (int st = bind(ctx)) return st;
+  if (rows == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, chosen_dev && tokens_io_dev && positions_io_dev && out_tokens_dev && step_io_dev, "tq_generate_advance: null pointer");
+  TQ_REQUIRE(ctx, rows <= 1024, "tq_generate_advance: at most 1024 sequences");
+  TQ_CUDA(ctx, launch_k(ctx, generate_advance_kernel, dim3(1), dim3(1024), 0, chosen_dev, (int)rows, tokens_io_dev,
+                        positions_io_dev, out_tokens_dev, (int)out_ld, step_io_dev));
   return TQ_OK;
 }
 

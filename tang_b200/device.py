@@ -158,6 +158,19 @@ class QuantComputeDevice:
         self._check(self._L.tq_upload(self._ctx, C.c_void_p(buf.ptr), C.c_void_p(a.ctypes.data), a.nbytes))
         return buf
 
+    def upload_into(self, buf: Buffer, data) -> None:
+        """``copy_from_slice`` into an existing buffer of the same element type."""
+        a = _host(data, _NP_OF[buf.dtype]).reshape(-1)
+        if a.size > buf.n:
+            raise TangqError(_lib.TQ_EINVAL, f"upload_into: {a.size} elements into a buffer of {buf.n}")
+        self._check(self._L.tq_upload(self._ctx, C.c_void_p(buf.ptr), C.c_void_p(a.ctypes.data), a.nbytes))
+
+    def argmax_rows(self, x: Buffer, rows: int, cols: int, slices: int = 1) -> Buffer:
+        """Greedy ``Sampler::sample`` (sampling.rs:108-111): first maximum of each f32 row, int32 [rows]."""
+        out = self.alloc(rows, _lib.I32)
+        self._check(self._L.tq_argmax_rows(self._ctx, C.c_void_p(x.ptr), slices, rows, cols, C.c_void_p(out.ptr)))
+        return out
+
     def upload_bf16(self, data_f32) -> Buffer:
         """Uploads f32 data and narrows it to bf16 on the device (round to nearest even)."""
         tmp = self.upload(data_f32, F32)

@@ -92,6 +92,49 @@ class LlamaModel:
         self.dev._check(self.dev._L.tq_llama_decode(C.c_void_p(self.handle), C.c_void_p(token_ids.ptr),
                                                     C.c_void_p(positions.ptr), batch, max_len, C.c_void_p(logits.ptr)))
 
+    def generate_greedy(self, prompts, n_new: int, comm_world: int = 1) -> np.ndarray:
+        """``generate`` with ``SamplingConfig::greedy()`` (crates/tang-infer/src/sampling.rs:229-256) for a batch
+        of equal-length prompts: the prompt is fed token by token through the decode step, then decode ->
+        first-maximum argmax -> advance is captured once as a CUDA graph and replayed `n_new` times; the logits
+        never leave the device.  Returns int32 [batch, n_new] (the caller cuts at its stop token: greedy choices
+        do not depend on what follows them)."""
+        dev, L = self.dev, self.dev._L
+        prompts = np.asarray(prompts, np.int32)
+        B, P = prompts.shape
+        if P < 1 or n_new < 1:
+            raise _lib.TangqError(_lib.TQ_EINVAL, "generate_greedy: need at least one prompt token and one new token")
+        if P + n_new > self.cfg.max_seq:
+            raise _lib.TangqError(_lib.TQ_EINVAL, "generate_greedy: prompt + new tokens exceed max_seq")
+        vocab = self.cfg.vocab
+        logits = dev.alloc(B * vocab, _lib.F32)
+        tok, pos = dev.alloc(B, _lib.I32), dev.alloc(B, _lib.I32)
+        chosen, step = dev.alloc(B, _lib.I32), dev.upload(np.zeros(1, np.int32), _lib.I32)
+        out = dev.upload(np.zeros(B * n_new, np.int32), _lib.I32)
+        for p in range(P - 1):                      # all prompt tokens but the last: fill the cache
+            dev.upload_into(tok, prompts[:, p].copy())
+            dev.upload_into(pos, np.full(B, p, np.int32))
+            self.decode(tok, pos, B, P + n_new, logits)
+        dev.upload_into(tok, prompts[:, P - 1].copy())
+        dev.upload_into(pos, np.full(B, P - 1, np.int32))
+
+        def one():
+            self.decode(tok, pos, B, P + n_new, logits)
+            dev._check(L.tq_argmax_rows(dev._ctx, C.c_void_p(logits.ptr), comm_world, B, vocab // comm_world, C.c_void_p(chosen.ptr)))
+            dev._check(L.tq_generate_advance(dev._ctx, C.c_void_p(chosen.ptr), B, C.c_void_p(tok.ptr), C.c_void_p(pos.ptr),
+                                             C.c_void_p(out.ptr), n_new, C.c_void_p(step.ptr)))
+        one()                                       # eager once (workspaces), then the remaining steps from a graph
+        if n_new > 1:
+            dev.sync()
+            dev.begin_capture()
+            one()
+            graph = dev.end_capture()
+            for _ in range(n_new - 1):
+                graph.launch()
+            dev.sync()
+            graph.free()
+        dev.sync()
+        return out.to_vec().reshape(B, n_new)
+
     def destroy(self) -> None:
         if self.handle:
             self.dev._L.tq_llama_destroy(C.c_void_p(self.handle))
