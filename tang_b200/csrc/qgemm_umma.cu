@@ -29,7 +29,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
   uint8_t* raw_s = tiles_s + (size_t)p.stages * stage_bytes;   // [raw stages][8 tiles]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int S = p.stages, RS = p.raw_stages;
+  const int S = p.stages, RS = p.raw_stages, KT = p.kt;
   const int rb0 = blockIdx.x * (kUmmaRows / kTileRows);        // first 16-row block
   const int m0 = blockIdx.y * p.ntok;                          // first token of this CTA
   const int kc_begin = blockIdx.z * p.kc_per_split;            // this CTA's slice of K, in 128-k tiles
@@ -44,7 +44,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     }
     for (int r = 0; r < RS; ++r) {
       mbar_init(&raw_full[r], 1);
-      mbar_init(&raw_empty[r], 2 * kUmmaGroupWarps);   // the two groups that read its halves
+      mbar_init(&raw_empty[r], kUmmaDqWarps);          // every group reads some tile of every ring slot
     }
     mbar_init(acc_full, 2);
     *failed = 0;
@@ -70,7 +70,10 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       const uint64_t pol_w = l2_policy_evict_first();
       int r = 0;
       uint32_t rph = 0;
-      for (int tile = 0; tile < kc_len && !*failed; ++tile) {
+      // one ring slot = KT consecutive k-tiles of the CTA's eight row blocks: eight copies of KT tiles each (the
+      // copy engine takes about as long over one tile as over four, so small copies cannot keep up with HBM)
+      for (int t0 = 0; t0 < kc_len && !*failed; t0 += KT) {
+        const uint32_t kcs = (uint32_t)min(KT, kc_len - t0);
         if (!mbar_wait_spin(&raw_empty[r], rph ^ 1u)) { give_up(DERR_EMPTY_WAIT); break; }
 #ifdef TQ_UMMA_PROFILE
         if (p.dbg & 4) {
@@ -79,11 +82,10 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
           continue;
         }
 #endif
-        mbar_arrive_expect_tx(&raw_full[r], 8u * TB);
+        mbar_arrive_expect_tx(&raw_full[r], 8u * kcs * TB);
         for (int i = 0; i < 8; ++i)
-          bulk_g2s(raw_s + ((size_t)r * 8 + i) * TB, p.tiles + ((size_t)(rb0 + i) * p.kc_total + kc_begin + tile) * TB, TB,
-                   &raw_full[r],
-                   pol_w);
+          bulk_g2s(raw_s + ((size_t)(r * 8 + i) * KT) * TB, p.tiles + ((size_t)(rb0 + i) * p.kc_total + kc_begin + t0) * TB,
+                   kcs * TB, &raw_full[r], pol_w);
         if (++r == RS) {
           r = 0;
           rph ^= 1u;
@@ -202,22 +204,18 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       const int rbi = combo >> 6, h = (combo >> 5) & 1, L = combo & 31;
       const int g = L >> 2, t = L & 3;
       const int row = rbi * 16 + g + 8 * h;
-      src_off[i] = rbi * TB + h * 512 + 16 * L;
-      sc_off[i] = rbi * TB + 1024 + (KIND == Q4_F16 ? h * 64 + g * 8 : h * 128 + g * 16);
+      src_off[i] = rbi * KT * TB + h * 512 + 16 * L;
+      sc_off[i] = rbi * KT * TB + 1024 + (KIND == Q4_F16 ? h * 64 + g * 8 : h * 128 + g * 16);
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) dst_off[i][jj] = row * 128 + (((4 * jj + t) ^ (row & 7)) << 4);
     }
     bool ok = true;
     const int c = group & 1;                                    // which 64-k half of the 128-k tile
-    int s = group, r = group >> 1;                               // ring slots of this group's first stage and tile
+    int s = group, r = 0, within = group >> 1;                   // A/B slot; packed-tile slot and the tile inside it
     uint32_t ph = 0, rph = 0;
     while (s >= S) {
       s -= S;
       ph ^= 1u;
-    }
-    while (r >= RS) {
-      r -= RS;
-      rph ^= 1u;
     }
     uint32_t tok_raw = mbar_test(&raw_full[r], rph), tok_empty = mbar_test(&empty[s], ph ^ 1u);
 #ifdef TQ_UMMA_PROFILE
@@ -238,20 +236,24 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       ok = !*failed && mbar_wait_token(&raw_full[r], rph, tok_raw) && mbar_wait_token(&empty[s], ph ^ 1u, tok_empty);
 #endif
       if (!ok) { give_up(DERR_FULL_WAIT); break; }
-      const int s_cur = s, r_cur = r;
+      const int s_cur = s, r_cur = r, within_cur = within;
       s += kUmmaGroups;
       while (s >= S) {
         s -= S;
         ph ^= 1u;
       }
-      r += kUmmaGroups / 2;
-      while (r >= RS) {
-        r -= RS;
-        rph ^= 1u;
+      within += kUmmaGroups / 2;                  // this group's next tile: two further on
+      const bool leaves = within >= KT;           // ... which lies in the next ring slot (KT is 2 or 4)
+      if (leaves) {
+        within -= KT;
+        if (++r == RS) {
+          r = 0;
+          rph ^= 1u;
+        }
       }
       uint8_t* a_hi = tiles_s + (size_t)s_cur * stage_bytes;
       uint8_t* a_lo = a_hi + kUmmaRows * 128;
-      const uint8_t* raw = raw_s + (size_t)r_cur * 8 * TB;
+      const uint8_t* raw = raw_s + ((size_t)r_cur * 8 * KT + within_cur) * TB;
 #ifdef TQ_UMMA_PROFILE
       if (!(p.dbg & 1))
 #endif
@@ -292,10 +294,10 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       __syncwarp();
       if (lane == 0) {                                                // one arrival per warp
         mbar_arrive(&a_full[s_cur]);
-        mbar_arrive(&raw_empty[r_cur]);
+        if (leaves) mbar_arrive(&raw_empty[r_cur]);   // done with this ring slot (nobody waits for the final ones)
       }
       if (kb + kUmmaGroups < n_kb) {                 // early look at what this group's next stage waits for
-        tok_raw = mbar_test(&raw_full[r], rph);
+        tok_raw = leaves ? mbar_test(&raw_full[r], rph) : 1u;
         tok_empty = mbar_test(&empty[s], ph ^ 1u);
       }
 #ifdef TQ_UMMA_PROFILE
@@ -409,10 +411,10 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   // Ring sizes.  Two rules come from the dequant groups running ahead of one another (a parity wait
   // is only sound when the waiter is at most one phase ahead of the barrier): at least kUmmaGroups
   // A/B stages, and an even number of packed-tile slots whenever slots are reused.  The token tile is
-  // the widest that leaves room for four stages and two packed tiles, then evened out over the tiles.
+  // the widest that leaves room for four stages and four packed tiles, then evened out over the tiles.
   const size_t kSmemMax = 227 * 1024, raw_tile = 8 * (size_t)qk_tile_bytes(w->kind);
   const size_t budget = kSmemMax - kUmmaHeader - 1024;
-  int ntok_max = (int)(((budget - 2 * raw_tile) / kUmmaGroups - (size_t)terms * kUmmaRows * 128) / 128) / 16 * 16;
+  int ntok_max = (int)(((budget - 4 * raw_tile) / kUmmaGroups - (size_t)terms * kUmmaRows * 128) / 128) / 16 * 16;
   if (ntok_max > 256) ntok_max = 256;
   const size_t n_tok_tiles = (m + ntok_max - 1) / ntok_max;
   const int ntok = (int)(((m + n_tok_tiles - 1) / n_tok_tiles + 15) / 16 * 16);
@@ -434,13 +436,17 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   while (acc_stride < ntok) acc_stride <<= 1;
   const int tmem_cols = 2 * acc_stride;
   // Four A/B stages are what the dequant groups need; everything else goes to the packed-tile ring, because
-  // the bytes in flight from HBM (ring slots not being read) are what hides its latency.
+  // the bytes in flight from HBM (ring slots not being read) are what hides its latency.  A ring slot holds
+  // KT = 4 k-tiles of the eight row blocks (eight 4.6 KB copies) when three such slots fit, else KT = 2.
   int stages = kUmmaGroups;
-  if ((budget - 2 * raw_tile) / umma_stage_bytes(terms, ntok) < (size_t)stages)
+  if ((budget - 4 * raw_tile) / umma_stage_bytes(terms, ntok) < (size_t)stages)
     return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: token tile of %d does not fit", ntok);
-  int raw_stages = (int)((budget - (size_t)stages * umma_stage_bytes(terms, ntok)) / raw_tile) & ~1;
+  const size_t avail = budget - (size_t)stages * umma_stage_bytes(terms, ntok);
+  int kt = avail / (4 * raw_tile) >= 3 ? 4 : 2;
+  int raw_stages = (int)(avail / ((size_t)kt * raw_tile));
   if (raw_stages > kUmmaMaxRawStages) raw_stages = kUmmaMaxRawStages;
-  if (raw_stages >= kc_per_split) raw_stages = kc_per_split;   // every slot used once: no reuse, any count will do
+  const int slots_needed = (kc_per_split + kt - 1) / kt;
+  if (raw_stages > slots_needed) raw_stages = slots_needed;
   if (stages < kUmmaGroups || raw_stages < 1) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: ring sizes %d/%d", stages, raw_stages);
   CUtensorMap map;
   const cuuint64_t gdim[2] = {(cuuint64_t)w->cols, (cuuint64_t)m};
@@ -474,7 +480,8 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   }
   p.stages = stages;
   p.raw_stages = raw_stages;
-  const size_t smem = umma_smem_bytes(w->kind, terms, ntok, stages, raw_stages);
+  p.kt = kt;
+  const size_t smem = umma_smem_bytes(w->kind, terms, ntok, stages, raw_stages * kt);
   if (smem > kSmemMax) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: %zu bytes of shared memory needed", smem);
   dim3 grid((unsigned)(w->rows / kUmmaRows), (unsigned)((m + ntok - 1) / ntok), (unsigned)splits);
   auto go = [&](auto kern) -> cudaError_t {

@@ -50,7 +50,8 @@ struct UmmaParams {
   int tmem_cols;          // allocation: two accumulators, power of two
   int acc_stride;         // columns between the accumulators of the even and the odd steps
   int stages;             // A/B ring depth
-  int raw_stages;         // packed-tile ring depth (128 k each): what keeps the HBM stream in flight
+  int raw_stages;         // packed-tile ring depth (slots of kt tiles of 128 k): what keeps the HBM stream in flight
+  int kt;                 // k-tiles per ring slot (2 or 4)
   int y_bf16;
   int splits;             // CTAs along K per output tile (gridDim.z)
   int kc_per_split;       // 128-k tiles per split
@@ -68,9 +69,9 @@ __host__ __device__ inline size_t umma_stage_bytes(int terms, int ntok) {
 }
 constexpr int kUmmaMaxRawStages = 16;
 constexpr int kUmmaHeader = 1024;
-__host__ __device__ inline size_t umma_smem_bytes(int kind, int terms, int ntok, int stages, int raw_stages) {
+__host__ __device__ inline size_t umma_smem_bytes(int kind, int terms, int ntok, int stages, int raw_tiles) {
   return kUmmaHeader + 1024 /*alignment slack*/ + (size_t)stages * umma_stage_bytes(terms, ntok) +
-         (size_t)raw_stages * 8 * qk_tile_bytes(kind);
+         (size_t)raw_tiles * 8 * qk_tile_bytes(kind);
 }
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
