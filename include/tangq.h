@@ -288,6 +288,14 @@ TQ_API int tq_moe_destroy(tq_moe* moe);
  * [n_tokens, top_k]. */
 TQ_API int tq_moe_ffn(tq_moe* moe, const void* h_bf16_dev, size_t n_tokens, float* out_dev, tq_comm* comm_or_null,
                       int* idx_out_dev, float* weight_out_dev);
+/* The same layer with the tokens SHARDED over the expert-parallel ranks: every rank passes its own n_tokens
+ * (>= 1, the SAME count on every rank: pad the shorter shards) rows and gets their outputs.  Each (token, choice) row travels to the rank that owns the expert
+ * (all-to-all dispatch, padded to the worst case of n_tokens*top_k rows per peer so that the exchange has a
+ * fixed size and can be captured in a graph), the owners run their experts on what arrived, and a second
+ * all-to-all brings the f32 results back to be weighted and summed where the token lives; shared experts run
+ * locally.  The communicator must have the layer's ep_size and ep_rank.  No reference counterpart. */
+TQ_API int tq_moe_ffn_dispatch(tq_moe* moe, const void* h_bf16_dev, size_t n_tokens, float* out_dev, tq_comm* comm_or_null,
+                               int* idx_out_dev_or_null, float* weight_out_dev_or_null);
 
 /* ---- multi-head latent attention, decode ------------------------------------------------------
  * No counterpart in the reference (it has no MLA).  Absorbed form: the bf16 cache row of position j

@@ -80,6 +80,7 @@ PROTOTYPES = {
     "tq_moe_create": (_i, [_p, _p, _p, _p, _p, _p, _p, _pp]),
     "tq_moe_destroy": (_i, [_p]),
     "tq_moe_ffn": (_i, [_p, _p, _sz, _p, _p, _p, _p]),
+    "tq_moe_ffn_dispatch": (_i, [_p, _p, _sz, _p, _p, _p, _p]),
     "tq_mla_decode": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, C.c_float, _p]),
     "tq_mla_absorb_q": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _p]),
     "tq_mla_unabsorb": (_i, [_p, _p, _p, _sz, _sz, _sz, _p, _i]),

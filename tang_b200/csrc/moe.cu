@@ -198,6 +198,56 @@ __global__ void moe_combine_kernel(const float* yo, const int* slot, const float
   }
 }
 
+// ---- expert parallelism with token dispatch (tokens sharded over ranks) ----------------------------
+// Every (token, choice) pair of this rank gets a place in the block of the send buffer that goes to the
+// expert's owner: place = owner * cap + (running count for that owner).  meta[] carries the owner's local
+// expert id, -1 marks padding.  Which pair gets which place within a block is not fixed (atomic counter),
+// but every row is processed on its own and its result comes back to the same place, so outputs do not
+// depend on it.
+__global__ void moe_dispatch_plan_kernel(const int* idx, int n, int n_local, int world, int cap, int* place, int* send_meta) {
+  __shared__ int cnt[64];
+  for (int i = threadIdx.x; i < world; i += blockDim.x) cnt[i] = 0;
+  for (int i = threadIdx.x; i < world * cap; i += blockDim.x) send_meta[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int owner = idx[i] / n_local;
+    const int pos = atomicAdd(&cnt[owner], 1);
+    place[i] = owner * cap + pos;
+    send_meta[owner * cap + pos] = idx[i] - owner * n_local;
+  }
+}
+
+__global__ void moe_dispatch_rows_kernel(const __nv_bfloat16* h, const int* place, int top_k, int d, __nv_bfloat16* send_x) {
+  const int i = blockIdx.x;   // (token, choice)
+  const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(i / top_k) * d);
+  uint4* dst = reinterpret_cast<uint4*>(send_x + (size_t)place[i] * d);
+  for (int v = threadIdx.x; v < d / 8; v += blockDim.x) dst[v] = src[v];
+}
+
+// received meta (-1 = padding) -> bucket ids for the count/slot kernels (padding goes to bucket n_local)
+__global__ void moe_recv_bucket_kernel(const int* meta, int n, int n_local, int* bucket) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) bucket[i] = meta[i] < 0 ? n_local : meta[i];
+}
+
+__global__ void moe_gather_recv_kernel(const __nv_bfloat16* recv_x, const int* bucket, const int* slot, int n_local, int d,
+                                       __nv_bfloat16* xs) {
+  const int i = blockIdx.x;
+  if (bucket[i] >= n_local) return;
+  const uint4* src = reinterpret_cast<const uint4*>(recv_x + (size_t)i * d);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)slot[i] * d);
+  for (int v = threadIdx.x; v < d / 8; v += blockDim.x) dst[v] = src[v];
+}
+
+// expert-order results -> the order the rows arrived in (padding rows are left untouched: nobody reads them)
+__global__ void moe_scatter_back_kernel(const float* yo, const int* bucket, const int* slot, int n_local, int d, float* back) {
+  const int i = blockIdx.x;
+  if (bucket[i] >= n_local) return;
+  const float4* src = reinterpret_cast<const float4*>(yo + (size_t)slot[i] * d);
+  float4* dst = reinterpret_cast<float4*>(back + (size_t)i * d);
+  for (int v = threadIdx.x; v < d / 4; v += blockDim.x) dst[v] = src[v];
+}
+
 }  // namespace tq
 
 struct tq_moe {
@@ -402,6 +452,103 @@ int tq_moe_ffn(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_de
                                                                  (int)sh_hi, (int)k, (int)d, nl, out_dev);
   TQ_LAUNCHED();
   if (comm) TQ_STEP(tq_all_reduce_f32(ctx, comm, out_dev, T * d));
+  if (idx_out_dev) TQ_CUDA(ctx, cudaMemcpyAsync(idx_out_dev, idx, n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+  if (weight_out_dev) TQ_CUDA(ctx, cudaMemcpyAsync(weight_out_dev, w, n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+#undef TQ_STEP
+#undef TQ_LAUNCHED
+  return TQ_OK;
+}
+
+int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_dev, tq_comm* comm, int* idx_out_dev,
+                        float* weight_out_dev) {
+  if (!m) return TQ_EINVAL;
+  tq_ctx* ctx = m->ctx;
+  if (int st = bind(ctx)) return st;
+  const tq_moe_config& c = m->cfg;
+  const int W = comm ? tq_comm_world(comm) : 1;
+  TQ_REQUIRE(ctx, (uint32_t)W == c.ep_size && (!comm || (uint32_t)tq_comm_rank(comm) == c.ep_rank),
+             "tq_moe_ffn_dispatch: the communicator must match the layer's expert-parallel rank and size");
+  TQ_REQUIRE(ctx, W <= 64, "tq_moe_ffn_dispatch: at most 64 ranks");
+  TQ_REQUIRE(ctx, n_tokens > 0 && h_bf16_dev && out_dev, "tq_moe_ffn_dispatch: every rank needs at least one token");
+  TQ_REQUIRE(ctx, ((uintptr_t)h_bf16_dev & 15) == 0, "tq_moe_ffn_dispatch: activations must be 16-byte aligned");
+  const size_t T = n_tokens, k = c.top_k, d = c.d_model, f = c.ffn, n = T * k;
+  const int nl = m->n_local;
+  const size_t cap = n;                      // places per peer: the worst case (every pair to one owner)
+  const size_t R = (size_t)W * cap;          // rows this rank may receive
+  auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off += up(bytes);
+    return o;
+  };
+  const size_t o_idx = take(n * 4), o_w = take(n * 4), o_place = take(n * 4), o_zero = take(n * 4), o_lg = take(T * c.n_experts * 8),
+               o_smeta = take(R * 4), o_rmeta = take(R * 4), o_sx = take(R * d * 2), o_rx = take(R * d * 2), o_bucket = take(R * 4),
+               o_slot = take(R * 4), o_cnt = take((nl + 2) * 4), o_off = take((nl + 2) * 4), o_cur = take((nl + 2) * 4),
+               o_active = take((nl + 2) * 4), o_xs = take(R * d * 2), o_gu = take(R * 2 * f * 4), o_act = take(R * f * 2),
+               o_yo = take(R * d * 4), o_back = take(R * d * 4), o_ret = take(R * d * 4), o_sh = take(T * d * 4),
+               o_shgu = take(T * 2 * f * 4), o_shact = take(T * f * 2);
+  if (int st = ensure_scratch(ctx, off)) return st;
+  uint8_t* s = static_cast<uint8_t*>(ctx->scratch);
+  int *idx = reinterpret_cast<int*>(s + o_idx), *place = reinterpret_cast<int*>(s + o_place), *zero = reinterpret_cast<int*>(s + o_zero);
+  float* w = reinterpret_cast<float*>(s + o_w);
+  int *smeta = reinterpret_cast<int*>(s + o_smeta), *rmeta = reinterpret_cast<int*>(s + o_rmeta);
+  __nv_bfloat16 *sx = reinterpret_cast<__nv_bfloat16*>(s + o_sx), *rx = reinterpret_cast<__nv_bfloat16*>(s + o_rx);
+  int *bucket = reinterpret_cast<int*>(s + o_bucket), *slot = reinterpret_cast<int*>(s + o_slot);
+  int *cnt = reinterpret_cast<int*>(s + o_cnt), *offs = reinterpret_cast<int*>(s + o_off), *cur = reinterpret_cast<int*>(s + o_cur);
+  int* active = reinterpret_cast<int*>(s + o_active);
+  __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16*>(s + o_xs), *act = reinterpret_cast<__nv_bfloat16*>(s + o_act);
+  float *gu = reinterpret_cast<float*>(s + o_gu), *yo = reinterpret_cast<float*>(s + o_yo), *back = reinterpret_cast<float*>(s + o_back),
+        *ret = reinterpret_cast<float*>(s + o_ret), *sh = reinterpret_cast<float*>(s + o_sh), *shgu = reinterpret_cast<float*>(s + o_shgu);
+  __nv_bfloat16* shact = reinterpret_cast<__nv_bfloat16*>(s + o_shact);
+  const __nv_bfloat16* h = static_cast<const __nv_bfloat16*>(h_bf16_dev);
+  int st;
+#define TQ_STEP(expr) \
+  if ((st = (expr)) != TQ_OK) return st;
+#define TQ_LAUNCHED()   \
+  ctx->launches++;      \
+  TQ_CUDA(ctx, cudaGetLastError());
+
+  // route this rank's tokens, plan the places, fill the send buffers
+  TQ_STEP(launch_router(ctx, h, m->wg, T, d, c.n_experts, k, c.renormalize, idx, w, reinterpret_cast<double*>(s + o_lg)));
+  moe_dispatch_plan_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)n, nl, W, (int)cap, place, smeta);
+  TQ_LAUNCHED();
+  moe_dispatch_rows_kernel<<<(unsigned)n, 128, 0, ctx->stream>>>(h, place, (int)k, (int)d, sx);
+  TQ_LAUNCHED();
+  // dispatch: rows and their expert ids to the owners
+  TQ_STEP(tq_all_to_all(ctx, comm, sx, rx, cap * d * 2));
+  TQ_STEP(tq_all_to_all(ctx, comm, smeta, rmeta, cap * 4));
+  // the owner's side: bucket by local expert, run the experts on what arrived
+  moe_recv_bucket_kernel<<<(unsigned)((R + 255) / 256), 256, 0, ctx->stream>>>(rmeta, (int)R, nl, bucket);
+  TQ_LAUNCHED();
+  moe_count_kernel<<<1, 1024, 0, ctx->stream>>>(bucket, (int)R, nl + 1, cnt, offs, cur, active, nl);
+  TQ_LAUNCHED();
+  moe_slot_kernel<<<(unsigned)((R + 255) / 256), 256, 0, ctx->stream>>>(bucket, (int)R, cur, slot);
+  TQ_LAUNCHED();
+  moe_gather_recv_kernel<<<(unsigned)R, 128, 0, ctx->stream>>>(rx, bucket, slot, nl, (int)d, xs);
+  TQ_LAUNCHED();
+  size_t want = 2 * R / (size_t)(nl > 0 ? nl : 1) / (size_t)W + 1;   // expected rows per local expert, with slack
+  int chunk = 8;
+  while (chunk < 64 && (size_t)chunk < want) chunk <<= 1;
+  const int max_rows = (int)((size_t)W * T < R ? (size_t)W * T : R);   // an expert gets a token at most once
+  const int max_active = (int)(R < (size_t)nl ? R : (size_t)nl);
+  TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, chunk, cnt, offs, max_rows, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
+  TQ_STEP(tq_swiglu(ctx, gu, gu + f, TQ_F32, 2 * f, R, f, act, TQ_BF16));
+  TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, chunk, cnt, offs, max_rows, 0, 0, yo, TQ_F32, d, active, max_active));
+  moe_scatter_back_kernel<<<(unsigned)R, 128, 0, ctx->stream>>>(yo, bucket, slot, nl, (int)d, back);
+  TQ_LAUNCHED();
+  // combine: results back to the places they came from
+  TQ_STEP(tq_all_to_all(ctx, comm, back, ret, cap * d * 4));
+  // shared experts run where the token lives
+  for (size_t i = 0; i < m->sh_gate_up.size(); ++i) {
+    TQ_STEP(tq_qlinear(ctx, m->sh_gate_up[i], h, TQ_BF16, d, T, shgu, TQ_F32, 2 * f, nullptr));
+    TQ_STEP(tq_swiglu(ctx, shgu, shgu + f, TQ_F32, 2 * f, T, f, shact, TQ_BF16));
+    TQ_STEP(tq_qlinear(ctx, m->sh_down[i], shact, TQ_BF16, f, T, sh, TQ_F32, d, i ? sh : nullptr));
+  }
+  TQ_CUDA(ctx, cudaMemsetAsync(zero, 0, n * 4, ctx->stream));
+  moe_combine_local_kernel<<<dim3((unsigned)T, (unsigned)((d + 1023) / 1024)), 256, 0, ctx->stream>>>(
+      ret, place, zero, w, c.n_shared ? sh : nullptr, 0, (int)T, (int)k, (int)d, 1, out_dev);
+  TQ_LAUNCHED();
   if (idx_out_dev) TQ_CUDA(ctx, cudaMemcpyAsync(idx_out_dev, idx, n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
   if (weight_out_dev) TQ_CUDA(ctx, cudaMemcpyAsync(weight_out_dev, w, n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
 #undef TQ_STEP

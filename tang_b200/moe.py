@@ -53,6 +53,18 @@ class MoeLayer:
                                                C.c_void_p(w.ptr if w else 0)))
         return (out, idx, w) if want_routing else out
 
+    def forward_dispatch(self, h_local: Buffer, n_tokens: int, comm=None, out: Buffer | None = None, want_routing: bool = False):
+        """Tokens sharded over the expert-parallel ranks: h_local holds THIS rank's bf16 [n_tokens, d_model] rows;
+        all-to-all dispatch to the experts' owners, all-to-all combine back (``tq_moe_ffn_dispatch``)."""
+        k = self.cfg.top_k
+        out = out or self.dev.alloc(n_tokens * self.cfg.d_model, _lib.F32)
+        idx = self.dev.alloc(n_tokens * k, _lib.I32) if want_routing else None
+        w = self.dev.alloc(n_tokens * k, _lib.F32) if want_routing else None
+        self.dev._check(self.dev._L.tq_moe_ffn_dispatch(C.c_void_p(self.handle), C.c_void_p(h_local.ptr), n_tokens,
+                                                        C.c_void_p(out.ptr), C.c_void_p(comm.handle if comm else 0),
+                                                        C.c_void_p(idx.ptr if idx else 0), C.c_void_p(w.ptr if w else 0)))
+        return (out, idx, w) if want_routing else out
+
     def destroy(self) -> None:
         if self.handle:
             self.dev._L.tq_moe_destroy(C.c_void_p(self.handle))

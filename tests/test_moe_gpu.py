@@ -72,3 +72,21 @@ def test_deepseek_v2_lite_shape(dev, orc, T):
     """d_model 2048, 64 routed + 2 shared experts of width 1408, top-6 (BASELINE configs[3])."""
     host = HostMoe(np.random.default_rng(7), d=2048, ffn=1408, n_experts=64, top_k=6, n_shared=2)
     check(dev, orc, host, T, seed=100 + T)
+
+
+@pytest.mark.parametrize("T", [1, 7, 40])
+def test_dispatch_variant_on_one_rank_equals_the_oracle(dev, orc, T):
+    """tq_moe_ffn_dispatch with a single rank: both exchanges are local copies, everything else is the same code
+    the multi-rank path runs (places, buckets, scatter back, combine)."""
+    import tang_b200 as tb
+
+    host = HostMoe(np.random.default_rng(15), d=256, ffn=256, n_experts=8, top_k=2, n_shared=1)
+    rng = np.random.default_rng(T)
+    hb, hf = bf16_round(rng.standard_normal((T, host.d)).astype(np.float32))
+    want, idx_o, _, _ = host.oracle(orc, hf)
+    layer = host.to_device(dev)
+    out, idx, _w = layer.forward_dispatch(dev.upload(hb, tb.BF16), T, want_routing=True)
+    dev.sync()
+    assert np.array_equal(idx.to_vec().reshape(T, host.k), idx_o)
+    assert rel_err(out.to_vec().reshape(T, host.d), want, floor_frac=1.0) < (1e-3 if T < 24 else 5e-3)
+    layer.destroy()

@@ -12,9 +12,9 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(mode, n, port):
+def _run(mode, n, port, worker="tp_worker.py"):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(HERE, "tp_worker.py"), mode]
+           "--master-port", str(port), os.path.join(HERE, worker), mode]
     env = dict(os.environ)
     env.setdefault("OMP_NUM_THREADS", "2")
     if mode == "gpu":
@@ -35,4 +35,22 @@ def test_tp2_decode_on_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     r = _run("gpu", 2, 29632)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_ep2_token_dispatch_protocol_with_gloo_on_cpu():
+    """Expert parallelism with sharded tokens: route, dispatch to the experts' owners, combine back; numpy + the
+    oracle's expert arithmetic over two gloo ranks must reproduce the unsharded oracle exactly."""
+    r = _run("cpu", 2, 29633, "ep_worker.py")
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "err" in r.stdout
+
+
+@pytest.mark.gpu
+def test_ep2_token_dispatch_on_two_gpus():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = _run("gpu", 2, 29634, "ep_worker.py")
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
