@@ -98,6 +98,13 @@ TQ_API int tq_qweight_from_arrays(tq_ctx* ctx, int kind, const void* payload_hos
  * fragment tiles, see csrc/qlayout.cuh); integer codes and scale bits are copied unchanged. */
 TQ_API int tq_qweight_from_device_arrays(tq_ctx* ctx, int kind, const void* payload_dev, const void* scales_dev,
                                          size_t rows, size_t cols, tq_qweight** out);
+/* quantize_matrix_q4 / quantize_matrix_q8 (crates/tang-infer/src/quantize.rs:193-220, with quantize_q4/q8 :47-118)
+ * on the device: `src` is the [rows, cols] matrix as it comes out of a checkpoint (f32, bf16 or f16, widened to
+ * f32 exactly, crates/tang-safetensors/src/lib.rs:262-297; ld = row stride in elements, 0 = dense), `kind` is
+ * TQ_Q4_F32 or TQ_Q8_F32.  Scales and integer codes are the reference's bit for bit (scale = amax/7 or amax/127,
+ * 1.0 for a zero block, round half away from zero, clamp, ragged tail padded with zeros). */
+TQ_API int tq_quantize_matrix(tq_ctx* ctx, const void* src_dev, int src_dtype, size_t ld, size_t rows, size_t cols, int kind,
+                              tq_qweight** out);
 TQ_API int tq_qweight_free(tq_ctx* ctx, tq_qweight* w);
 TQ_API int tq_qweight_shape(const tq_qweight* w, size_t* rows, size_t* cols, int* kind);
 TQ_API size_t tq_qweight_bytes(const tq_qweight* w); /* payload + scale bytes one matvec has to stream */
@@ -167,6 +174,24 @@ TQ_API int tq_embedding(tq_ctx* ctx, const void* weight_dev, int w_dtype, const 
  * vocabulary gathered rank-major from `slices` tensor-parallel ranks, slices = 1 for a plain matrix -- and the
  * index written is slice * cols + column. */
 TQ_API int tq_argmax_rows(tq_ctx* ctx, const float* x_dev, size_t slices, size_t rows, size_t cols, int* idx_out_dev);
+/* Sampler::sample (crates/tang-infer/src/sampling.rs:86-158) for `rows` sequences at once, on the device:
+ * repetition penalty (once per occurrence in the sequence's past tokens: positive logits divided, the others
+ * multiplied), temperature (0 = greedy: first maximum), exp(l - max), top-k (entries equal to the k-th largest
+ * survive; 0 = off), normalisation, top-p (descending probability, equal probabilities in index order, cut after
+ * the first rank whose running sum reaches p; 1 = off), re-normalisation, and one step of the reference's LCG
+ * (sampling.rs:72-79) per sequence for the categorical draw.  logits f32 [slices][rows][cols] as for
+ * tq_argmax_rows.  rng_states [rows] are read and advanced (unused when temperature = 0).  past_tokens
+ * [rows][past_ld] / past_lens [rows] may be null (no penalty).  While at most 1024 probabilities survive the
+ * top-k filter, every sum whose order matters is formed in the reference's order. */
+typedef struct tq_sampler_config {
+  double temperature;
+  uint64_t top_k;
+  double top_p;
+  double repetition_penalty;
+} tq_sampler_config;
+TQ_API int tq_sample(tq_ctx* ctx, const float* logits_dev, size_t slices, size_t rows, size_t cols, const tq_sampler_config* cfg,
+                     unsigned long long* rng_states_dev, const int* past_tokens_dev_or_null, const int* past_lens_dev_or_null,
+                     size_t past_ld, int* tokens_out_dev);
 /* The bookkeeping of `generate` (sampling.rs:229-256) between two decode steps, on the device: stores the chosen
  * tokens in out_tokens[row][*step], makes them the next step's input, adds one to every position and to *step.
  * With the decode step and tq_argmax_rows in front of it, one captured graph generates a token per replay and

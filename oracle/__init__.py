@@ -331,6 +331,29 @@ def topk_indices_f64(v, k):
     return out
 
 
+class SamplerConfig(C.Structure):
+    """``SamplingConfig`` (crates/tang-infer/src/sampling.rs:6-20) without the loop controls."""
+    _fields_ = [("temperature", C.c_double), ("top_k", C.c_uint64), ("top_p", C.c_double), ("repetition_penalty", C.c_double)]
+
+
+def lcg_next_f64(state: int):
+    """One step of the sampler's LCG: returns (fraction in [0, 1), new state)."""
+    st = C.c_uint64(state)
+    lib().orc_lcg_next_f64.restype = C.c_double
+    r = lib().orc_lcg_next_f64(C.byref(st))
+    return float(r), int(st.value)
+
+
+def sampler_sample(logits, cfg: "SamplerConfig", rng_state: int, past=()):
+    """``Sampler::sample`` (sampling.rs:86-158): returns (token, new rng state)."""
+    logits = _c(logits, np.float64)
+    past = _c(np.asarray(past, np.int64), np.int64)
+    st = C.c_uint64(rng_state)
+    lib().orc_sampler_sample.restype = C.c_int64
+    tok = lib().orc_sampler_sample(_ptr(logits), _sz(logits.size), _ptr(past), _sz(past.size), C.byref(cfg), C.byref(st))
+    return int(tok), int(st.value)
+
+
 # ----------------------------------------------------------------------------- layer compositions
 
 class QWeight(C.Structure):

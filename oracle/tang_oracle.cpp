@@ -602,4 +602,86 @@ ORC_API void orc_topk_indices_f64(const double* v, size_t n, size_t k, int32_t* 
   for (size_t i = 0; i < k && i < n; ++i) idx_out[i] = idx[i];
 }
 
+// sampling.rs:72-79  rand_f64: 64-bit LCG (Knuth's MMIX constants), top 53 bits as a fraction in [0, 1).
+ORC_API double orc_lcg_next_f64(uint64_t* state) {
+  *state = *state * 6364136223846793005ULL + 1442695040888963407ULL;
+  return (double)(*state >> 11) / (double)(1ULL << 53);
+}
+
+// sampling.rs:196-218  top_p_filter: indices sorted by probability, descending (Rust's sort_by is stable, so
+// equal probabilities keep ascending index order); the cumulative sum runs in that order and everything after
+// the first rank at which it reaches p is zeroed.
+static void top_p_filter(std::vector<double>& probs, double p) {
+  std::vector<size_t> idx(probs.size());
+  for (size_t i = 0; i < idx.size(); ++i) idx[i] = i;
+  std::stable_sort(idx.begin(), idx.end(), [&](size_t a, size_t b) { return probs[a] > probs[b]; });
+  double cumsum = 0.0;
+  size_t cutoff = probs.size();
+  for (size_t rank = 0; rank < idx.size(); ++rank) {
+    cumsum += probs[idx[rank]];
+    if (cumsum >= p) {
+      cutoff = rank + 1;
+      break;
+    }
+  }
+  for (size_t rank = cutoff; rank < idx.size(); ++rank) probs[idx[rank]] = 0.0;
+}
+
+// sampling.rs:86-158  Sampler::sample, step for step: f64 copy of the logits; repetition penalty once per
+// occurrence in past_tokens (divide positive logits, multiply the others); temperature 0 -> argmax; scale by
+// 1/temperature; exp(l - max); top-k threshold (ties at the threshold survive); normalise (sum <= 0 -> argmax);
+// top-p filter and re-normalise; categorical draw with one LCG step (sampling.rs:161-174: first index whose
+// running sum exceeds r, else the last index).
+struct OrcSamplerConfig {
+  double temperature;
+  uint64_t top_k;
+  double top_p;
+  double repetition_penalty;
+};
+
+ORC_API int64_t orc_sampler_sample(const double* logits, size_t n, const int64_t* past, size_t n_past,
+                                   const OrcSamplerConfig* cfg, uint64_t* rng_state) {
+  std::vector<double> probs(logits, logits + n);
+  if (cfg->repetition_penalty != 1.0) {
+    for (size_t j = 0; j < n_past; ++j) {
+      if (past[j] >= 0 && (size_t)past[j] < n) {
+        double& v = probs[(size_t)past[j]];
+        if (v > 0.0) v /= cfg->repetition_penalty;
+        else v *= cfg->repetition_penalty;
+      }
+    }
+  }
+  if (cfg->temperature == 0.0) return (int64_t)orc_argmax_f64(probs.data(), n);
+  if (cfg->temperature != 1.0) {
+    const double inv_t = 1.0 / cfg->temperature;
+    for (double& v : probs) v *= inv_t;
+  }
+  double mx = -std::numeric_limits<double>::infinity();
+  for (double v : probs) mx = std::fmax(mx, v);
+  for (double& v : probs) v = std::exp(v - mx);
+  if (cfg->top_k > 0 && cfg->top_k < n) {
+    const double thr = orc_kth_largest_f64(probs.data(), n, (size_t)cfg->top_k);
+    for (double& v : probs)
+      if (v < thr) v = 0.0;
+  }
+  double sum = 0.0;
+  for (double v : probs) sum += v;
+  if (sum <= 0.0) return (int64_t)orc_argmax_f64(probs.data(), n);
+  for (double& v : probs) v /= sum;
+  if (cfg->top_p < 1.0) {
+    top_p_filter(probs, cfg->top_p);
+    double s2 = 0.0;
+    for (double v : probs) s2 += v;
+    if (s2 > 0.0)
+      for (double& v : probs) v /= s2;
+  }
+  const double r = orc_lcg_next_f64(rng_state);
+  double cumsum = 0.0;
+  for (size_t i = 0; i < n; ++i) {
+    cumsum += probs[i];
+    if (r < cumsum) return (int64_t)i;
+  }
+  return (int64_t)n - 1;
+}
+
 ORC_API int orc_max_threads(void) { return clamp_threads(0); }

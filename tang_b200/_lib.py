@@ -41,6 +41,7 @@ PROTOTYPES = {
     "tq_convert": (_i, [_p, _p, _i, _p, _i, _sz]),
     "tq_qweight_from_blocks": (_i, [_p, _i, _p, _sz, _sz, _pp]),
     "tq_qweight_from_arrays": (_i, [_p, _i, _p, _p, _sz, _sz, _pp]),
+    "tq_quantize_matrix": (_i, [_p, _p, _i, _sz, _sz, _sz, _i, _pp]),
     "tq_qweight_from_device_arrays": (_i, [_p, _i, _p, _p, _sz, _sz, _pp]),
     "tq_qweight_free": (_i, [_p, _p]),
     "tq_qweight_shape": (_i, [_p, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_i)]),
@@ -56,6 +57,7 @@ PROTOTYPES = {
     "tq_swiglu": (_i, [_p, _p, _p, _i, _sz, _sz, _sz, _p, _i]),
     "tq_embedding": (_i, [_p, _p, _i, _p, _sz, _sz, _sz, _p, _i]),
     "tq_argmax_rows": (_i, [_p, _p, _sz, _sz, _sz, _p]),
+    "tq_sample": (_i, [_p, _p, _sz, _sz, _sz, _p, _p, _p, _p, _sz, _p]),
     "tq_generate_advance": (_i, [_p, _p, _sz, _p, _p, _p, _sz, _p]),
     "tq_kv_attention": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p]),
     "tq_gqa_decode": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),

@@ -41,7 +41,6 @@ struct tq_qweight {
   uint8_t* tiles = nullptr;    // fragment tiles (csrc/qlayout.cuh), owned
   size_t tile_bytes = 0;
   float* row_scales = nullptr; // TQ_I8_ROW only, owned
-  bool f16_ok = false;         // Q4 kinds: every scale, times 8, is a normal f16 number (or zero)
 };
 
 namespace tq {

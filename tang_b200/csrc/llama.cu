@@ -79,7 +79,6 @@ int tq_qweight_concat_rows(tq_ctx* ctx, const tq_qweight* const* parts, size_t n
   TQ_REQUIRE(ctx, parts && n_parts > 0 && out, "tq_qweight_concat_rows: null argument");
   *out = nullptr;
   size_t rows = 0;
-  bool f16_ok = true;
   for (size_t i = 0; i < n_parts; ++i) {
     TQ_REQUIRE(ctx, parts[i] != nullptr, "tq_qweight_concat_rows: null part");
     TQ_REQUIRE(ctx, parts[i]->kind == parts[0]->kind && parts[i]->cols == parts[0]->cols,
@@ -87,13 +86,11 @@ int tq_qweight_concat_rows(tq_ctx* ctx, const tq_qweight* const* parts, size_t n
     TQ_REQUIRE(ctx, i + 1 == n_parts || parts[i]->rows % kTileRows == 0,
                "tq_qweight_concat_rows: every part but the last needs a row count that is a multiple of 16");
     rows += parts[i]->rows;
-    f16_ok = f16_ok && parts[i]->f16_ok;
   }
   tq_qweight* w = new (std::nothrow) tq_qweight();
   if (!w) return fail(ctx, TQ_ENOMEM, "out of host memory");
   *w = *parts[0];
   w->rows = rows;
-  w->f16_ok = f16_ok;
   w->n_rb = (int)((rows + kTileRows - 1) / kTileRows);
   w->tile_bytes = (size_t)w->n_rb * w->n_kc * qk_tile_bytes(w->kind);
   w->tiles = nullptr;

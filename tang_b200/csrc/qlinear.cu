@@ -21,7 +21,7 @@ static inline size_t scale_elem(int kind) { return kind == TQ_Q4_F16 ? 2 : 4; }
 // for t == 0, the block's scale.  Integer codes and scale bits are copied, never recomputed.
 // ---------------------------------------------------------------------------------------------
 __global__ void repack_kernel(const uint8_t* pay, const uint8_t* sc, size_t ld_pay, size_t ld_sc, int kind, size_t rows,
-                              size_t cols, int n_rb, int n_kc, uint8_t* tiles, int* bad_scale) {
+                              size_t cols, int n_rb, int n_kc, uint8_t* tiles) {
   const size_t total = (size_t)n_rb * n_kc * 2 * 32 * 4;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -72,15 +72,10 @@ __global__ void repack_kernel(const uint8_t* pay, const uint8_t* sc, size_t ld_p
       uint16_t v = 0;
       if (live) v = *reinterpret_cast<const uint16_t*>(sc + row * ld_sc + 2 * (k0 / 32));
       *reinterpret_cast<uint16_t*>(tile + off) = v;
-      if ((v & 0x7FFFu) > 0x6FFFu) *bad_scale = 1;            // 8 * |scale| would leave the f16 range
     } else {
       uint32_t v = 0;
       if (live) v = *reinterpret_cast<const uint32_t*>(sc + row * ld_sc + 4 * (k0 / 32));
       *reinterpret_cast<uint32_t*>(tile + off) = v;
-      if (kind == Q4_F32) {
-        const float a = fabsf(__uint_as_float(v));
-        if (!(a <= 8188.0f) || (a != 0.0f && a < 6.103515625e-05f)) *bad_scale = 1;   // overflow, NaN or f16-subnormal
-      }
     }
   }
 }
@@ -332,6 +327,46 @@ static int make_weight(tq_ctx* ctx, int kind, size_t rows, size_t cols, tq_qweig
   return TQ_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// quantize_q4 / quantize_q8 of tang-infer (crates/tang-infer/src/quantize.rs:47-71, 84-118) on the device,
+// row by row as quantize_matrix_q4/q8 do (:193-220).  One warp per (row, 32-block), one lane per value:
+// amax = max |v| (NaN ignored, as f32::max does), scale = amax / 7 (or / 127), 1.0 for an all-zero block,
+// q = round(v * (1 / scale)) with ties away from zero, clamped; a ragged tail is padded with q = 0.
+// Every operation is a correctly rounded f32 operation with no fusing, so codes and scales are the reference's
+// bit for bit.  Writes the plain structure-of-arrays form the repack reads.
+// ---------------------------------------------------------------------------------------------
+__global__ void quantize_rows_kernel(const void* src, int src_dtype, size_t ld, size_t rows, size_t cols, int is4,
+                                     uint8_t* pay, float* scales) {
+  const size_t bpr = (cols + 31) / 32;
+  const size_t blk = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (blk >= rows * bpr) return;
+  const int lane = threadIdx.x & 31;
+  const size_t row = blk / bpr, b = blk - row * bpr, k = b * 32 + lane;
+  float v = 0.f;
+  const bool live = k < cols;
+  if (live) {
+    if (src_dtype == TQ_F32) v = static_cast<const float*>(src)[row * ld + k];
+    else if (src_dtype == TQ_BF16) v = __bfloat162float(static_cast<const __nv_bfloat16*>(src)[row * ld + k]);
+    else v = __half2float(static_cast<const __half*>(src)[row * ld + k]);
+  }
+  float amax = live ? fabsf(v) : 0.f;
+  if (!(amax == amax)) amax = 0.f;                       // f32::max(acc, NaN) keeps acc
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float scale = amax == 0.f ? 1.0f : __fdiv_rn(amax, is4 ? 7.0f : 127.0f);
+  const float inv = __fdiv_rn(1.0f, scale);
+  float q = roundf(__fmul_rn(v, inv));                   // ties away from zero, like f32::round
+  q = fminf(fmaxf(q, is4 ? -8.0f : -128.0f), is4 ? 7.0f : 127.0f);
+  int qi = live ? (int)q : 0;                            // a NaN product casts to 0 in Rust as well
+  if (!(q == q)) qi = 0;
+  if (is4) {
+    const int hi = __shfl_down_sync(0xffffffffu, qi, 1);
+    if ((lane & 1) == 0) pay[blk * 16 + (lane >> 1)] = (uint8_t)((qi + 8) | ((hi + 8) << 4));
+  } else {
+    pay[blk * 32 + lane] = (uint8_t)(int8_t)qi;
+  }
+  if (lane == 0) scales[blk] = scale;
+}
+
 // Input strides of the plain arrays for a given kind.
 static void plain_strides(int kind, size_t cols, size_t* ld_pay, size_t* ld_sc) {
   const size_t bpr = (cols + 31) / 32;
@@ -344,21 +379,10 @@ static int repack_from_device(tq_ctx* ctx, tq_qweight* w, const uint8_t* pay, co
   size_t ld_pay, ld_sc;
   plain_strides(w->kind, w->cols, &ld_pay, &ld_sc);
   const size_t n = (size_t)w->n_rb * w->n_kc * 256;
-  int* bad_scale = nullptr;   // raised by the repack when a Q4 scale does not survive as an f16 operand
-  TQ_CUDA(ctx, cudaMalloc(&bad_scale, sizeof(int)));
-  cudaError_t e = cudaMemsetAsync(bad_scale, 0, sizeof(int), ctx->stream);
-  if (e == cudaSuccess) {
-    repack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(pay, sc, ld_pay, ld_sc, w->kind, w->rows, w->cols,
-                                                                       w->n_rb, w->n_kc, w->tiles, bad_scale);
-    ctx->launches++;
-    e = cudaGetLastError();
-  }
-  int bad = 1;
-  if (e == cudaSuccess) e = cudaMemcpyAsync(&bad, bad_scale, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-  cudaFree(bad_scale);
-  TQ_CUDA(ctx, e);
-  w->f16_ok = (w->kind == TQ_Q4_F16 || w->kind == TQ_Q4_F32) && bad == 0;
+  repack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(pay, sc, ld_pay, ld_sc, w->kind, w->rows, w->cols,
+                                                                     w->n_rb, w->n_kc, w->tiles);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
   if (w->kind == TQ_I8_ROW)
     TQ_CUDA(ctx, cudaMemcpyAsync(w->row_scales, sc, w->rows * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
   return TQ_OK;
@@ -378,6 +402,46 @@ int tq_qweight_from_device_arrays(tq_ctx* ctx, int kind, const void* payload_dev
   if (int st = make_weight(ctx, kind, rows, cols, &w)) return st;
   if (int st = repack_from_device(ctx, w, static_cast<const uint8_t*>(payload_dev), static_cast<const uint8_t*>(scales_dev))) {
     tq_qweight_free(ctx, w);
+    return st;
+  }
+  *out = w;
+  return TQ_OK;
+}
+
+int tq_quantize_matrix(tq_ctx* ctx, const void* src_dev, int src_dtype, size_t ld, size_t rows, size_t cols, int kind,
+                       tq_qweight** out) {
+  if (int st = bind(ctx)) return st;
+  TQ_REQUIRE(ctx, out != nullptr, "null output handle");
+  *out = nullptr;
+  TQ_REQUIRE(ctx, kind == TQ_Q4_F32 || kind == TQ_Q8_F32, "tq_quantize_matrix: kind must be TQ_Q4_F32 or TQ_Q8_F32 (the reference's block formats)");
+  TQ_REQUIRE(ctx, src_dtype == TQ_F32 || src_dtype == TQ_BF16 || src_dtype == TQ_F16, "tq_quantize_matrix: source must be f32, bf16 or f16");
+  TQ_REQUIRE(ctx, src_dev && rows > 0 && cols > 0, "tq_quantize_matrix: null source or empty matrix");
+  if (ld == 0) ld = cols;
+  TQ_REQUIRE(ctx, ld >= cols, "tq_quantize_matrix: row stride smaller than the row");
+  size_t ld_pay, ld_sc;
+  plain_strides(kind, cols, &ld_pay, &ld_sc);
+  uint8_t* pay = nullptr;
+  float* sc = nullptr;
+  cudaError_t e = cudaMalloc(&pay, rows * ld_pay + 16);
+  if (e == cudaSuccess) e = cudaMalloc(&sc, rows * ld_sc + 16);
+  int st = TQ_OK;
+  tq_qweight* w = nullptr;
+  if (e != cudaSuccess) st = fail(ctx, e == cudaErrorMemoryAllocation ? TQ_ENOMEM : TQ_ECUDA, "tq_quantize_matrix: %s", cudaGetErrorString(e));
+  if (st == TQ_OK) st = make_weight(ctx, kind, rows, cols, &w);
+  if (st == TQ_OK) {
+    const size_t n_blocks = rows * ((cols + 31) / 32);
+    quantize_rows_kernel<<<(unsigned)((n_blocks + 7) / 8), 256, 0, ctx->stream>>>(src_dev, src_dtype, ld, rows, cols, is_q4(kind) ? 1 : 0,
+                                                                                pay, sc);
+    ctx->launches++;
+    if (cudaGetLastError() != cudaSuccess) st = fail(ctx, TQ_ECUDA, "tq_quantize_matrix: launch failed");
+  }
+  if (st == TQ_OK) st = repack_from_device(ctx, w, pay, reinterpret_cast<const uint8_t*>(sc));
+  if (cudaStreamSynchronize(ctx->stream) != cudaSuccess && st == TQ_OK) st = fail(ctx, TQ_ECUDA, "tq_quantize_matrix: failed");
+  if (pay) cudaFree(pay);
+  if (sc) cudaFree(sc);
+  if (st != TQ_OK) {
+    if (w) tq_qweight_free(ctx, w);
+    cudaGetLastError();
     return st;
   }
   *out = w;

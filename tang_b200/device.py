@@ -171,6 +171,15 @@ class QuantComputeDevice:
         self._check(self._L.tq_argmax_rows(self._ctx, C.c_void_p(x.ptr), slices, rows, cols, C.c_void_p(out.ptr)))
         return out
 
+    def sample(self, logits: Buffer, rows: int, cols: int, cfg: "SamplerConfig", rng_states: Buffer | None = None,
+               past: Buffer | None = None, past_lens: Buffer | None = None, past_ld: int = 0, slices: int = 1) -> Buffer:
+        """``Sampler::sample`` (sampling.rs:86-158) for `rows` sequences; rng_states is a U64 buffer [rows] that the
+        call advances.  Returns int32 [rows]."""
+        out = self.alloc(rows, _lib.I32)
+        self._check(self._L.tq_sample(self._ctx, C.c_void_p(logits.ptr), slices, rows, cols, C.byref(cfg),
+                                      _opt_ptr(rng_states), _opt_ptr(past), _opt_ptr(past_lens), past_ld, C.c_void_p(out.ptr)))
+        return out
+
     def upload_bf16(self, data_f32) -> Buffer:
         """Uploads f32 data and narrows it to bf16 on the device (round to nearest even)."""
         tmp = self.upload(data_f32, F32)
@@ -237,6 +246,12 @@ class QuantComputeDevice:
         h = C.c_void_p()
         self._check(self._L.tq_qweight_from_device_arrays(self._ctx, kind, C.c_void_p(payload_ptr),
                                                           C.c_void_p(scales_ptr), rows, cols, C.byref(h)))
+        return self._wrap_q(h)
+
+    def quantize_matrix(self, src: Buffer, rows: int, cols: int, kind: int) -> QBuffer:
+        """``quantize_matrix_q4`` / ``quantize_matrix_q8`` (quantize.rs:193-220) on the device, bit-exact."""
+        h = C.c_void_p()
+        self._check(self._L.tq_quantize_matrix(self._ctx, C.c_void_p(src.ptr), src.dtype, 0, rows, cols, kind, C.byref(h)))
         return self._wrap_q(h)
 
     def dequantize(self, w: QBuffer):
@@ -310,6 +325,12 @@ class QuantComputeDevice:
     @property
     def launch_count(self) -> int:
         return int(self._L.tq_launch_count(self._ctx))
+
+
+class SamplerConfig(C.Structure):
+    """``SamplingConfig`` (crates/tang-infer/src/sampling.rs:6-20): temperature, top_k (0 = off), top_p (1 = off),
+    repetition_penalty (1 = off)."""
+    _fields_ = [("temperature", C.c_double), ("top_k", C.c_uint64), ("top_p", C.c_double), ("repetition_penalty", C.c_double)]
 
 
 class Graph:

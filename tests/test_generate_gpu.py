@@ -79,3 +79,85 @@ def test_generate_greedy_follows_the_oracle(dev, orc):
     assert np.array_equal(model2.generate_greedy(prompts, N), out)
     model.destroy()
     model2.destroy()
+
+
+def _draws(dev, orc, logits, cfg_vals, seeds, n_draws, past=None, slices=1):
+    """`n_draws` successive tq_sample calls on the same logits [rows, V] against the oracle's Sampler, row by row."""
+    import tang_b200 as tb
+
+    rows, V = logits.shape
+    x = logits
+    if slices > 1:
+        x = np.ascontiguousarray(logits.reshape(rows, slices, V // slices).transpose(1, 0, 2))
+    xb = dev.upload(x.astype(np.float32))
+    st = dev.upload(np.array(seeds, np.uint64).view(np.float64), tb.F64)
+    cfg = tb.SamplerConfig(*cfg_vals)
+    pb = lb = None
+    ld = 0
+    if past is not None:
+        ld = max(len(p) for p in past)
+        arr = np.zeros((rows, ld), np.int32)
+        for r, p in enumerate(past):
+            arr[r, :len(p)] = p
+        pb, lb = dev.upload(arr, tb.I32), dev.upload(np.array([len(p) for p in past], np.int32), tb.I32)
+    got = np.stack([dev.sample(xb, rows, V // slices, cfg, st, pb, lb, ld, slices=slices).to_vec() for _ in range(n_draws)], axis=1)
+    dev.sync()
+    ocfg = orc.SamplerConfig(*cfg_vals)
+    want = np.zeros_like(got)
+    final = []
+    for r in range(rows):
+        s = int(seeds[r])
+        for j in range(n_draws):
+            want[r, j], s = orc.sampler_sample(logits[r].astype(np.float32).astype(np.float64), ocfg, s, past[r] if past is not None else ())
+        final.append(s)
+    if cfg_vals[0] != 0.0:
+        assert list(st.to_vec().view(np.uint64)) == final          # the LCG states advanced exactly as the reference's
+    return got, want
+
+
+def test_sampler_reference_cases_on_device(dev, orc):
+    """sampling.rs:298-340: top_k = 2 over [1, 100, 0.1, 99] only ever yields tokens 1 and 3 (seed 12345);
+    top_p = 0.5 over [10, 0, 0, 0] always yields 0 (seed 99)."""
+    got, want = _draws(dev, orc, np.array([[1.0, 100.0, 0.1, 99.0]]), (1.0, 2, 1.0, 1.0), [12345], 100)
+    assert np.array_equal(got, want) and set(got[0]) == {1, 3}
+    got, want = _draws(dev, orc, np.array([[10.0, 0.0, 0.0, 0.0]]), (1.0, 0, 0.5, 1.0), [99], 20)
+    assert np.array_equal(got, want) and set(got[0]) == {0}
+
+
+@pytest.mark.parametrize("cfg", [(0.7, 40, 0.9, 1.0),      # SamplingConfig::standard()
+                                 (1.0, 5, 1.0, 1.0),       # top-k only
+                                 (1.3, 50, 0.6, 1.0),
+                                 (1.0, 1, 1.0, 1.0)])
+def test_sampler_matches_the_oracle_draw_for_draw(dev, orc, cfg):
+    rng = np.random.default_rng(int(cfg[1]) + 17)
+    logits = (rng.standard_normal((4, 32000)) * 3).astype(np.float32)
+    logits[1, [7, 900, 31999]] = logits[1].max() + 1.0        # exact ties at the top
+    got, want = _draws(dev, orc, logits, cfg, [1, 2, 3, 2 ** 63 + 5], 40)
+    assert np.array_equal(got, want)
+
+
+def test_sampler_repetition_penalty_and_greedy(dev, orc):
+    rng = np.random.default_rng(4)
+    logits = rng.standard_normal((3, 5000)).astype(np.float32)
+    past = [[int(np.argmax(logits[0]))] * 3 + [5, 9], [], list(range(0, 5000, 7))]
+    for cfg in ((0.0, 0, 1.0, 1.7), (0.8, 20, 0.95, 1.3)):
+        got, want = _draws(dev, orc, logits, cfg, [11, 12, 13], 10, past=past)
+        assert np.array_equal(got, want)
+
+
+def test_sampler_without_top_k_and_over_rank_major_slices(dev, orc):
+    """top_k off: more than 1024 probabilities survive, so the sums are block reductions and the nucleus threshold a
+    weighted radix selection (a draw can differ from the reference only when a running sum lands within rounding
+    of a threshold: not in these seeds)."""
+    rng = np.random.default_rng(8)
+    logits = (rng.standard_normal((2, 6000)) * 2).astype(np.float32)
+    for cfg in ((1.0, 0, 1.0, 1.0), (0.9, 0, 0.8, 1.0)):
+        got, want = _draws(dev, orc, logits, cfg, [21, 22], 30, slices=4)
+        assert np.array_equal(got, want)
+
+
+def test_sampler_llama3_vocabulary(dev, orc):
+    rng = np.random.default_rng(9)
+    logits = (rng.standard_normal((2, 128256)) * 4).astype(np.float32)
+    got, want = _draws(dev, orc, logits, (0.7, 40, 0.9, 1.0), [5, 6], 8)
+    assert np.array_equal(got, want)

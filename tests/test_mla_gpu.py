@@ -63,3 +63,31 @@ def test_absorbed_equals_naive_in_the_oracle(orc):
     a = orc.mla_decode_f64(*args, absorbed=True)
     n = orc.mla_decode_f64(*args, absorbed=False)
     assert rel_err(a, n, floor_frac=1.0) < 1e-2      # only the two bf16 roundings of the absorbed form apart
+
+
+@pytest.mark.gpu
+def test_head_shards_concatenate_to_the_full_result(dev, orc):
+    """Tensor parallelism of MLA decode is by head with the latent cache replicated: running the two halves of
+    the heads (their rows of W_UK / W_UV, their queries) separately gives the full output's halves bit for bit;
+    only the row-parallel W_O that follows needs an all-reduce (tests/test_tp.py covers that pattern)."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(77)
+    H, B, lens = 32, 2, [300, 77]
+    max_seq = max(lens) + 1
+    w_qk, s_qk, w_uv, s_uv, qn, qr, cache = make(rng, H, B, max_seq)
+    cbuf = dev.upload(cache[0], tb.BF16)
+
+    def run(h0, h1):
+        n = h1 - h0
+        wq = dev.upload_qarrays(tb.I8_ROW, w_qk[h0 * C_:h1 * C_], s_qk[h0 * C_:h1 * C_], n * C_, NOPE)
+        wu = dev.upload_qarrays(tb.I8_ROW, w_uv[h0 * VD:h1 * VD], s_uv[h0 * VD:h1 * VD], n * VD, C_)
+        o = tb.mla_decode(dev, wq, wu, dev.upload(np.ascontiguousarray(qn[0][:, h0:h1]), tb.BF16),
+                          dev.upload(np.ascontiguousarray(qr[0][:, h0:h1]), tb.BF16), cbuf, np.array(lens, np.int32), B, n, NOPE, VD,
+                          max_seq * (C_ + R_), max(lens))
+        dev.sync()
+        return o.to_vec().reshape(B, n * VD)
+
+    full = run(0, H)
+    halves = np.concatenate([run(0, H // 2), run(H // 2, H)], axis=1)
+    assert np.array_equal(full, halves)

@@ -265,3 +265,73 @@ def test_golden_matvec(orc):
             s, p = orc.quantize_matrix_q4(w, rows, cols)
             y = orc.q4_matvec(s, p, rows, cols, x)
         assert np.array_equal(y, want), name
+
+
+# ---------------------------------------------------------------------------------------------
+# Sampler (crates/tang-infer/src/sampling.rs)
+# ---------------------------------------------------------------------------------------------
+def test_lcg_known_answers(orc):
+    """sampling.rs:72-79: state' = state * 6364136223846793005 + 1442695040888963407 (mod 2^64), r = (state' >> 11) / 2^53,
+    recomputed here with Python integers."""
+    state = 42   # Sampler::new's seed (sampling.rs:63-68)
+    for _ in range(5):
+        want_state = (state * 6364136223846793005 + 1442695040888963407) % (1 << 64)
+        r, got_state = orc.lcg_next_f64(state)
+        assert got_state == want_state
+        assert r == (want_state >> 11) / float(1 << 53) and 0.0 <= r < 1.0
+        state = got_state
+
+
+def test_sampler_reference_cases(orc):
+    """The reference's own sampler tests (sampling.rs:265-340)."""
+    greedy = orc.SamplerConfig(0.0, 0, 1.0, 1.0)
+    assert orc.sampler_sample([1.0, 3.0, 10.0, 2.0], greedy, 42)[0] == 2            # greedy_sampling
+    st = 42
+    for _ in range(10):                                                              # greedy_sampling_repeated
+        tok, st = orc.sampler_sample([1.0, 5.0, 3.0], greedy, st)
+        assert tok == 1
+    assert orc.sampler_sample([1.0, 2.0, 5.0, 3.0], greedy, 42)[0] == 2              # temperature_zero_is_greedy
+    cfg = orc.SamplerConfig(1.0, 2, 1.0, 1.0)                                        # top_k_filters, seed 12345
+    st, seen = 12345, set()
+    for _ in range(100):
+        tok, st = orc.sampler_sample([1.0, 100.0, 0.1, 99.0], cfg, st)
+        seen.add(tok)
+    assert seen == {1, 3}
+    cfg = orc.SamplerConfig(1.0, 0, 0.5, 1.0)                                        # top_p_filters, seed 99
+    st = 99
+    for _ in range(20):
+        tok, st = orc.sampler_sample([10.0, 0.0, 0.0, 0.0], cfg, st)
+        assert tok == 0
+
+
+def test_sampler_rules_read_from_the_source(orc):
+    # repetition penalty: once per occurrence; positive logits are divided, the others multiplied (sampling.rs:94-104)
+    cfg = orc.SamplerConfig(0.0, 0, 1.0, 2.0)
+    assert orc.sampler_sample([4.0, 3.0, 1.0], cfg, 1, past=[0])[0] == 1             # 4/2 = 2 < 3
+    assert orc.sampler_sample([4.0, 1.5, 1.0], cfg, 1, past=[0])[0] == 0             # 4/2 = 2 > 1.5
+    assert orc.sampler_sample([4.0, 1.5, 1.0], cfg, 1, past=[0, 0])[0] == 1          # 4/2/2 = 1 < 1.5
+    assert orc.sampler_sample([-1.0, -1.5, -3.0], cfg, 1, past=[0])[0] == 1          # -1*2 = -2 < -1.5
+    # top-k keeps every entry that ties with the k-th largest (sampling.rs:127-133): k = 1 with two equal maxima
+    cfg = orc.SamplerConfig(1.0, 1, 1.0, 1.0)
+    st, seen = 7, set()
+    for _ in range(200):
+        tok, st = orc.sampler_sample([2.0, 5.0, 5.0, 1.0], cfg, st)
+        seen.add(tok)
+    assert seen == {1, 2}
+    # top-p cuts after the first rank whose running sum reaches p; equal probabilities keep index order
+    cfg = orc.SamplerConfig(1.0, 0, 0.5, 1.0)
+    st, seen = 3, set()
+    for _ in range(200):
+        tok, st = orc.sampler_sample([1.0, 1.0, 1.0, 1.0], cfg, st)   # 0.25 each: ranks 0, 1 reach 0.5
+        seen.add(tok)
+    assert seen == {0, 1}
+    # the draw itself: r < running sum, probabilities in index order
+    cfg = orc.SamplerConfig(1.0, 0, 1.0, 1.0)
+    logits = np.log(np.array([0.1, 0.2, 0.3, 0.4]))
+    st = 2024
+    for _ in range(50):
+        r, _ = orc.lcg_next_f64(st)
+        tok, st = orc.sampler_sample(logits, cfg, st)
+        p = np.exp(logits - logits.max())
+        p /= p.sum()
+        assert tok == int(np.searchsorted(np.cumsum(p), r, side="right"))

@@ -248,3 +248,42 @@ def test_tensor_memory_gemm(dev, orc, kind, rows, cols, m):
     # and the split-K meet adds its partials in a fixed order: the same call gives the same bits
     y24b = dev.qlinear(dev.upload(xbits[:24], tb.BF16), w, 24, tb.F32).to_vec().reshape(24, rows)
     assert np.array_equal(y24, y24b)
+
+
+@pytest.mark.parametrize("kind", [0, 2])                   # Q4 and Q8 blocks with f32 scales: the reference's own formats
+@pytest.mark.parametrize("rows,cols,src", [(5, 100, "f32"), (3, 32, "f32"), (64, 4096, "f32"), (40, 1000, "bf16")])
+def test_device_quantizer_is_bit_exact(dev, orc, kind, rows, cols, src):
+    """tq_quantize_matrix against quantize_matrix_q4/q8 (quantize.rs:47-118,193-220): every integer code and every
+    dequantised value (code * scale in f32) identical, including all-zero blocks (scale 1.0), exact .5 ties
+    (rounded away from zero), the clamp at the block maximum and a ragged tail."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(kind * 100 + rows + cols)
+    w = rng.standard_normal((rows, cols)).astype(np.float32)
+    w[0, :32] = 0.0                                          # zero block
+    if cols >= 64:
+        qmax = 7.0 if kind == 0 else 127.0
+        w[1, 32:64] = np.linspace(-1.0, 1.0, 32, dtype=np.float32)
+        w[1, 32] = -qmax                                     # amax = qmax: scale 1, inv_scale 1
+        w[1, 33:40] = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 3.5], np.float32)   # ties
+        w[1, 40] = qmax                                      # +qmax stays, -qmax-1 never appears for Q8; Q4 clamps at -8
+    if src == "bf16":
+        bits, w = bf16_round(w)
+        buf = dev.upload(bits, tb.BF16)
+    else:
+        buf = dev.upload(w, tb.F32)
+    qw = dev.quantize_matrix(buf, rows, cols, kind)
+    deq, ints = dev.dequantize(qw)
+    bpr = (cols + 31) // 32
+    for r in range(rows):
+        if kind == 0:
+            sc, packed = orc.quantize_q4(w[r])
+            want_i = orc.unpack_q4(packed)[:cols]
+            want_v = orc.dequantize_q4(sc, packed)[:cols]
+        else:
+            sc, vals = orc.quantize_q8(w[r])
+            want_i = vals[:cols]
+            want_v = orc.dequantize_q8(sc, vals)[:cols]
+        assert sc.size == bpr
+        assert np.array_equal(ints[r], want_i), r
+        assert np.array_equal(deq[r].view(np.uint32), want_v.view(np.uint32)), r
