@@ -100,6 +100,8 @@ int tq_ctx_create(int device, void* stream, tq_ctx** out) {
   }
   if (cudaMalloc(&ctx->dev_err, (1 + kTileCounters) * sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaMemsetAsync(ctx->dev_err, 0, (1 + kTileCounters) * sizeof(int), ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_err), sizeof(int), cudaHostAllocDefault) != cudaSuccess) return bail(TQ_ECUDA);
+  *ctx->host_err = 0;
   if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
   *out = ctx;
   return TQ_OK;
@@ -113,6 +115,7 @@ int tq_ctx_destroy(tq_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->splitk) cudaFree(ctx->splitk);
   if (ctx->dev_err) cudaFree(ctx->dev_err);
+  if (ctx->host_err) cudaFreeHost(ctx->host_err);
   if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
   return TQ_OK;
@@ -124,9 +127,10 @@ void* tq_ctx_stream(tq_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
 int tq_sync(tq_ctx* ctx) {
   if (int st = bind(ctx)) return st;
+  // the status word rides behind the work on the same stream: one wait, no second round trip
+  TQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_err, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  int code = 0;
-  TQ_CUDA(ctx, cudaMemcpy(&code, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+  const int code = *ctx->host_err;
   if (code != 0) {
     cudaMemset(ctx->dev_err, 0, sizeof(int));
     return fail(ctx, TQ_ETIMEOUT, "a kernel gave up a bounded wait (device code %d)", code);

@@ -18,6 +18,7 @@ struct tq_ctx {
   bool owns_stream = false;
   int* dev_err = nullptr;        // device status word written by kernels that give up a bounded wait,
                                  // followed by kTileCounters zeroed tile counters (split-K meets)
+  int* host_err = nullptr;       // pinned copy target of dev_err: tq_sync reads the status with one stream wait
   void* xprep = nullptr;         // activation staging for tq_qlinear (bf16 copy / 3-way f32 split)
   size_t xprep_bytes = 0;
   void* scratch = nullptr;       // general workspace (attention partials, host-call staging, ...)

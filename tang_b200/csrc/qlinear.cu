@@ -623,6 +623,16 @@ int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void*
     xd = s + off_x2;
   }
   const int dev_dt = dtype == TQ_BF16 ? TQ_BF16 : TQ_F32;
+  if (dtype != TQ_F64) {
+    // A pinned result vector is visible to the device: the kernel stores y straight into it (posted writes over
+    // the bus) and the separate device-to-host copy disappears.  x is still copied once: every CTA reads all of it.
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, y_host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer) {
+      if (int st = tq_qlinear(ctx, w, xd, dev_dt, 0, m, attr.devicePointer, dev_dt, 0, nullptr)) return st;
+      return tq_sync(ctx);
+    }
+    cudaGetLastError();   // an unregistered pointer is not an error here
+  }
   if (int st = tq_qlinear(ctx, w, xd, dev_dt, 0, m, s + off_y, dev_dt, 0, nullptr)) return st;
   const void* yd = s + off_y;
   if (dtype == TQ_F64) {

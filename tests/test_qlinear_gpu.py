@@ -287,3 +287,25 @@ def test_device_quantizer_is_bit_exact(dev, orc, kind, rows, cols, src):
         assert sc.size == bpr
         assert np.array_equal(ints[r], want_i), r
         assert np.array_equal(deq[r].view(np.uint32), want_v.view(np.uint32)), r
+
+
+def test_host_matvec_into_pinned_memory(dev, orc):
+    """A pinned result vector is written by the kernel itself (no device-to-host copy): same bits as the pageable path."""
+    import ctypes as C
+
+    import torch
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(31)
+    rows, cols = 512, 1024
+    sc, pay = make_weight(rng, 1, rows, cols)
+    w = _upload(dev, 1, sc, pay, rows, cols)
+    for dt, tdt, npdt in ((tb.F32, torch.float32, np.float32), (tb.BF16, torch.bfloat16, np.uint16)):
+        x32 = rng.standard_normal(cols).astype(np.float32)
+        xh = torch.from_numpy(x32).to(tdt).pin_memory()
+        yh = torch.empty(rows, dtype=tdt).pin_memory()
+        dev._check(dev._L.tq_q_matvec_host(dev._ctx, C.c_void_p(w.handle), C.c_void_p(xh.data_ptr()), C.c_void_p(yh.data_ptr()), dt, 1))
+        x_np = xh.view(torch.int16).numpy().view(np.uint16) if dt == tb.BF16 else xh.numpy()
+        y_pageable = dev._matvec_host(w, x_np.copy(), 1)
+        y_pinned = yh.view(torch.int16).numpy().view(np.uint16) if dt == tb.BF16 else yh.numpy()
+        assert np.array_equal(y_pinned, y_pageable)
