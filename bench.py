@@ -166,7 +166,7 @@ def run_reference(args, rank: int) -> None:
 
 
 def workload_config(args) -> dict:
-    return {"workload": f"int4-g32/f16-scale dequant-GEMV K={K_IN} N={N_OUT} M={args.m} (BASELINE configs[1])",
+    return {"workload": f"int4-g32/f16-scale dequant-GEMV K={K_IN} N={N_OUT} M={args.m} (the headline int4 GEMM configuration)",
             "layers_per_step": args.layers, "m": args.m,
             "l2": f"{args.layers} distinct weight matrices per step ({args.layers * algorithmic_bytes(args.m) / 1e6:.0f} MB) >> 126 MB L2",
             "parallelism": f"replicated column shards x{args.gpus}, no data-path collective"}
@@ -361,7 +361,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
 
 # ----------------------------------------------------------------------------------------------
-# Llama-3-8B-shaped decode step (BASELINE configs[2]): 32 layers, d 4096, 32/8 heads of 128, FFN
+# Llama-3-8B-shaped decode step (the decode configuration): 32 layers, d 4096, 32/8 heads of 128, FFN
 # 14336, vocab 128256, int4-g32/f16 weights, bf16 KV cache prefilled to 2048 positions; tensor
 # parallel over the ranks of this job.  Random-init weights generated on the device.
 # ----------------------------------------------------------------------------------------------
@@ -473,9 +473,9 @@ def run_decode(dev, tb, torch, stream, comm, rank, world, args, barrier):
 
 
 # ----------------------------------------------------------------------------------------------
-# The other BASELINE configurations, timed briefly at N=1 and reported under "extras": the M sweep of
-# configs[1], the DeepSeek-V2-Lite-shaped MoE layer (configs[3]) and the DeepSeek-V3-shaped MLA decode
-# attention (configs[4]).  Seeded synthetic inputs generated on the device.
+# The other benchmark configurations, timed briefly at N=1 and reported under "extras": the M sweep of
+# the int4 GEMM, the DeepSeek-V2-Lite-shaped MoE layer and the DeepSeek-V3-shaped MLA decode
+# attention.  Seeded synthetic inputs generated on the device.
 # ----------------------------------------------------------------------------------------------
 def _time_ms(torch, stream, dev, fn, reps, warm=2):
     for _ in range(warm):
@@ -522,7 +522,7 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
         stream.synchronize()
         return t
 
-    # ---- configs[1]: M sweep over 6 distinct matrices (198 MB > L2), bf16 results, one CUDA graph per M
+    # ---- int4 GEMM: M sweep over 6 distinct matrices (198 MB > L2), bf16 results, one CUDA graph per M
     n_mat = 6
     ws = [q4(N_OUT, K_IN) for _ in range(n_mat)]
     sweep = []
@@ -550,7 +550,7 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
     del ws
     torch.cuda.empty_cache()
 
-    # ---- configs[3]: MoE layer, d 2048, 64 routed + 2 shared experts of width 1408, top-6
+    # ---- MoE layer, d 2048, 64 routed + 2 shared experts of width 1408, top-6
     d, ffn, E, k, nsh = 2048, 1408, 64, 6, 2
     wg = bf16((E, d), 0.02)
     layer = tb.MoeLayer(dev, tb.MoeConfig(d, ffn, E, k, nsh, 0, 0, 1), tb.Buffer(dev, wg.data_ptr(), wg.numel(), tb.BF16, owns=False),
@@ -576,7 +576,7 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
     layer.destroy()
     torch.cuda.empty_cache()
 
-    # ---- configs[4]: MLA decode attention, 128 heads, latent 512 + rope 64, int8 per-row W_UK / W_UV
+    # ---- MLA decode attention, 128 heads, latent 512 + rope 64, int8 per-row W_UK / W_UV
     H, NOPE, VD, CL, RP = 128, 128, 128, 512, 64
     wq, wu = i8(H * CL, NOPE), i8(H * VD, CL)
     mla = []

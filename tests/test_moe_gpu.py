@@ -69,7 +69,7 @@ def test_renormalised_weights(dev, orc):
 
 @pytest.mark.parametrize("T", [1, 64])
 def test_deepseek_v2_lite_shape(dev, orc, T):
-    """d_model 2048, 64 routed + 2 shared experts of width 1408, top-6 (BASELINE configs[3])."""
+    """d_model 2048, 64 routed + 2 shared experts of width 1408, top-6."""
     host = HostMoe(np.random.default_rng(7), d=2048, ffn=1408, n_experts=64, top_k=6, n_shared=2)
     check(dev, orc, host, T, seed=100 + T)
 
