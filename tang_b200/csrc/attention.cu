@@ -41,7 +41,6 @@ struct GqaParams {
   int out_f32;
   float* part_o;                 // [B, n_heads, n_splits, kHD]
   float* part_ml;                // [B, n_heads, n_splits, 2]
-  int* counters;                 // [B * n_kv] zero between launches (in-kernel merge of the splits), or null
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -247,36 +246,6 @@ __global__ void __launch_bounds__(kAttnThreads) gqa_decode_kernel(const GqaParam
       }
     }
   }
-  if (p.n_splits > 1 && p.counters) {
-    // The split that finishes last merges the partials of its (sequence, KV head) in split order: one launch
-    // less per layer, and the result does not depend on which CTA came last.
-    __shared__ int last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int* c = p.counters + b * p.n_kv + kvh;
-      last = atomicAdd(c, 1) == p.n_splits - 1;
-      if (last) *c = 0;
-    }
-    __syncthreads();
-    if (!last) return;
-    __threadfence();
-    for (int idx = threadIdx.x; idx < p.group * kHD; idx += kAttnThreads) {
-      const int r = idx / kHD, d = idx % kHD;
-      const size_t bh = (size_t)b * p.n_heads + kvh * p.group + r;
-      float M = -FLT_MAX;
-      for (int s2 = 0; s2 < p.n_splits; ++s2) M = fmaxf(M, __ldcg(p.part_ml + (bh * p.n_splits + s2) * 2));
-      float L = 0.f, O = 0.f;
-      for (int s2 = 0; s2 < p.n_splits; ++s2) {
-        const float wgt = exp2f((__ldcg(p.part_ml + (bh * p.n_splits + s2) * 2) - M) * kLog2e);
-        L += __ldcg(p.part_ml + (bh * p.n_splits + s2) * 2 + 1) * wgt;
-        O += __ldcg(p.part_o + (bh * p.n_splits + s2) * kHD + d) * wgt;
-      }
-      const float v = L > 0.f ? O / L : 0.f;
-      if (p.out_f32) reinterpret_cast<float*>(p.out)[bh * kHD + d] = v;
-      else reinterpret_cast<__nv_bfloat16*>(p.out)[bh * kHD + d] = __float2bfloat16_rn(v);
-    }
-  }
 }
 
 __global__ void __launch_bounds__(kHD) gqa_combine_kernel(const float* part_o, const float* part_ml, int n_splits,
@@ -385,11 +354,9 @@ int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const voi
     TQ_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_set = true;
   }
-  // the in-kernel merge needs one counter per (sequence, KV head); beyond that a second kernel merges
-  p.counters = (n_splits > 1 && (size_t)B * n_kv <= (size_t)kTileCounters) ? ctx->dev_err + 1 : nullptr;
   dim3 grid((unsigned)n_splits, (unsigned)n_kv, (unsigned)B);
   TQ_CUDA(ctx, launch_k(ctx, gqa_decode_kernel, grid, dim3(kAttnThreads), smem, p));
-  if (n_splits > 1 && !p.counters)
+  if (n_splits > 1)
     TQ_CUDA(ctx, launch_k(ctx, gqa_combine_kernel, dim3((unsigned)(B * n_heads)), dim3(kHD), 0, (const float*)p.part_o,
                           (const float*)p.part_ml, n_splits, out, p.out_f32));
   return TQ_OK;
@@ -510,7 +477,6 @@ int tq_gqa_decode_noalloc(tq_ctx* ctx, const void* q_dev, const void* k_cache_de
   p.chunk = (tiles_per_split > 0 ? tiles_per_split : 1) * kTileKeys;
   p.part_o = n_splits > 1 ? static_cast<float*>(g_noalloc_ptr[ctx->device]) : nullptr;
   p.part_ml = n_splits > 1 ? p.part_o + n_part * kHD : nullptr;
-  p.counters = nullptr;   // this entry keeps the two-kernel form: it owns no zeroed counters
   dim3 grid((unsigned)n_splits, (unsigned)n_kv, (unsigned)B);
   gqa_decode_kernel<<<grid, kAttnThreads, smem, ctx->stream>>>(p);
   ctx->launches++;
