@@ -29,6 +29,11 @@ int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const v
 constexpr int kMaxExperts = 256;
 constexpr int kMaxTopK = 16;
 
+int launch_qgemm_umma_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, size_t m_total,
+                              const int* counts, const int* offsets, const int* active, int max_active, int max_rows,
+                              int expected_rows, void* y, int y_dtype, size_t ldy);
+bool umma_grouped_supported(const tq_qweight* w, int n_groups);
+
 // One CTA of eight warps per token; warp w computes the logits of experts w, w + 8, ...
 // The reference order is one f64 addition per k, ascending, of products that are exact in f64 (bf16 x
 // bf16).  A warp-parallel sum gives the SAME BITS whenever no addition can round, whatever the order:
@@ -440,9 +445,22 @@ int tq_moe_ffn(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_de
   while (cap < 64 && (size_t)cap < want) cap <<= 1;
   if ((size_t)cap > T) cap = (int)T;
   const int max_active = (int)(n < (size_t)nl ? n : (size_t)nl);   // at most one expert per (token, choice)
-  TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, cap, cnt, offs, (int)T, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
+  // from about 24 rows per expert on, the expert GEMMs run on the tcgen05 kernel (one launch over all experts)
+  const size_t expected = n / (size_t)c.n_experts;
+  const bool tensor_path = expected >= 24 && umma_grouped_supported(m->w_gate_up, nl) && umma_grouped_supported(m->w_down, nl);
+  if (tensor_path) {
+    TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_gate_up, nl, xs, d, n, cnt, offs, active, max_active, (int)T, (int)(expected * 3 / 2),
+                                      gu, TQ_F32, 2 * f));
+  } else {
+    TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, cap, cnt, offs, (int)T, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
+  }
   TQ_STEP(tq_swiglu(ctx, gu, gu + f, TQ_F32, 2 * f, n, f, act, TQ_BF16));
-  TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, cap, cnt, offs, (int)T, 0, 0, yo, TQ_F32, d, active, max_active));
+  if (tensor_path) {
+    TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_down, nl, act, f, n, cnt, offs, active, max_active, (int)T, (int)(expected * 3 / 2), yo,
+                                      TQ_F32, d));
+  } else {
+    TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, cap, cnt, offs, (int)T, 0, 0, yo, TQ_F32, d, active, max_active));
+  }
   for (size_t i = 0; i < m->sh_gate_up.size() && Ts > 0; ++i) {
     TQ_STEP(tq_qlinear(ctx, m->sh_gate_up[i], h + sh_lo * d, TQ_BF16, d, Ts, shgu, TQ_F32, 2 * f, nullptr));
     TQ_STEP(tq_swiglu(ctx, shgu, shgu + f, TQ_F32, 2 * f, Ts, f, shact, TQ_BF16));
@@ -532,9 +550,21 @@ int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, floa
   while (chunk < 64 && (size_t)chunk < want) chunk <<= 1;
   const int max_rows = (int)((size_t)W * T < R ? (size_t)W * T : R);   // an expert gets a token at most once
   const int max_active = (int)(R < (size_t)nl ? R : (size_t)nl);
-  TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, chunk, cnt, offs, max_rows, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
+  const size_t expected = (size_t)W * n / (size_t)c.n_experts;      // rows per local expert when routing is even
+  const bool tensor_path = expected >= 24 && umma_grouped_supported(m->w_gate_up, nl) && umma_grouped_supported(m->w_down, nl);
+  if (tensor_path) {
+    TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_gate_up, nl, xs, d, R, cnt, offs, active, max_active, max_rows, (int)(expected * 3 / 2),
+                                      gu, TQ_F32, 2 * f));
+  } else {
+    TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, chunk, cnt, offs, max_rows, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
+  }
   TQ_STEP(tq_swiglu(ctx, gu, gu + f, TQ_F32, 2 * f, R, f, act, TQ_BF16));
-  TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, chunk, cnt, offs, max_rows, 0, 0, yo, TQ_F32, d, active, max_active));
+  if (tensor_path) {
+    TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_down, nl, act, f, R, cnt, offs, active, max_active, max_rows, (int)(expected * 3 / 2), yo,
+                                      TQ_F32, d));
+  } else {
+    TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, chunk, cnt, offs, max_rows, 0, 0, yo, TQ_F32, d, active, max_active));
+  }
   moe_scatter_back_kernel<<<(unsigned)R, 128, 0, ctx->stream>>>(yo, bucket, slot, nl, (int)d, back);
   TQ_LAUNCHED();
   // combine: results back to the places they came from

@@ -31,8 +31,25 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.stages, RS = p.raw_stages, KT = p.kt;
   const int rb0 = blockIdx.x * (kUmmaRows / kTileRows);        // first 16-row block
-  const int m0 = blockIdx.y * p.ntok;                          // first token of this CTA
-  const int kc_begin = blockIdx.z * p.kc_per_split;            // this CTA's slice of K, in 128-k tiles
+  int m0 = blockIdx.y * p.ntok;                                // first token of this CTA
+  int m_end = p.m_total;                                       // rows at or beyond this are not this CTA's to store
+  const uint8_t* tile_base = p.tiles;
+  if (p.g_counts) {
+    // grouped (experts): blockIdx.z picks the group, whose rows are g_offsets[e] .. +g_counts[e] of x and y and
+    // whose weights start g_tile_stride bytes further on; token tiles beyond the group's rows leave at once
+    pdl_wait();
+    int e = blockIdx.z;
+    if (p.g_active) {
+      e = p.g_active[e];
+      if (e < 0) return;
+    }
+    const int cnt = p.g_counts[e];
+    if (m0 >= cnt) return;
+    m_end = p.g_offsets[e] + cnt;
+    m0 += p.g_offsets[e];
+    tile_base += (size_t)e * p.g_tile_stride;
+  }
+  const int kc_begin = p.g_counts ? 0 : blockIdx.z * p.kc_per_split;   // this CTA's slice of K, in 128-k tiles
   const int kc_len = min(p.kc_per_split, p.kc_total - kc_begin);
   const int n_kb = kc_len * 2;                                 // 64-k steps
 
@@ -84,7 +101,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
 #endif
         mbar_arrive_expect_tx(&raw_full[r], 8u * kcs * TB);
         for (int i = 0; i < 8; ++i)
-          bulk_g2s(raw_s + ((size_t)(r * 8 + i) * KT) * TB, p.tiles + ((size_t)(rb0 + i) * p.kc_total + kc_begin + t0) * TB,
+          bulk_g2s(raw_s + ((size_t)(r * 8 + i) * KT) * TB, tile_base + ((size_t)(rb0 + i) * p.kc_total + kc_begin + t0) * TB,
                    kcs * TB, &raw_full[r], pol_w);
         if (++r == RS) {
           r = 0;
@@ -330,13 +347,13 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int m = m0 + c0 + i;
-            if (m < p.m_total) __stcg(part + (size_t)m * p.n_rows + n, v[i]);
+            if (m < m_end) __stcg(part + (size_t)m * p.n_rows + n, v[i]);
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int m = m0 + c0 + i;
-            if (m < p.m_total) {
+            if (m < m_end) {
               if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(v[i]);
               else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + n] = v[i];
             }
@@ -402,8 +419,10 @@ bool umma_supported(const tq_qweight* w, size_t m) {
 }
 
 // y[m, rows] = x[m, cols] . W^T through the tcgen05 kernel.  x: bf16, 16-byte aligned rows.
+// With `grp`: `grp->n_groups` weight matrices stacked by rows (experts); group e multiplies rows
+// offsets[e] .. +counts[e] of x (device arrays) and m is the total row count of x / y.
 int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
-                      size_t ldy, int terms) {
+                      size_t ldy, int terms, const UmmaGroups* grp) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return fail(ctx, TQ_EUNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
   TQ_REQUIRE(ctx, umma_supported(w, m), "tcgen05 GEMM: needs a Q4 weight with rows %% 128 == 0 and cols %% 128 == 0");
@@ -416,12 +435,19 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   const size_t budget = kSmemMax - kUmmaHeader - 1024;
   int ntok_max = (int)(((budget - 4 * raw_tile) / kUmmaGroups - (size_t)terms * kUmmaRows * 128) / 128) / 16 * 16;
   if (ntok_max > 256) ntok_max = 256;
-  const size_t n_tok_tiles = (m + ntok_max - 1) / ntok_max;
-  const int ntok = (int)(((m + n_tok_tiles - 1) / n_tok_tiles + 15) / 16 * 16);
+  const size_t rows_g = grp ? w->rows / grp->n_groups : w->rows;       // output features per group
+  if (grp) TQ_REQUIRE(ctx, grp->n_groups > 0 && w->rows % grp->n_groups == 0 && rows_g % kUmmaRows == 0 && grp->counts && grp->offsets,
+                      "tcgen05 GEMM: every group needs a multiple of 128 output features");
+  // grouped: the token tile follows the expected rows per group (tiles past a group's rows leave at once)
+  const size_t m_tile_basis = grp ? (size_t)grp->expected_rows : m;
+  const size_t n_tok_tiles = grp ? 1 : (m + ntok_max - 1) / ntok_max;
+  int ntok = (int)(((m_tile_basis + n_tok_tiles - 1) / n_tok_tiles + 15) / 16 * 16);
+  if (ntok > ntok_max) ntok = ntok_max;
+  if (ntok < 16) ntok = 16;
   // Few output tiles (narrow layers, small batches) leave most SMs idle: split K over gridDim.z.
   const int base_ctas = (int)(w->rows / kUmmaRows) * (int)n_tok_tiles;
   int splits = 1;
-  if (base_ctas < (ctx->sm_count * 3) / 4) {
+  if (!grp && base_ctas < (ctx->sm_count * 3) / 4) {
     splits = ctx->sm_count / base_ctas;
     if (splits > w->n_kc / 4) splits = w->n_kc / 4;      // at least eight 64-k steps per CTA
     if (splits > 16) splits = 16;
@@ -462,7 +488,11 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.y = y;
   p.ldy = (long long)ldy;
   p.m_total = (int)m;
-  p.n_rows = (int)w->rows;
+  p.n_rows = (int)rows_g;
+  p.g_counts = grp ? grp->counts : nullptr;
+  p.g_offsets = grp ? grp->offsets : nullptr;
+  p.g_active = grp ? grp->active : nullptr;
+  p.g_tile_stride = (long long)(rows_g / kTileRows) * w->n_kc * qk_tile_bytes(w->kind);
   p.kc_total = w->n_kc;
   p.ntok = ntok;
   p.tmem_cols = tmem_cols;
@@ -483,7 +513,11 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.kt = kt;
   const size_t smem = umma_smem_bytes(w->kind, terms, ntok, stages, raw_stages * kt);
   if (smem > kSmemMax) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: %zu bytes of shared memory needed", smem);
-  dim3 grid((unsigned)(w->rows / kUmmaRows), (unsigned)((m + ntok - 1) / ntok), (unsigned)splits);
+  dim3 grid((unsigned)(rows_g / kUmmaRows), (unsigned)((m + ntok - 1) / ntok), (unsigned)splits);
+  if (grp) {
+    grid.y = (unsigned)((grp->max_rows + ntok - 1) / ntok);
+    grid.z = (unsigned)((grp->active && grp->max_active < grp->n_groups) ? grp->max_active : grp->n_groups);
+  }
   auto go = [&](auto kern) -> cudaError_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -510,6 +544,26 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   }
 #endif
   return TQ_OK;
+}
+
+// Grouped entry for the other translation units: experts stacked by rows, rows of x / y grouped by expert.
+int launch_qgemm_umma_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, size_t m_total,
+                              const int* counts, const int* offsets, const int* active, int max_active, int max_rows,
+                              int expected_rows, void* y, int y_dtype, size_t ldy) {
+  UmmaGroups g;
+  g.n_groups = n_groups;
+  g.counts = counts;
+  g.offsets = offsets;
+  g.active = active;
+  g.max_active = max_active;
+  g.max_rows = max_rows;
+  g.expected_rows = expected_rows;
+  return launch_qgemm_umma(ctx, w, x_bf16, ldx, m_total, y, y_dtype, ldy, y_dtype == TQ_F32 ? 2 : 1, &g);
+}
+
+bool umma_grouped_supported(const tq_qweight* w, int n_groups) {
+  return (w->kind == TQ_Q4_F16 || w->kind == TQ_Q4_F32) && n_groups > 0 && w->rows % n_groups == 0 &&
+         (w->rows / n_groups) % kUmmaRows == 0 && w->cols % kTileK == 0;
 }
 
 }  // namespace tq

@@ -57,11 +57,26 @@ struct UmmaParams {
   int kc_per_split;       // 128-k tiles per split
   float* partial;         // [splits][m_total][n_rows] f32, only when splits > 1
   int* counters;          // one per output tile, zero between launches
+  const int* g_counts;    // grouped launches (experts stacked by rows): rows of x / y per group, or null
+  const int* g_offsets;   // first row of each group
+  const int* g_active;    // optional list of group ids with rows (-1 = unused entry); blockIdx.z indexes it
+  long long g_tile_stride;   // bytes between the groups' fragment tiles
   int* err;
 #ifdef TQ_UMMA_PROFILE
   long long* prof;      // cycle counters of CTA 0 (profiling builds only)
   int dbg;              // bit 0: no dequant math, 1: no MMA, 2: no weight copies, 3: no activation copies
 #endif
+};
+
+// Host-side description of a grouped launch (device arrays come from the router's bookkeeping kernels).
+struct UmmaGroups {
+  int n_groups = 1;
+  const int* counts = nullptr;
+  const int* offsets = nullptr;
+  const int* active = nullptr;
+  int max_active = 0;      // upper bound of groups with rows (sizes gridDim.z)
+  int max_rows = 0;        // upper bound of counts[e] (sizes gridDim.y)
+  int expected_rows = 0;   // typical counts[e]: sets the token tile
 };
 
 __host__ __device__ inline size_t umma_stage_bytes(int terms, int ntok) {

@@ -282,8 +282,9 @@ int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const v
 }
 
 bool umma_supported(const tq_qweight* w, size_t m);
+struct UmmaGroups;
 int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
-                      size_t ldy, int terms);
+                      size_t ldy, int terms, const UmmaGroups* grp);
 
 // Activation rows from which the tcgen05 kernel takes over from the mma.sync kernel (TQ_UMMA_MIN_M
 // overrides; 0 disables the tcgen05 path).
@@ -575,7 +576,7 @@ int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x_dtype,
     if (int st = ensure_xprep(ctx, rows_staged * kx * 2)) return st;
   }
   if (direct && !residual_dev && umma_min_m() > 0 && m >= (size_t)umma_min_m() && umma_supported(w, m))
-    return launch_qgemm_umma(ctx, w, x_dev, ldx, m, y_dev, y_dtype, ldy, y_dtype == TQ_F32 ? 2 : 1);
+    return launch_qgemm_umma(ctx, w, x_dev, ldx, m, y_dev, y_dtype, ldy, y_dtype == TQ_F32 ? 2 : 1, nullptr);
   const size_t xe = x_dtype == TQ_F32 ? 4 : 2, ye = y_dtype == TQ_F32 ? 4 : 2;
   for (size_t m0 = 0; m0 < m; m0 += chunk) {
     const size_t mc = m - m0 < chunk ? m - m0 : chunk;

@@ -74,7 +74,7 @@ def test_deepseek_v2_lite_shape(dev, orc, T):
     check(dev, orc, host, T, seed=100 + T)
 
 
-@pytest.mark.parametrize("T", [1, 7, 40])
+@pytest.mark.parametrize("T", [1, 7, 40, 130])
 def test_dispatch_variant_on_one_rank_equals_the_oracle(dev, orc, T):
     """tq_moe_ffn_dispatch with a single rank: both exchanges are local copies, everything else is the same code
     the multi-rank path runs (places, buckets, scatter back, combine)."""
