@@ -11,6 +11,8 @@ namespace tq {
 
 int ensure_xprep(tq_ctx* ctx, size_t bytes) {
   if (ctx->xprep_bytes >= bytes) return TQ_OK;
+  if (ctx->capturing)   // growing means a stream wait and an allocation, neither of which a capture allows
+    return fail(ctx, TQ_EINVAL, "a workspace has to grow (%zu bytes) during graph capture: run the same calls once before tq_graph_begin", bytes);
   if (ctx->xprep) {
     TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     TQ_CUDA(ctx, cudaFree(ctx->xprep));
@@ -25,6 +27,8 @@ int ensure_xprep(tq_ctx* ctx, size_t bytes) {
 
 int ensure_scratch(tq_ctx* ctx, size_t bytes) {
   if (ctx->scratch_bytes >= bytes) return TQ_OK;
+  if (ctx->capturing)   // growing means a stream wait and an allocation, neither of which a capture allows
+    return fail(ctx, TQ_EINVAL, "a workspace has to grow (%zu bytes) during graph capture: run the same calls once before tq_graph_begin", bytes);
   if (ctx->scratch) {
     TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     TQ_CUDA(ctx, cudaFree(ctx->scratch));
@@ -39,6 +43,8 @@ int ensure_scratch(tq_ctx* ctx, size_t bytes) {
 
 int ensure_splitk(tq_ctx* ctx, size_t bytes) {
   if (ctx->splitk_bytes >= bytes) return TQ_OK;
+  if (ctx->capturing)   // growing means a stream wait and an allocation, neither of which a capture allows
+    return fail(ctx, TQ_EINVAL, "a workspace has to grow (%zu bytes) during graph capture: run the same calls once before tq_graph_begin", bytes);
   if (ctx->splitk) {
     TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     TQ_CUDA(ctx, cudaFree(ctx->splitk));
