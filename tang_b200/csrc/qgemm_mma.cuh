@@ -214,20 +214,15 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
     uint32_t ph = 0;
     int st0 = body_off;  // offset of the current stage
     int kc = wk_i * TPW;
-    uint32_t tok = mbar_test(&full_bar[0], 0);   // looked at one stage ahead, so the answer is there when needed
 #pragma unroll 1
     for (int it = 0; it < n_iters; ++it, kc += KT) {
-      if (!tok) {
-        if (*failed) break;
-        if (!mbar_wait_spin(&full_bar[s], ph)) {
-          *failed = 1;
-          atomicCAS(p.err, 0, (int)DERR_FULL_WAIT);
-          break;
-        }
-      }
-      {
-        const bool wrap = s + 1 == S;
-        tok = it + 1 < n_iters ? mbar_test(&full_bar[wrap ? 0 : s + 1], wrap ? ph ^ 1u : ph) : 0u;
+      // (looking at the next stage's barrier one stage ahead was measured: 11.9 -> 12.4 us; with four CTAs per SM
+      // the other warps already cover the wait)
+      if (*failed) break;
+      if (!mbar_wait_spin(&full_bar[s], ph)) {
+        *failed = 1;
+        atomicCAS(p.err, 0, (int)DERR_FULL_WAIT);
+        break;
       }
       const int nu = (rb_ok && p.debug != 1) ? min(TPW, p.kc_total - kc) : 0;       // tiles of this warp that exist
 #pragma unroll 1
