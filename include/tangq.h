@@ -193,11 +193,13 @@ TQ_API int tq_sample(tq_ctx* ctx, const float* logits_dev, size_t slices, size_t
                      unsigned long long* rng_states_dev, const int* past_tokens_dev_or_null, const int* past_lens_dev_or_null,
                      size_t past_ld, int* tokens_out_dev);
 /* The bookkeeping of `generate` (sampling.rs:229-256) between two decode steps, on the device: stores the chosen
- * tokens in out_tokens[row][*step], makes them the next step's input, adds one to every position and to *step.
- * With the decode step and tq_argmax_rows in front of it, one captured graph generates a token per replay and
- * no logits leave the device.  rows <= 1024. */
+ * tokens in out_tokens[row][*step], makes them the next step's input, adds one to every position, to *step and
+ * (when given) to every entry of lens_io -- the per-sequence count of past tokens that tq_sample's repetition
+ * penalty reads when out_tokens is the sequences' whole history and *step starts at the prompt length.
+ * With the decode step and tq_argmax_rows / tq_sample in front of it, one captured graph generates a token per
+ * replay and no logits leave the device.  rows <= 1024. */
 TQ_API int tq_generate_advance(tq_ctx* ctx, const int* chosen_dev, size_t rows, int* tokens_io_dev, int* positions_io_dev,
-                               int* out_tokens_dev, size_t out_ld, int* step_io_dev);
+                               int* out_tokens_dev, size_t out_ld, int* step_io_dev, int* lens_io_dev_or_null);
 
 /* ---- attention -------------------------------------------------------------------------------
  * ComputeDevice::kv_attention (device.rs:161-180; cpu.rs:257-315) on f32 buffers, exactly the

@@ -58,7 +58,7 @@ PROTOTYPES = {
     "tq_embedding": (_i, [_p, _p, _i, _p, _sz, _sz, _sz, _p, _i]),
     "tq_argmax_rows": (_i, [_p, _p, _sz, _sz, _sz, _p]),
     "tq_sample": (_i, [_p, _p, _sz, _sz, _sz, _p, _p, _p, _p, _sz, _p]),
-    "tq_generate_advance": (_i, [_p, _p, _sz, _p, _p, _p, _sz, _p]),
+    "tq_generate_advance": (_i, [_p, _p, _sz, _p, _p, _p, _sz, _p, _p]),
     "tq_kv_attention": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p]),
     "tq_gqa_decode": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),
     "tq_gqa_decode_noalloc": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),

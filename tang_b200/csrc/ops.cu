@@ -266,7 +266,7 @@ __global__ void argmax_rows_kernel(const float* x, int slices, int rows, int col
 // Between two decode steps of a generation loop: record the chosen tokens, make them the next input, advance the
 // positions.  The step counter lives on the device so that the same captured graph can be replayed.
 __global__ void generate_advance_kernel(const int* chosen, int rows, int* tokens_io, int* positions_io, int* out_tokens,
-                                        int out_ld, int* step_io) {
+                                        int out_ld, int* step_io, int* lens_io) {
   pdl_wait();
   pdl_launch_dependents();
   const int step = *step_io;
@@ -275,6 +275,7 @@ __global__ void generate_advance_kernel(const int* chosen, int rows, int* tokens
     if (step < out_ld) out_tokens[(size_t)i * out_ld + step] = chosen[i];
     tokens_io[i] = chosen[i];
     positions_io[i] += 1;
+    if (lens_io) lens_io[i] += 1;
   }
   __syncthreads();                       // a single block (rows <= 1024): every thread has read `step`
   if (threadIdx.x == 0) *step_io = step + 1;
@@ -394,13 +395,13 @@ int tq_argmax_rows(tq_ctx* ctx, const float* x_dev, size_t slices, size_t rows, 
 }
 
 int tq_generate_advance(tq_ctx* ctx, const int* chosen_dev, size_t rows, int* tokens_io_dev, int* positions_io_dev,
-                        int* out_tokens_dev, size_t out_ld, int* step_io_dev) {
+                        int* out_tokens_dev, size_t out_ld, int* step_io_dev, int* lens_io_dev) {
   if (int st = bind(ctx)) return st;
   if (rows == 0) return TQ_OK;
   TQ_REQUIRE(ctx, chosen_dev && tokens_io_dev && positions_io_dev && out_tokens_dev && step_io_dev, "tq_generate_advance: null pointer");
   TQ_REQUIRE(ctx, rows <= 1024, "tq_generate_advance: at most 1024 sequences");
   TQ_CUDA(ctx, launch_k(ctx, generate_advance_kernel, dim3(1), dim3(1024), 0, chosen_dev, (int)rows, tokens_io_dev,
-                        positions_io_dev, out_tokens_dev, (int)out_ld, step_io_dev));
+                        positions_io_dev, out_tokens_dev, (int)out_ld, step_io_dev, lens_io_dev));
   return TQ_OK;
 }
 

@@ -92,24 +92,34 @@ class LlamaModel:
         self.dev._check(self.dev._L.tq_llama_decode(C.c_void_p(self.handle), C.c_void_p(token_ids.ptr),
                                                     C.c_void_p(positions.ptr), batch, max_len, C.c_void_p(logits.ptr)))
 
-    def generate_greedy(self, prompts, n_new: int, comm_world: int = 1) -> np.ndarray:
-        """``generate`` with ``SamplingConfig::greedy()`` (crates/tang-infer/src/sampling.rs:229-256) for a batch
-        of equal-length prompts: the prompt is fed token by token through the decode step, then decode ->
-        first-maximum argmax -> advance is captured once as a CUDA graph and replayed `n_new` times; the logits
-        never leave the device.  Returns int32 [batch, n_new] (the caller cuts at its stop token: greedy choices
-        do not depend on what follows them)."""
+    def generate(self, prompts, n_new: int, sampling=None, seed: int = 42, comm_world: int = 1) -> np.ndarray:
+        """``generate`` (crates/tang-infer/src/sampling.rs:229-256) for a batch of equal-length prompts.  The prompt
+        is fed token by token through the decode step; then decode -> ``Sampler::sample`` -> advance is captured
+        once as a CUDA graph and replayed `n_new` times, the logits never leaving the device.  `sampling` is a
+        ``SamplerConfig`` (None or temperature 0: greedy, the first maximum); every sequence owns an LCG seeded
+        with `seed` (as ``Sampler::with_seed`` per call of ``generate``); the repetition penalty sees the prompt and
+        everything generated so far.  Returns int32 [batch, n_new]; the caller cuts at its stop token (what is
+        drawn before a stop token does not depend on what follows)."""
+        from .device import SamplerConfig
+
         dev, L = self.dev, self.dev._L
         prompts = np.asarray(prompts, np.int32)
         B, P = prompts.shape
         if P < 1 or n_new < 1:
-            raise _lib.TangqError(_lib.TQ_EINVAL, "generate_greedy: need at least one prompt token and one new token")
+            raise _lib.TangqError(_lib.TQ_EINVAL, "generate: need at least one prompt token and one new token")
         if P + n_new > self.cfg.max_seq:
-            raise _lib.TangqError(_lib.TQ_EINVAL, "generate_greedy: prompt + new tokens exceed max_seq")
-        vocab = self.cfg.vocab
+            raise _lib.TangqError(_lib.TQ_EINVAL, "generate: prompt + new tokens exceed max_seq")
+        cfg = sampling if sampling is not None else SamplerConfig(0.0, 0, 1.0, 1.0)
+        vocab, ld = self.cfg.vocab, P + n_new
         logits = dev.alloc(B * vocab, _lib.F32)
         tok, pos = dev.alloc(B, _lib.I32), dev.alloc(B, _lib.I32)
-        chosen, step = dev.alloc(B, _lib.I32), dev.upload(np.zeros(1, np.int32), _lib.I32)
-        out = dev.upload(np.zeros(B * n_new, np.int32), _lib.I32)
+        chosen = dev.alloc(B, _lib.I32)
+        step = dev.upload(np.full(1, P, np.int32), _lib.I32)            # column of the history the next token goes to
+        hist = np.zeros((B, ld), np.int32)
+        hist[:, :P] = prompts
+        hist_d = dev.upload(hist, _lib.I32)                             # prompt + generated tokens: the penalty's past
+        lens = dev.upload(np.full(B, P, np.int32), _lib.I32)
+        rng = dev.upload(np.full(B, seed, np.uint64).view(np.float64), _lib.F64)
         for p in range(P - 1):                      # all prompt tokens but the last: fill the cache
             dev.upload_into(tok, prompts[:, p].copy())
             dev.upload_into(pos, np.full(B, p, np.int32))
@@ -119,9 +129,10 @@ class LlamaModel:
 
         def one():
             self.decode(tok, pos, B, P + n_new, logits)
-            dev._check(L.tq_argmax_rows(dev._ctx, C.c_void_p(logits.ptr), comm_world, B, vocab // comm_world, C.c_void_p(chosen.ptr)))
+            dev._check(L.tq_sample(dev._ctx, C.c_void_p(logits.ptr), comm_world, B, vocab // comm_world, C.byref(cfg),
+                                   C.c_void_p(rng.ptr), C.c_void_p(hist_d.ptr), C.c_void_p(lens.ptr), ld, C.c_void_p(chosen.ptr)))
             dev._check(L.tq_generate_advance(dev._ctx, C.c_void_p(chosen.ptr), B, C.c_void_p(tok.ptr), C.c_void_p(pos.ptr),
-                                             C.c_void_p(out.ptr), n_new, C.c_void_p(step.ptr)))
+                                             C.c_void_p(hist_d.ptr), ld, C.c_void_p(step.ptr), C.c_void_p(lens.ptr)))
         one()                                       # eager once (workspaces), then the remaining steps from a graph
         if n_new > 1:
             dev.sync()
@@ -133,7 +144,11 @@ class LlamaModel:
             dev.sync()
             graph.free()
         dev.sync()
-        return out.to_vec().reshape(B, n_new)
+        return hist_d.to_vec().reshape(B, ld)[:, P:].copy()
+
+    def generate_greedy(self, prompts, n_new: int, comm_world: int = 1) -> np.ndarray:
+        """``generate`` with ``SamplingConfig::greedy()``."""
+        return self.generate(prompts, n_new, None, comm_world=comm_world)
 
     def destroy(self) -> None:
         if self.handle:
