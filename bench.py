@@ -609,6 +609,23 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
         del cache
         torch.cuda.empty_cache()
     out["mla_dsv3_decode"] = mla
+
+    # ---- prefill attention: one sequence, Llama-3-8B heads (32 query / 8 KV heads of 128), causal chunk of q_len positions
+    pre = []
+    for q_len in (512, 2048):
+        nh, nkv, hd = 32, 8, 128
+        q = bf16((1, q_len, nh * hd))
+        kc, vc = bf16((1, q_len, nkv * hd)), bf16((1, q_len, nkv * hd))
+        o = torch.empty((1, q_len, nh * hd), dtype=torch.bfloat16, device="cuda")
+        st0 = dev.upload(np.zeros(1, np.int32), tb.I32)
+
+        def fn():
+            dev._check(L_.tq_gqa_prefill(dev._ctx, C.c_void_p(q.data_ptr()), C.c_void_p(kc.data_ptr()), C.c_void_p(vc.data_ptr()),
+                                         C.c_void_p(st0.ptr), 1, q_len, nh, nkv, hd, q_len * nkv * hd, C.c_void_p(o.data_ptr()), tb.BF16))
+        ms = _time_ms(torch, stream, dev, fn, 10, 3)
+        flops = 4.0 * nh * hd * q_len * (q_len + 1) / 2          # QK^T and PV over the causal half
+        pre.append({"q_len": q_len, "us": ms * 1e3, "tflops": flops / ms / 1e9})
+    out["gqa_prefill_llama_heads"] = pre
     return out
 
 

@@ -228,6 +228,14 @@ TQ_API int tq_gqa_decode(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev
 TQ_API int tq_gqa_decode_noalloc(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev,
                                  const int* lens_dev, size_t batch, size_t n_heads, size_t n_kv_heads,
                                  size_t head_dim, size_t seq_stride, size_t max_len, void* out_dev, int out_dtype);
+/* The same attention for a chunk of q_len new positions per sequence (prefill; kv_attention with q_len > 1,
+ * device.rs:161-180): q bf16 [batch][q_len][n_heads*128]; query i of sequence b attends cache positions
+ * 0 .. cache_start[b] + i, the chunk's own K/V rows being in the cache already; out [batch][q_len][n_heads*128]
+ * bf16 or f32.  Probabilities enter the tensor core as bf16 (results to the bf16 bar).  n_heads/n_kv_heads in
+ * {1, 2, 4, 8}. */
+TQ_API int tq_gqa_prefill(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev,
+                          const int* cache_start_dev, size_t batch, size_t q_len, size_t n_heads, size_t n_kv_heads,
+                          size_t head_dim, size_t seq_stride, void* out_dev, int out_dtype);
 
 /* ---- collectives -----------------------------------------------------------------------------
  * NCCL over NVLink at the shard boundaries (the reference's only collective is a star sum over

@@ -61,6 +61,7 @@ PROTOTYPES = {
     "tq_generate_advance": (_i, [_p, _p, _sz, _p, _p, _p, _sz, _p, _p]),
     "tq_kv_attention": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p]),
     "tq_gqa_decode": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),
+    "tq_gqa_prefill": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),
     "tq_gqa_decode_noalloc": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p, _i]),
     "tq_comm_unique_id": (_i, [_p]),
     "tq_comm_create": (_i, [_p, _p, _i, _i, _pp]),

@@ -267,6 +267,191 @@ __global__ void __launch_bounds__(kHD) gqa_combine_kernel(const float* part_o, c
   else reinterpret_cast<__nv_bfloat16*>(out)[bh * kHD + d] = __float2bfloat16_rn(v);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Causal GQA attention for a chunk of q_len new positions per sequence (prefill, q_len > 1 of
+// ComputeDevice::kv_attention, crates/tang-compute/src/device.rs:161-180; cpu.rs:257-315): query i of sequence b
+// attends cache positions 0 .. cache_start[b] + i.  bf16 q / K / V, f32 online softmax, bf16 probabilities into
+// the tensor core (mma.sync m16n8k16).  A CTA owns 64 (position, head-of-the-group) rows of one KV head -- so the
+// K/V tiles it streams (cp.async, double-buffered, 64 keys each) serve every query head of the group -- and each
+// of its four warps 16 of those rows against all 64 keys of a tile.
+// ---------------------------------------------------------------------------------------------
+struct PrefillParams {
+  const __nv_bfloat16* q;        // [B][q_len][n_heads*kHD]
+  const __nv_bfloat16* k_cache;  // [B][max_seq][n_kv*kHD], the chunk's own K/V already appended
+  const __nv_bfloat16* v_cache;
+  const int* cache_start;        // [B] positions in the cache before this chunk
+  size_t seq_stride;
+  int q_len, n_heads, n_kv, group;
+  float scale;
+  void* out;                     // [B][q_len][n_heads*kHD]
+  int out_f32;
+};
+
+__global__ void __launch_bounds__(kAttnThreads) gqa_prefill_kernel(const PrefillParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* k_s = smem;
+  uint8_t* v_s = smem + 2 * kTileKeys * kRowBytes;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int pos_per_cta = 64 / p.group;
+  const int pos0 = blockIdx.x * pos_per_cta;                     // first query position of this CTA
+  const int start = p.cache_start[b];
+  const int last_pos = min(p.q_len, pos0 + pos_per_cta) - 1;     // last live query position
+  const int k_end = start + last_pos + 1;                        // keys this CTA needs (causal)
+  const int n_tiles = (k_end + kTileKeys - 1) / kTileKeys;
+  const size_t row_elems = (size_t)p.n_kv * kHD;
+  const __nv_bfloat16* kbase = p.k_cache + (size_t)b * p.seq_stride + (size_t)kvh * kHD;
+  const __nv_bfloat16* vbase = p.v_cache + (size_t)b * p.seq_stride + (size_t)kvh * kHD;
+
+  // this lane's two rows: r = 16*warp + g and + 8 -> (position, head)
+  int qpos[2];
+  bool live[2];
+  uint32_t qa[8][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = 16 * warp + g + 8 * h;
+    const int pl = r / p.group, head = kvh * p.group + r % p.group;
+    qpos[h] = pos0 + pl;
+    live[h] = qpos[h] < p.q_len;
+    const __nv_bfloat16* qrow = p.q + (((size_t)b * p.q_len + (live[h] ? qpos[h] : 0)) * p.n_heads + head) * kHD;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][h] = live[h] ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t) : 0u;          // a0 / a1
+      qa[ks][2 + h] = live[h] ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t + 8) : 0u;  // a2 / a3
+    }
+  }
+
+  auto load_tile = [&](int tile, int buf) {
+    const int key0 = tile * kTileKeys;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int c = threadIdx.x + i * kAttnThreads;
+      const int which = c >> 10, rc = c & 1023, row = rc >> 4, ch = rc & 15;
+      const int key = key0 + row;
+      const bool valid = key < k_end;
+      const __nv_bfloat16* src = (which ? vbase : kbase) + (size_t)(valid ? key : 0) * row_elems + ch * 8;
+      uint8_t* dst = (which ? v_s : k_s) + ((size_t)buf * kTileKeys + row) * kRowBytes + ch * 16;
+      cp_async16(dst, src, valid);
+    }
+    cp_async_commit();
+  };
+
+  float o[16][4];   // [d-tile][row g: d 2t, 2t+1 | row g+8: d 2t, 2t+1]
+#pragma unroll
+  for (int dn = 0; dn < 16; ++dn) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.f;
+  float m_run[2] = {-FLT_MAX, -FLT_MAX}, l_run[2] = {0.f, 0.f};
+
+  if (n_tiles > 0) load_tile(0, 0);
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int buf = tile & 1;
+    if (tile + 1 < n_tiles) {
+      load_tile(tile + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key0 = tile * kTileKeys;
+    const uint8_t* kt = k_s + (size_t)buf * kTileKeys * kRowBytes;
+    const uint8_t* vt = v_s + (size_t)buf * kTileKeys * kRowBytes;
+    // ---- S = Q K^T for 16 rows x 64 keys
+    float sacc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+      const uint8_t* krow = kt + (size_t)(8 * nt + g) * kRowBytes + 4 * t;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks + 16);
+        mma_bf16_16816(sacc[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      }
+    }
+    // ---- causal mask, online softmax (rows g and g+8; a row's 64 scores live in its four lanes)
+    float mx[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int h = c >> 1, key = key0 + 8 * nt + 2 * t + (c & 1);
+        const bool ok = live[h] && key <= start + qpos[h];
+        const float v = ok ? sacc[nt][c] * p.scale : -FLT_MAX;
+        sacc[nt][c] = v;
+        mx[h] = fmaxf(mx[h], v);
+      }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      alpha[h] = exp2f((m_run[h] - m_new) * kLog2e);
+      m_run[h] = m_new;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int h = c >> 1;
+        const float pv = sacc[nt][c] == -FLT_MAX ? 0.f : exp2f((sacc[nt][c] - m_run[h]) * kLog2e);
+        sacc[nt][c] = pv;
+        psum[h] += pv;
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + psum[h];
+#pragma unroll
+    for (int dn = 0; dn < 16; ++dn) {
+      o[dn][0] *= alpha[0];
+      o[dn][1] *= alpha[0];
+      o[dn][2] *= alpha[1];
+      o[dn][3] *= alpha[1];
+    }
+    // ---- O += P V, 16 keys per k-step; the S accumulator layout is the A fragment layout
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t a0 = pack_bf16(sacc[2 * j][0], sacc[2 * j][1]);
+      const uint32_t a1 = pack_bf16(sacc[2 * j][2], sacc[2 * j][3]);
+      const uint32_t a2 = pack_bf16(sacc[2 * j + 1][0], sacc[2 * j + 1][1]);
+      const uint32_t a3 = pack_bf16(sacc[2 * j + 1][2], sacc[2 * j + 1][3]);
+      const uint8_t* vrow = vt + (size_t)(16 * j + (lane & 7) + 8 * ((lane >> 3) & 1)) * kRowBytes + 16 * (lane >> 4);
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, vrow + 32 * dp);
+        mma_bf16_16816(o[2 * dp], a0, a1, a2, a3, vb[0], vb[1]);
+        mma_bf16_16816(o[2 * dp + 1], a0, a1, a2, a3, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();
+  }
+  // ---- normalise and store
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!live[h]) continue;
+    const int r = 16 * warp + g + 8 * h;
+    const int head = kvh * p.group + r % p.group;
+    const float inv = l_run[h] > 0.f ? 1.0f / l_run[h] : 0.f;
+    const size_t oi = (((size_t)b * p.q_len + qpos[h]) * p.n_heads + head) * kHD;
+#pragma unroll
+    for (int dn = 0; dn < 16; ++dn) {
+      const float v0 = o[dn][2 * h] * inv, v1 = o[dn][2 * h + 1] * inv;
+      if (p.out_f32) {
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + oi + 8 * dn + 2 * t) = make_float2(v0, v1);
+      } else {
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) + oi + 8 * dn + 2 * t) = pack_bf16(v0, v1);
+      }
+    }
+  }
+}
+
 // ComputeDevice::kv_attention on f32 buffers (cpu.rs:257-315): one warp per (query, head); each
 // lane owns head_dim/32 output columns; positions are visited in order with the reference's
 // running-max update, dot products reduced across the warp.
@@ -377,6 +562,42 @@ int tq_gqa_decode(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, const
   TQ_REQUIRE(ctx, max_len > 0, "tq_gqa_decode: max_len must bound the sequence lengths");
   return launch_gqa_decode(ctx, q_dev, k_cache_dev, v_cache_dev, lens_dev, (int)batch, (int)n_heads, (int)n_kv_heads,
                            (int)head_dim, seq_stride, (int)max_len, out_dev, out_dtype);
+}
+
+int tq_gqa_prefill(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev, const int* cache_start_dev,
+                   size_t batch, size_t q_len, size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t seq_stride,
+                   void* out_dev, int out_dtype) {
+  if (int st = bind(ctx)) return st;
+  if (batch == 0 || q_len == 0) return TQ_OK;
+  TQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && cache_start_dev && out_dev, "tq_gqa_prefill: null pointer");
+  TQ_REQUIRE(ctx, head_dim == (size_t)kHD, "tq_gqa_prefill: head_dim must be %d", kHD);
+  const size_t group = n_kv_heads ? n_heads / n_kv_heads : 0;
+  TQ_REQUIRE(ctx, n_kv_heads > 0 && n_heads % n_kv_heads == 0 && (group == 1 || group == 2 || group == 4 || group == 8),
+             "tq_gqa_prefill: n_heads/n_kv_heads must be 1, 2, 4 or 8");
+  TQ_REQUIRE(ctx, out_dtype == TQ_BF16 || out_dtype == TQ_F32, "tq_gqa_prefill: out must be bf16 or f32");
+  PrefillParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q_dev);
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache_dev);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache_dev);
+  p.cache_start = cache_start_dev;
+  p.seq_stride = seq_stride;
+  p.q_len = (int)q_len;
+  p.n_heads = (int)n_heads;
+  p.n_kv = (int)n_kv_heads;
+  p.group = (int)group;
+  p.scale = 1.0f / sqrtf((float)head_dim);
+  p.out = out_dev;
+  p.out_f32 = out_dtype == TQ_F32;
+  const size_t smem = 4 * (size_t)kTileKeys * kRowBytes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    TQ_CUDA(ctx, cudaFuncSetAttribute(gqa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set = true;
+  }
+  const size_t pos_per_cta = 64 / group;
+  dim3 grid((unsigned)((q_len + pos_per_cta - 1) / pos_per_cta), (unsigned)n_kv_heads, (unsigned)batch);
+  TQ_CUDA(ctx, launch_k(ctx, gqa_prefill_kernel, grid, dim3(kAttnThreads), smem, p));
+  return TQ_OK;
 }
 
 int tq_kv_attention(tq_ctx* ctx, const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,

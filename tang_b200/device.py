@@ -422,6 +422,18 @@ def _add_ops(cls):
                                           C.c_void_p(out.ptr), out_dtype))
         return out
 
+    def gqa_prefill(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, cache_start, batch: int, q_len: int, n_heads: int,
+                    n_kv_heads: int, head_dim: int, seq_stride: int, out_dtype: int = BF16) -> Buffer:
+        """``kv_attention`` with q_len > 1 (device.rs:161-180) over bf16 caches, batched: query i of sequence b attends
+        positions 0 .. cache_start[b] + i (``tq_gqa_prefill``)."""
+        cb = cache_start if isinstance(cache_start, Buffer) else self.upload(np.asarray(cache_start, np.int32), _lib.I32)
+        out = self.alloc(batch * q_len * n_heads * head_dim, out_dtype)
+        self._check(self._L.tq_gqa_prefill(self._ctx, C.c_void_p(q.ptr), C.c_void_p(k_cache.ptr), C.c_void_p(v_cache.ptr),
+                                           C.c_void_p(cb.ptr), batch, q_len, n_heads, n_kv_heads, head_dim, seq_stride,
+                                           C.c_void_p(out.ptr), out_dtype))
+        out._keep = cb
+        return out
+
     def concat_rows(self, parts) -> QBuffer:
         arr = (C.c_void_p * len(parts))(*[p.handle for p in parts])
         h = C.c_void_p()
@@ -429,7 +441,7 @@ def _add_ops(cls):
         return self._wrap_q(h)
 
     for f in (rms_norm, rms_norm_residual, rope_tables, rope_forward, swiglu_fused, embedding, kv_attention, gqa_decode,
-              concat_rows):
+              gqa_prefill, concat_rows):
         setattr(cls, f.__name__, f)
 
 

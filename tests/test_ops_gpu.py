@@ -114,3 +114,41 @@ def test_gqa_decode_bf16_cache(dev, orc, B, nh, nkv, lens):
     out16 = dev.gqa_decode(dev.upload(qb, tb.BF16), dev.upload(kb, tb.BF16), dev.upload(vb, tb.BF16), np.array(lens, np.int32),
                            B, nh, nkv, hd, max_seq * kv_dim, max(lens)).to_vec().reshape(B, nh * hd)
     assert np.array_equal(out16, bf16_round(out)[0])
+
+
+@pytest.mark.parametrize("B,nh,nkv,q_len,starts", [(2, 8, 2, 50, [0, 37]),        # group 4, ragged chunk, a cached prefix
+                                                  (1, 4, 4, 64, [0]),            # no grouping, exactly one CTA tile of positions
+                                                  (1, 8, 1, 33, [100]),          # group 8 (8 positions per CTA)
+                                                  (3, 4, 2, 130, [0, 5, 63]),    # several query tiles, tile-boundary prefixes
+                                                  (1, 32, 8, 512, [0])])         # Llama-3-8B heads, a 512-token chunk
+def test_gqa_prefill_causal_chunk(dev, orc, B, nh, nkv, q_len, starts):
+    """kv_attention with q_len > 1 (device.rs:161-180; cpu.rs:257-315) on bf16 caches: query i attends positions
+    0 .. cache_start + i.  Probabilities pass through bf16 on their way into the tensor core, so the bar is the
+    bf16 one, measured against max(|ref|, rms)."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(B * 1000 + nh + q_len)
+    hd = 128
+    max_seq = max(starts) + q_len + 3
+    kv_dim = nkv * hd
+    qb, qf = bf16_round(rng.standard_normal((B, q_len, nh * hd)).astype(np.float32))
+    kb, kf = bf16_round(rng.standard_normal((B, max_seq, kv_dim)).astype(np.float32))
+    vb, vf = bf16_round(rng.standard_normal((B, max_seq, kv_dim)).astype(np.float32))
+    out = dev.gqa_prefill(dev.upload(qb, tb.BF16), dev.upload(kb, tb.BF16), dev.upload(vb, tb.BF16), np.array(starts, np.int32),
+                          B, q_len, nh, nkv, hd, max_seq * kv_dim, out_dtype=tb.F32)
+    dev.sync()
+    got = out.to_vec().reshape(B, q_len, nh * hd)
+    pick = range(q_len) if q_len <= 64 else sorted(set([0, 1, 15, 16, 63, 64, q_len // 2, q_len - 2, q_len - 1]))
+    for b in range(B):
+        for i in pick:
+            n = starts[b] + i + 1
+            want = orc.attention_decode_f64(qf[b, i], kf[b, :n], vf[b, :n], n, nh, nkv, hd)
+            assert rel_err(got[b, i], want, floor_frac=1.0) < 1e-2, (b, i)
+    out16 = dev.gqa_prefill(dev.upload(qb, tb.BF16), dev.upload(kb, tb.BF16), dev.upload(vb, tb.BF16), np.array(starts, np.int32),
+                            B, q_len, nh, nkv, hd, max_seq * kv_dim).to_vec().reshape(B, q_len, nh * hd)
+    assert np.array_equal(out16, bf16_round(got)[0])
+    # a chunk of one position is the decode case
+    dec = dev.gqa_decode(dev.upload(np.ascontiguousarray(qb[:, 0]), tb.BF16), dev.upload(kb, tb.BF16), dev.upload(vb, tb.BF16),
+                         np.array([s + 1 for s in starts], np.int32), B, nh, nkv, hd, max_seq * kv_dim, max(starts) + 1,
+                         out_dtype=tb.F32).to_vec().reshape(B, nh * hd)
+    assert rel_err(got[:, 0], dec, floor_frac=1.0) < 1e-2
