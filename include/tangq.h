@@ -293,6 +293,13 @@ TQ_API int tq_llama_hidden(tq_llama* model, float** hidden_dev);
  * vocabulary slices).  Asynchronous; capturable once run eagerly. */
 TQ_API int tq_llama_decode(tq_llama* model, const int* token_ids_dev, const int* positions_dev, size_t batch,
                            size_t max_len, float* logits_dev);
+/* The same step for a chunk of q_len new tokens per sequence (prompt processing): token_ids [batch][q_len],
+ * sequence b's chunk starts at position cache_start[b] (its earlier positions are in the cache already).
+ * Appends the chunk's K/V rows, runs causal attention over cache + chunk (tq_gqa_prefill) and the linear layers
+ * on all batch*q_len rows at once; logits [batch, vocab] (gathered as for tq_llama_decode) are those of each
+ * sequence's LAST chunk position.  Workspaces grow on first use: not inside a graph capture. */
+TQ_API int tq_llama_prefill(tq_llama* model, const int* token_ids_dev, const int* cache_start_dev, size_t batch, size_t q_len,
+                            float* logits_dev);
 
 /* ---- mixture-of-experts FFN -------------------------------------------------------------------
  * No counterpart in the reference (it has no MoE); composed from its primitives.  Router: logits =

@@ -79,6 +79,7 @@ PROTOTYPES = {
     "tq_llama_kv_cache": (_i, [_p, _sz, _pp, _pp, C.POINTER(_sz)]),
     "tq_llama_hidden": (_i, [_p, _pp]),
     "tq_llama_decode": (_i, [_p, _p, _p, _sz, _sz, _p]),
+    "tq_llama_prefill": (_i, [_p, _p, _p, _sz, _sz, _p]),
     "tq_moe_router": (_i, [_p, _p, _p, _sz, _sz, _sz, _sz, _i, _p, _p, _p]),
     "tq_moe_create": (_i, [_p, _p, _p, _p, _p, _p, _p, _pp]),
     "tq_moe_destroy": (_i, [_p]),

@@ -28,7 +28,7 @@ extern "C" int tq_comm_rank(const tq_comm*);
 namespace tq {
 int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const float* sin_t, const int* positions, int B,
                     int n_heads, int n_kv, int hd, int max_seq, void* q_out, void* k_cache, void* v_cache,
-                    size_t seq_stride);
+                    size_t seq_stride, int q_len);
 int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, const int* lens, int B,
                       int n_heads, int n_kv, int head_dim, size_t seq_stride, int max_len, void* out, int out_dtype);
 
@@ -61,6 +61,10 @@ struct tq_llama {
   float *h = nullptr, *delta = nullptr, *qkv = nullptr, *gu = nullptr, *logits_l = nullptr;
   __nv_bfloat16 *xn = nullptr, *qb = nullptr, *attn = nullptr, *act = nullptr;
   int* lens = nullptr;
+  // prefill workspaces (rows = sequences x chunk length), grown on demand by tq_llama_prefill
+  size_t pre_rows = 0;
+  float *p_h = nullptr, *p_delta = nullptr, *p_qkv = nullptr, *p_gu = nullptr;
+  __nv_bfloat16 *p_xn = nullptr, *p_qb = nullptr, *p_attn = nullptr, *p_act = nullptr, *p_last = nullptr;
   std::vector<void*> owned;
 };
 
@@ -261,7 +265,7 @@ int tq_llama_decode(tq_llama* m, const int* token_ids_dev, const int* positions_
                         L.attn_norm, TQ_BF16, B, d, c.eps, m->xn, TQ_BF16, have_delta ? m->h : nullptr));
     TQ_STEP(tq_qlinear(ctx, L.wqkv, m->xn, TQ_BF16, d, B, m->qkv, TQ_F32, q_dim + 2 * kv_dim, nullptr));
     TQ_STEP(launch_qkv_post(ctx, m->qkv, m->cos_t, m->sin_t, positions_dev, B, m->heads_l, m->kv_l, (int)hd, (int)c.max_seq,
-                            m->qb, L.k_cache, L.v_cache, seq_stride));
+                            m->qb, L.k_cache, L.v_cache, seq_stride, 1));
     TQ_STEP(launch_gqa_decode(ctx, m->qb, L.k_cache, L.v_cache, m->lens, B, m->heads_l, m->kv_l, (int)hd, seq_stride,
                               (int)max_len, m->attn, TQ_BF16));
     TQ_STEP(tq_qlinear(ctx, L.wo, m->attn, TQ_BF16, q_dim, B, m->delta, TQ_F32, d, nullptr));
@@ -282,6 +286,76 @@ int tq_llama_decode(tq_llama* m, const int* token_ids_dev, const int* positions_
     // column-parallel head: this rank's vocabulary slice, gathered rank-major: logits_dev is
     // [tp][B][vocab/tp]
     TQ_STEP(tq_qlinear(ctx, m->lm_head, m->xn, TQ_BF16, d, B, m->logits_l, TQ_F32, m->vocab_l, nullptr));
+    TQ_STEP(tq_all_gather(ctx, m->comm, m->logits_l, logits_dev, (size_t)B * m->vocab_l * sizeof(float)));
+  }
+#undef TQ_STEP
+  return TQ_OK;
+}
+
+int tq_llama_prefill(tq_llama* m, const int* token_ids_dev, const int* cache_start_dev, size_t batch, size_t q_len,
+                     float* logits_dev) {
+  if (!m) return TQ_EINVAL;
+  tq_ctx* ctx = m->ctx;
+  if (int st = bind(ctx)) return st;
+  const tq_llama_config& c = m->cfg;
+  TQ_REQUIRE(ctx, batch > 0 && batch <= c.max_batch, "tq_llama_prefill: batch must be 1..%u", c.max_batch);
+  TQ_REQUIRE(ctx, q_len > 0 && q_len <= c.max_seq, "tq_llama_prefill: chunk length must be 1..max_seq");
+  TQ_REQUIRE(ctx, token_ids_dev && cache_start_dev && logits_dev, "tq_llama_prefill: null pointer");
+  TQ_REQUIRE(ctx, m->lm_head != nullptr, "tq_llama_prefill: head weights not set");
+  for (auto& L : m->layers) TQ_REQUIRE(ctx, L.wqkv != nullptr, "tq_llama_prefill: a layer has no weights");
+  const size_t R = batch * q_len, d = c.d_model, hd = c.head_dim;
+  const size_t q_dim = (size_t)m->heads_l * hd, kv_dim = (size_t)m->kv_l * hd;
+  const size_t seq_stride = (size_t)c.max_seq * kv_dim;
+  if (R > m->pre_rows) {   // (re)size the chunk's workspaces
+    TQ_REQUIRE(ctx, !ctx->capturing, "tq_llama_prefill: workspaces must be sized before graph capture (run once eagerly)");
+    TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    void** slots[] = {(void**)&m->p_h, (void**)&m->p_delta, (void**)&m->p_qkv, (void**)&m->p_gu, (void**)&m->p_xn,
+                      (void**)&m->p_qb, (void**)&m->p_attn, (void**)&m->p_act, (void**)&m->p_last};
+    const size_t bytes[] = {R * d * 4, R * d * 4, R * (q_dim + 2 * kv_dim) * 4, R * 2 * m->ffn_l * 4, R * d * 2,
+                            R * q_dim * 2, R * q_dim * 2, R * (size_t)m->ffn_l * 2, (size_t)c.max_batch * d * 2};
+    for (int i = 0; i < 9; ++i) {
+      if (*slots[i]) {
+        for (auto& o : m->owned)
+          if (o == *slots[i]) o = nullptr;
+        cudaFree(*slots[i]);
+        *slots[i] = nullptr;
+      }
+      if (int st = dev_alloc(m, slots[i], bytes[i])) return st;
+    }
+    m->pre_rows = R;
+  }
+  int st;
+#define TQ_STEP(expr) \
+  if ((st = (expr)) != TQ_OK) return st;
+  const int Ri = (int)R, B = (int)batch;
+  TQ_STEP(tq_embedding(ctx, m->embed, TQ_BF16, token_ids_dev, R, d, c.vocab, m->p_h, TQ_F32));
+  bool have_delta = false;
+  for (size_t l = 0; l < m->layers.size(); ++l) {
+    const LlamaLayerW& L = m->layers[l];
+    TQ_STEP(tq_rms_norm(ctx, have_delta ? (const void*)m->p_delta : (const void*)m->p_h, TQ_F32, have_delta ? m->p_h : nullptr,
+                        L.attn_norm, TQ_BF16, R, d, c.eps, m->p_xn, TQ_BF16, have_delta ? m->p_h : nullptr));
+    TQ_STEP(tq_qlinear(ctx, L.wqkv, m->p_xn, TQ_BF16, d, R, m->p_qkv, TQ_F32, q_dim + 2 * kv_dim, nullptr));
+    TQ_STEP(launch_qkv_post(ctx, m->p_qkv, m->cos_t, m->sin_t, cache_start_dev, Ri, m->heads_l, m->kv_l, (int)hd, (int)c.max_seq,
+                            m->p_qb, L.k_cache, L.v_cache, seq_stride, (int)q_len));
+    TQ_STEP(tq_gqa_prefill(ctx, m->p_qb, L.k_cache, L.v_cache, cache_start_dev, batch, q_len, m->heads_l, m->kv_l, hd, seq_stride,
+                           m->p_attn, TQ_BF16));
+    TQ_STEP(tq_qlinear(ctx, L.wo, m->p_attn, TQ_BF16, q_dim, R, m->p_delta, TQ_F32, d, nullptr));
+    TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->p_delta, R * d));
+    TQ_STEP(tq_rms_norm(ctx, m->p_delta, TQ_F32, m->p_h, L.ffn_norm, TQ_BF16, R, d, c.eps, m->p_xn, TQ_BF16, m->p_h));
+    TQ_STEP(tq_qlinear(ctx, L.wgu, m->p_xn, TQ_BF16, d, R, m->p_gu, TQ_F32, 2 * (size_t)m->ffn_l, nullptr));
+    TQ_STEP(tq_swiglu(ctx, m->p_gu, m->p_gu + m->ffn_l, TQ_F32, 2 * (size_t)m->ffn_l, R, m->ffn_l, m->p_act, TQ_BF16));
+    TQ_STEP(tq_qlinear(ctx, L.wdown, m->p_act, TQ_BF16, m->ffn_l, R, m->p_delta, TQ_F32, d, nullptr));
+    TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->p_delta, R * d));
+    have_delta = true;
+  }
+  TQ_STEP(tq_rms_norm(ctx, m->p_delta, TQ_F32, m->p_h, m->final_norm, TQ_BF16, R, d, c.eps, m->p_xn, TQ_BF16, m->p_h));
+  // the LM head only sees each sequence's last row
+  TQ_CUDA(ctx, cudaMemcpy2DAsync(m->p_last, d * 2, m->p_xn + (q_len - 1) * d, q_len * d * 2, d * 2, batch, cudaMemcpyDeviceToDevice,
+                                 ctx->stream));
+  if (m->tp == 1) {
+    TQ_STEP(tq_qlinear(ctx, m->lm_head, m->p_last, TQ_BF16, d, B, logits_dev, TQ_F32, c.vocab, nullptr));
+  } else {
+    TQ_STEP(tq_qlinear(ctx, m->lm_head, m->p_last, TQ_BF16, d, B, m->logits_l, TQ_F32, m->vocab_l, nullptr));
     TQ_STEP(tq_all_gather(ctx, m->comm, m->logits_l, logits_dev, (size_t)B * m->vocab_l * sizeof(float)));
   }
 #undef TQ_STEP

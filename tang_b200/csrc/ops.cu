@@ -176,27 +176,29 @@ __global__ void embedding_kernel(const void* weight, int w_dt, const int* ids, s
 //   qkv [B, (n_heads + 2*n_kv) * hd] f32  ->  q_out [B, n_heads*hd] bf16 (rotated),
 //   k_cache[b, pos_b, :] = bf16(rot(k)),  v_cache[b, pos_b, :] = bf16(v).
 // Cache layout per sequence is [max_seq, n_kv*hd] (crates/tang-infer/src/kv_cache.rs:12-24).
+// With q_len > 1 (prefill) the rows are [sequence][i] and row i of sequence b sits at position positions[b] + i.
 __global__ void qkv_post_kernel(const float* qkv, const float* cos_t, const float* sin_t, const int* positions, int B,
                                 int n_heads, int n_kv, int hd, int max_seq, __nv_bfloat16* q_out,
-                                __nv_bfloat16* k_cache, __nv_bfloat16* v_cache, size_t seq_stride) {
+                                __nv_bfloat16* k_cache, __nv_bfloat16* v_cache, size_t seq_stride, int q_len) {
   pdl_wait();
   pdl_launch_dependents();
   const int half = hd / 2;
   const int pairs_per_row = (n_heads + 2 * n_kv) * half;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)B * pairs_per_row) return;
-  const int b = (int)(idx / pairs_per_row);
+  const int row = (int)(idx / pairs_per_row);   // B counts rows (sequences x q_len)
   const int pr = (int)(idx % pairs_per_row);
   const int head = pr / half, i = pr % half;
-  const int pos = positions[b];
-  const size_t src = (size_t)b * (n_heads + 2 * n_kv) * hd + (size_t)head * hd + 2 * i;
+  const int b = row / q_len;
+  const int pos = positions[b] + row % q_len;
+  const size_t src = (size_t)row * (n_heads + 2 * n_kv) * hd + (size_t)head * hd + 2 * i;
   const float x0 = qkv[src], x1 = qkv[src + 1];
   if (head < n_heads + n_kv) {
     const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
     const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
     const __nv_bfloat162 pk = __floats2bfloat162_rn(r0, r1);
     if (head < n_heads) {
-      *reinterpret_cast<__nv_bfloat162*>(q_out + (size_t)b * n_heads * hd + (size_t)head * hd + 2 * i) = pk;
+      *reinterpret_cast<__nv_bfloat162*>(q_out + (size_t)row * n_heads * hd + (size_t)head * hd + 2 * i) = pk;
     } else if (pos < max_seq) {
       const int kh = head - n_heads;
       *reinterpret_cast<__nv_bfloat162*>(k_cache + (size_t)b * seq_stride + (size_t)pos * n_kv * hd + (size_t)kh * hd + 2 * i) = pk;
@@ -210,11 +212,11 @@ __global__ void qkv_post_kernel(const float* qkv, const float* cos_t, const floa
 
 int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const float* sin_t, const int* positions, int B,
                     int n_heads, int n_kv, int hd, int max_seq, void* q_out, void* k_cache, void* v_cache,
-                    size_t seq_stride) {
+                    size_t seq_stride, int q_len) {
   const size_t n = (size_t)B * (n_heads + 2 * n_kv) * (hd / 2);
   TQ_CUDA(ctx, launch_k(ctx, qkv_post_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, qkv, cos_t, sin_t, positions, B,
                         n_heads, n_kv, hd, max_seq, static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
-                        static_cast<__nv_bfloat16*>(v_cache), seq_stride));
+                        static_cast<__nv_bfloat16*>(v_cache), seq_stride, q_len));
   return TQ_OK;
 }
 

@@ -92,9 +92,15 @@ class LlamaModel:
         self.dev._check(self.dev._L.tq_llama_decode(C.c_void_p(self.handle), C.c_void_p(token_ids.ptr),
                                                     C.c_void_p(positions.ptr), batch, max_len, C.c_void_p(logits.ptr)))
 
+    def prefill(self, token_ids: Buffer, cache_start: Buffer, batch: int, q_len: int, logits: Buffer) -> None:
+        """``model.forward(&tokens, cache, pos)`` for a chunk of `q_len` tokens per sequence (prompt processing): appends the
+        chunk to the cache and leaves the logits of each sequence's last chunk position; asynchronous."""
+        self.dev._check(self.dev._L.tq_llama_prefill(C.c_void_p(self.handle), C.c_void_p(token_ids.ptr), C.c_void_p(cache_start.ptr),
+                                                     batch, q_len, C.c_void_p(logits.ptr)))
+
     def generate(self, prompts, n_new: int, sampling=None, seed: int = 42, comm_world: int = 1) -> np.ndarray:
         """``generate`` (crates/tang-infer/src/sampling.rs:229-256) for a batch of equal-length prompts.  The prompt
-        is fed token by token through the decode step; then decode -> ``Sampler::sample`` -> advance is captured
+        goes through one prefill chunk (all tokens but the last); then decode -> ``Sampler::sample`` -> advance is captured
         once as a CUDA graph and replayed `n_new` times, the logits never leaving the device.  `sampling` is a
         ``SamplerConfig`` (None or temperature 0: greedy, the first maximum); every sequence owns an LCG seeded
         with `seed` (as ``Sampler::with_seed`` per call of ``generate``); the repetition penalty sees the prompt and
@@ -120,10 +126,9 @@ class LlamaModel:
         hist_d = dev.upload(hist, _lib.I32)                             # prompt + generated tokens: the penalty's past
         lens = dev.upload(np.full(B, P, np.int32), _lib.I32)
         rng = dev.upload(np.full(B, seed, np.uint64).view(np.float64), _lib.F64)
-        for p in range(P - 1):                      # all prompt tokens but the last: fill the cache
-            dev.upload_into(tok, prompts[:, p].copy())
-            dev.upload_into(pos, np.full(B, p, np.int32))
-            self.decode(tok, pos, B, P + n_new, logits)
+        if P > 1:                                   # all prompt tokens but the last: one prefill chunk fills the cache
+            self.prefill(dev.upload(np.ascontiguousarray(prompts[:, :P - 1]), _lib.I32), dev.upload(np.zeros(B, np.int32), _lib.I32),
+                         B, P - 1, logits)
         dev.upload_into(tok, prompts[:, P - 1].copy())
         dev.upload_into(pos, np.full(B, P - 1, np.int32))
 

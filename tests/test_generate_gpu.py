@@ -184,7 +184,8 @@ def test_generate_with_sampling_equals_oracle_sampler_on_the_device_logits(dev, 
     ocfg = orc.SamplerConfig(*vals)
     states = [77] * B
     seqs = [list(p) for p in prompts]
-    for p in range(P + N - 1):
+    ref.prefill(dev.upload(np.ascontiguousarray(prompts[:, :P - 1]), tb.I32), dev.upload(np.zeros(B, np.int32), tb.I32), B, P - 1, logits)
+    for p in range(P - 1, P + N - 1):
         tok = np.array([s[p] for s in seqs], np.int32)
         ref.decode(dev.upload(tok, tb.I32), dev.upload(np.full(B, p, np.int32), tb.I32), B, P + N, logits)
         dev.sync()

@@ -129,3 +129,48 @@ def test_layer_stage_by_stage(dev, orc):
     att_o = orc.attention_decode_f64(f(qr_d.to_vec()).astype(np.float64), f(kb[:pos + 1]).astype(np.float64),
                                      f(vb[:pos + 1]).astype(np.float64), pos + 1, nh, nkv, hd)
     assert rel_err(att_d, att_o) < 1e-3
+
+
+def test_prefill_chunk_equals_token_by_token(dev, orc):
+    """tq_llama_prefill over a 40-token prompt (tcgen05 GEMMs over all rows, chunk attention) against the oracle's
+    token-by-token loop: the last position's logits, the cache rows it appended, and a decode step that follows."""
+    import tang_b200 as tb
+
+    host = HostLlama(np.random.default_rng(21), n_layers=2, d=256, n_heads=4, n_kv=2, hd=128, ffn=512, vocab=1024)
+    B, P, max_seq = 2, 40, 64
+    rng = np.random.default_rng(22)
+    prompts = rng.integers(0, host.vocab, (B, P)).astype(np.int32)
+    kv_dim = host.n_kv * host.hd
+    model = host.to_device(dev, max_seq, B)
+    logits = dev.alloc(B * host.vocab, tb.F32)
+    model.prefill(dev.upload(prompts, tb.I32), dev.upload(np.zeros(B, np.int32), tb.I32), B, P, logits)
+    dev.sync()
+    got = logits.to_vec().reshape(B, host.vocab)
+    nxt = rng.integers(0, host.vocab, B).astype(np.int32)
+    model.decode(dev.upload(nxt, tb.I32), dev.upload(np.full(B, P, np.int32), tb.I32), B, P + 1, logits)
+    dev.sync()
+    got2 = logits.to_vec().reshape(B, host.vocab)
+    for b in range(B):
+        kc = [np.zeros((max_seq, kv_dim), np.uint16) for _ in range(host.n_layers)]
+        vc = [np.zeros((max_seq, kv_dim), np.uint16) for _ in range(host.n_layers)]
+        for p in range(P):
+            want = host.oracle_decode(orc, int(prompts[b, p]), kc, vc, p)
+        assert logits_err(got[b], want) < TOL_LOGITS, b
+        for li in range(host.n_layers):
+            kbuf, vbuf, _ = model.kv_buffers(li)
+            kd = kbuf.to_vec().reshape(B, max_seq, kv_dim)[b, :P]
+            vd = vbuf.to_vec().reshape(B, max_seq, kv_dim)[b, :P]
+            f = lambda bits: (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+            assert rel_err(f(kd), f(kc[li][:P]), floor_frac=1.0) < 2e-2
+            assert rel_err(f(vd), f(vc[li][:P]), floor_frac=1.0) < 2e-2
+        want2 = host.oracle_decode(orc, int(nxt[b]), kc, vc, P)
+        assert logits_err(got2[b], want2) < TOL_LOGITS, b
+    # a second chunk continues from the cache: prefill of [0, 24) then [24, 40) gives the same last logits
+    m2 = host.to_device(dev, max_seq, B)
+    lg2 = dev.alloc(B * host.vocab, tb.F32)
+    m2.prefill(dev.upload(np.ascontiguousarray(prompts[:, :24]), tb.I32), dev.upload(np.zeros(B, np.int32), tb.I32), B, 24, lg2)
+    m2.prefill(dev.upload(np.ascontiguousarray(prompts[:, 24:]), tb.I32), dev.upload(np.full(B, 24, np.int32), tb.I32), B, P - 24, lg2)
+    dev.sync()
+    assert logits_err(lg2.to_vec().reshape(B, host.vocab), got) < TOL_LOGITS
+    model.destroy()
+    m2.destroy()
