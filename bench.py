@@ -348,7 +348,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "parity_max_rel_err_vs_oracle": parity,
             "decode": None if decode is None else {
                 "metric": "llama3_8b_shape_decode_tokens_per_s", "peak_gbs": peak,
-                "results": [dict(r, frac_of_hbm_peak=r["gbs_per_gpu"] / peak) for r in decode]},
+                "results": [dict(r, frac_of_hbm_peak=r["gbs_per_gpu"] / peak) for r in decode if "batch" in r],
+                "prefill": [r for r in decode if "prefill_tokens" in r]},
             "extras": extras,
         }
         print(json.dumps(out))
@@ -468,6 +469,35 @@ def run_decode(dev, tb, torch, stream, comm, rank, world, args, barrier):
         out.append({"batch": B, "tp": world, "layers": args.decode_layers, "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3),
                     "bytes_per_gpu": byt, "gbs_per_gpu": byt / (ms * 1e-3) / 1e9, "logits_finite": finite,
                     "kernels_per_step": int((dev.launch_count - l0) // (steps + max(args.warmup, 3)))})
+    # prompt processing with the same model: one sequence, a 2048-token chunk from an empty cache
+    q_len = min(2048, c["ctx"])
+    with torch.cuda.stream(stream):
+        ptok = torch.randint(0, c["vocab"], (q_len,), dtype=torch.int32, device="cuda")
+        start0 = torch.zeros((1,), dtype=torch.int32, device="cuda")
+        plog = torch.empty((world, 1, c["vocab"] // world), dtype=torch.float32, device="cuda")
+    stream.synchronize()
+    mk = lambda t, dt: tb.Buffer(dev, t.data_ptr(), t.numel(), dt, owns=False)
+    model.prefill(mk(ptok, tb.I32), mk(start0, tb.I32), 1, q_len, mk(plog, tb.F32))      # sizes the workspaces
+    dev.sync()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        for _ in range(reps):
+            model.prefill(mk(ptok, tb.I32), mk(start0, tb.I32), 1, q_len, mk(plog, tb.F32))
+        ev1.record(stream)
+    barrier()
+    pms = ev0.elapsed_time(ev1) / reps
+    t = torch.tensor([pms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    pms = float(t[0])
+    w_params = args.decode_layers * (c["d"] * (c["n_heads"] + 2 * c["n_kv"]) * c["hd"] + c["d"] * c["n_heads"] * c["hd"] + 3 * c["d"] * c["ffn"])
+    out.append({"prefill_tokens": q_len, "tp": world, "layers": args.decode_layers, "ms": pms, "tokens_per_s": q_len / (pms * 1e-3),
+                "tflops_per_gpu": 2.0 * q_len * w_params / world / (pms * 1e-3) / 1e12, "logits_finite": bool(torch.isfinite(plog).all().item())})
     model.destroy()
     return out
 
