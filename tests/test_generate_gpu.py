@@ -204,3 +204,45 @@ def test_generate_with_sampling_equals_oracle_sampler_on_the_device_logits(dev, 
     assert np.array_equal(g1, g2)
     for m in (ref, m2, m3):
         m.destroy()
+
+
+def test_argument_errors_of_the_newer_entry_points(dev, orc):
+    """Bad arguments come back as status codes with a message (no unwinding, no device work)."""
+    import ctypes as C
+
+    import tang_b200 as tb
+
+    x = dev.upload(np.zeros((2, 16), np.float32))
+    st = dev.upload(np.zeros(2, np.uint64).view(np.float64), tb.F64)
+    with pytest.raises(tb.TangqError, match="temperature"):
+        dev.sample(x, 2, 16, tb.SamplerConfig(-1.0, 0, 1.0, 1.0), st)
+    with pytest.raises(tb.TangqError, match="penalty"):
+        dev.sample(x, 2, 16, tb.SamplerConfig(1.0, 0, 1.0, 0.0), st)
+    with pytest.raises(tb.TangqError, match="LCG"):
+        dev.sample(x, 2, 16, tb.SamplerConfig(1.0, 0, 1.0, 1.0), None)          # sampling without states
+    assert list(dev.sample(x, 2, 16, tb.SamplerConfig(0.0, 0, 1.0, 1.0), None).to_vec()) == [0, 0]   # greedy needs none
+    q = dev.alloc(2 * 3 * 128, tb.BF16)
+    kv = dev.alloc(4 * 128, tb.BF16)
+    with pytest.raises(tb.TangqError, match="n_heads/n_kv_heads"):
+        dev.gqa_prefill(q, kv, kv, [0], 1, 2, 3, 1, 128, 4 * 128)                 # group of 3
+    with pytest.raises(tb.TangqError, match="head_dim"):
+        dev.gqa_prefill(q, kv, kv, [0], 1, 2, 2, 2, 64, 4 * 128)
+    w = dev.upload(np.zeros((4, 32), np.float32))
+    with pytest.raises(tb.TangqError, match="kind"):
+        dev.quantize_matrix(w, 4, 32, tb.Q4_F16)                                  # the reference has f32 scales only
+    with pytest.raises(tb.TangqError, match="empty"):
+        dev.quantize_matrix(w, 0, 32, tb.Q4_F32)
+    # a workspace that would have to grow inside a capture is refused with an explanation, and the capture still ends
+    big = dev.upload(np.zeros((8, 300000), np.float32))          # 19 MB of f64 workspace: more than anything before it
+    st4 = dev.upload(np.zeros(8, np.uint64).view(np.float64), tb.F64)
+    out4 = dev.alloc(8, tb.I32)
+    cfg = tb.SamplerConfig(1.0, 5, 1.0, 1.0)
+    dev.begin_capture()
+    rc = dev._L.tq_sample(dev._ctx, C.c_void_p(big.ptr), 1, 8, 300000, C.byref(cfg), C.c_void_p(st4.ptr), None, None, 0,
+                          C.c_void_p(out4.ptr))
+    msg = dev._L.tq_last_error(dev._ctx).decode()
+    g = dev.end_capture()
+    g.free()
+    assert rc == tb._lib.TQ_EINVAL and "graph capture" in msg
+    dev.sample(big, 8, 300000, cfg, st4)         # outside a capture the workspace simply grows
+    dev.sync()
