@@ -26,6 +26,7 @@ constexpr int kHD = 128;              // head dimension of the MMA kernel
 constexpr int kTileKeys = 64;         // positions per smem tile
 constexpr int kRowBytes = kHD * 2 + 16;  // padded smem row: 272 B keeps ldmatrix / 4-byte reads conflict-free
 constexpr int kAttnThreads = 128;
+constexpr int kMaxSplits = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct GqaParams {
@@ -252,17 +253,32 @@ __global__ void __launch_bounds__(kHD) gqa_combine_kernel(const float* part_o, c
                                                           void* out, int out_f32) {
   pdl_wait();
   pdl_launch_dependents();
+  // the splits' merge weights once per CTA (a few numbers), then independent loads over the partial outputs
+  __shared__ float wgt_s[kMaxSplits];
+  __shared__ float inv_l;
   const size_t bh = blockIdx.x;  // b * n_heads + head
   const int d = threadIdx.x;
-  float M = -FLT_MAX;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(bh * n_splits + s) * 2]);
-  float L = 0.f, O = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float wgt = exp2f((part_ml[(bh * n_splits + s) * 2] - M) * kLog2e);
-    L += part_ml[(bh * n_splits + s) * 2 + 1] * wgt;
-    O += part_o[(bh * n_splits + s) * kHD + d] * wgt;
+  if (threadIdx.x < 32) {
+    float M = -FLT_MAX;
+    for (int s = threadIdx.x; s < n_splits; s += 32) M = fmaxf(M, part_ml[(bh * n_splits + s) * 2]);
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.f;
+    for (int s = threadIdx.x; s < n_splits; s += 32) {
+      const float wgt = exp2f((part_ml[(bh * n_splits + s) * 2] - M) * kLog2e);
+      wgt_s[s] = wgt;
+      L += part_ml[(bh * n_splits + s) * 2 + 1] * wgt;
+    }
+    // lanes hold disjoint splits: add them in lane order so that the sum does not depend on the shuffle tree
+    float Lsum = 0.f;
+    for (int l = 0; l < 32; ++l) Lsum += __shfl_sync(0xffffffffu, L, l);
+    if (threadIdx.x == 0) inv_l = Lsum > 0.f ? 1.0f / Lsum : 0.f;
   }
-  const float v = L > 0.f ? O / L : 0.f;
+  __syncthreads();
+  const float* src = part_o + bh * n_splits * kHD + d;
+  float O = 0.f;
+#pragma unroll 8
+  for (int s = 0; s < n_splits; ++s) O += src[(size_t)s * kHD] * wgt_s[s];
+  const float v = O * inv_l;
   if (out_f32) reinterpret_cast<float*>(out)[bh * kHD + d] = v;
   else reinterpret_cast<__nv_bfloat16*>(out)[bh * kHD + d] = __float2bfloat16_rn(v);
 }
@@ -518,6 +534,7 @@ int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const voi
   int want = (4 * ctx->sm_count + B * n_kv - 1) / (B * n_kv);
   int max_splits = (tiles + 1) / 2;
   if (max_splits < 1) max_splits = 1;
+  if (max_splits > kMaxSplits) max_splits = kMaxSplits;   // the merge kernel keeps one weight per split in shared memory
   int n_splits = want < 1 ? 1 : (want > max_splits ? max_splits : want);
   const int tiles_per_split = (tiles + n_splits - 1) / n_splits;
   n_splits = (tiles + tiles_per_split - 1) / tiles_per_split;
@@ -671,6 +688,7 @@ int tq_gqa_decode_noalloc(tq_ctx* ctx, const void* q_dev, const void* k_cache_de
   const int want = (4 * ctx->sm_count + B * n_kv - 1) / (B * n_kv);
   int max_splits = (tiles + 1) / 2;
   if (max_splits < 1) max_splits = 1;
+  if (max_splits > kMaxSplits) max_splits = kMaxSplits;   // the merge kernel keeps one weight per split in shared memory
   int n_splits = want < 1 ? 1 : (want > max_splits ? max_splits : want);
   const int tiles_per_split = (tiles + n_splits - 1) / n_splits;
   n_splits = (tiles + tiles_per_split - 1) / tiles_per_split;
