@@ -11,7 +11,8 @@ template <int KIND, int TERMS>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
-  constexpr int TB = (KIND == Q4_F16) ? 1152 : 1280;
+  constexpr int TB = (KIND == I8_ROW) ? 2048 : (KIND == Q4_F16) ? 1152 : 1280;
+  static_assert(KIND != I8_ROW || TERMS == 1, "int8 rows carry no scale into the operand: one exact term");
   constexpr int kMaxStages = 6;
   // ---- shared-memory carve-up (operand tiles need 1024-byte alignment for the 128-byte swizzle)
   uint8_t* smem = smem_raw;
@@ -34,6 +35,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
   int m0 = blockIdx.y * p.ntok;                                // first token of this CTA
   int m_end = p.m_total;                                       // rows at or beyond this are not this CTA's to store
   const uint8_t* tile_base = p.tiles;
+  const float* row_scales = p.row_scales;   // TQ_I8_ROW: per output row, applied to the accumulator
   if (p.g_counts) {
     // grouped (experts): blockIdx.z picks the group, whose rows are g_offsets[e] .. +g_counts[e] of x and y and
     // whose weights start g_tile_stride bytes further on; token tiles beyond the group's rows leave at once
@@ -48,6 +50,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     m_end = p.g_offsets[e] + cnt;
     m0 += p.g_offsets[e];
     tile_base += (size_t)e * p.g_tile_stride;
+    row_scales += (size_t)e * p.n_rows;
   }
   const int kc_begin = p.g_counts ? 0 : blockIdx.z * p.kc_per_split;   // this CTA's slice of K, in 128-k tiles
   const int kc_len = min(p.kc_per_split, p.kc_total - kc_begin);
@@ -221,7 +224,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       const int rbi = combo >> 6, h = (combo >> 5) & 1, L = combo & 31;
       const int g = L >> 2, t = L & 3;
       const int row = rbi * 16 + g + 8 * h;
-      src_off[i] = rbi * KT * TB + h * 512 + 16 * L;
+      src_off[i] = rbi * KT * TB + (KIND == I8_ROW ? h * 1024 : h * 512) + 16 * L;
       sc_off[i] = rbi * KT * TB + 1024 + (KIND == Q4_F16 ? h * 64 + g * 8 : h * 128 + g * 16);
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) dst_off[i][jj] = row * 128 + (((4 * jj + t) ^ (row & 7)) << 4);
@@ -276,6 +279,18 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
 #endif
 #pragma unroll
       for (int i = 0; i < kCombos; ++i) {
+        if constexpr (KIND == I8_ROW) {
+          // int8 with one scale per output row: the integers go into the operand as they are (exact in bf16) and the
+          // row scale multiplies the accumulator in the epilogue -- an exact product with a single term
+          const uint4 w4 = *reinterpret_cast<const uint4*>(raw + src_off[i] + 512 * c);   // [even k | odd k] of blocks 2c, 2c+1
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            uint32_t q[4];
+            dequant_i8_words(jj ? w4.z : w4.x, jj ? w4.w : w4.y, q);
+            *reinterpret_cast<uint4*>(a_hi + dst_off[i][jj]) = make_uint4(q[0], q[1], q[2], q[3]);
+          }
+          continue;
+        }
         const uint2 w2 = *reinterpret_cast<const uint2*>(raw + src_off[i] + 8 * c);   // blocks 2c, 2c+1
         // The scale as s_hi + s_lo, two bf16 numbers (exact for an f16 scale: 11 = 8 + 3 significant bits).
         // With t = q*s_lo (7 bits, exact in bf16), hi = fma(q, s_hi, t) is the exact product rounded once;
@@ -341,6 +356,13 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)(p.acc_stride + c0), v1);
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] += v1[i];
+        if constexpr (KIND == I8_ROW) {
+          if (p.splits == 1) {   // (with K split, the scale multiplies the sum of the partials instead)
+            const float rs = row_scales[n];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] *= rs;
+          }
+        }
         if (p.splits > 1) {
           // K is split over gridDim.z CTAs: park the f32 partial; the last CTA of the tile adds them up
           float* part = p.partial + (size_t)blockIdx.z * p.m_total * p.n_rows;
@@ -388,6 +410,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         const float* src = p.partial + (size_t)m * p.n_rows + n;
         float sum = 0.f;
         for (int z = 0; z < p.splits; ++z) sum += __ldcg(src + z * plane);
+        if constexpr (KIND == I8_ROW) sum *= row_scales[n];
         if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(sum);
         else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + n] = sum;
       }
@@ -415,7 +438,8 @@ static EncodeTiledFn encode_tiled() {
 }
 
 bool umma_supported(const tq_qweight* w, size_t m) {
-  return (w->kind == TQ_Q4_F16 || w->kind == TQ_Q4_F32) && w->rows % kUmmaRows == 0 && w->cols % kTileK == 0 && m >= 1;
+  return (w->kind == TQ_Q4_F16 || w->kind == TQ_Q4_F32 || w->kind == TQ_I8_ROW) && w->rows % kUmmaRows == 0 &&
+         w->cols % kTileK == 0 && m >= 1;
 }
 
 // y[m, rows] = x[m, cols] . W^T through the tcgen05 kernel.  x: bf16, 16-byte aligned rows.
@@ -423,9 +447,10 @@ bool umma_supported(const tq_qweight* w, size_t m) {
 // offsets[e] .. +counts[e] of x (device arrays) and m is the total row count of x / y.
 int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
                       size_t ldy, int terms, const UmmaGroups* grp) {
+  if (w->kind == TQ_I8_ROW) terms = 1;   // exact with one term: the row scale is applied to the accumulator
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return fail(ctx, TQ_EUNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
-  TQ_REQUIRE(ctx, umma_supported(w, m), "tcgen05 GEMM: needs a Q4 weight with rows %% 128 == 0 and cols %% 128 == 0");
+  TQ_REQUIRE(ctx, umma_supported(w, m), "tcgen05 GEMM: needs a Q4 or int8-per-row weight with rows %% 128 == 0 and cols %% 128 == 0");
   TQ_REQUIRE(ctx, ((uintptr_t)x_bf16 & 15) == 0 && (ldx * 2) % 16 == 0, "tcgen05 GEMM: activation rows must be 16-byte aligned");
   // Ring sizes.  Two rules come from the dequant groups running ahead of one another (a parity wait
   // is only sound when the waiter is at most one phase ahead of the barrier): at least kUmmaGroups
@@ -485,6 +510,7 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   if (cr != CUDA_SUCCESS) return fail(ctx, TQ_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
   UmmaParams p;
   p.tiles = w->tiles;
+  p.row_scales = w->row_scales;
   p.y = y;
   p.ldy = (long long)ldy;
   p.m_total = (int)m;
@@ -531,7 +557,8 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.dbg = getenv("TQ_UMMA_DBG") ? atoi(getenv("TQ_UMMA_DBG")) : 0;
 #endif
   cudaError_t e;
-  if (w->kind == TQ_Q4_F16) e = terms == 2 ? go(qgemm_umma_kernel<Q4_F16, 2>) : go(qgemm_umma_kernel<Q4_F16, 1>);
+  if (w->kind == TQ_I8_ROW) e = go(qgemm_umma_kernel<I8_ROW, 1>);
+  else if (w->kind == TQ_Q4_F16) e = terms == 2 ? go(qgemm_umma_kernel<Q4_F16, 2>) : go(qgemm_umma_kernel<Q4_F16, 1>);
   else e = terms == 2 ? go(qgemm_umma_kernel<Q4_F32, 2>) : go(qgemm_umma_kernel<Q4_F32, 1>);
   TQ_CUDA(ctx, e);
 #ifdef TQ_UMMA_PROFILE

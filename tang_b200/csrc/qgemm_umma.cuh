@@ -41,6 +41,7 @@ constexpr int kUmmaThreads = 32 * (kUmmaFirstDqWarp + kUmmaDqWarps);
 
 struct UmmaParams {
   const uint8_t* tiles;   // fragment tiles [n_row_blocks][kc_total][tile_bytes]
+  const float* row_scales;   // TQ_I8_ROW: one scale per output row (applied to the accumulator), else unused
   void* y;                // [M][ldy] f32 or bf16
   long long ldy;
   int m_total;            // activation rows

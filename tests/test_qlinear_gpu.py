@@ -221,11 +221,13 @@ def test_config1_int4_full_size(dev, orc, m):
     (1, 384, 1024, 300),      # several token tiles (evened out), ragged last one
     (1, 1024, 2048, 512),
     (0, 512, 4096, 130),      # long k: every ring wraps many times
+    (3, 256, 512, 40),        # int8 with one scale per row: integers into the operand, scale on the accumulator
+    (3, 4096, 4096, 64),      # the int8 benchmark shape at a decode batch (split K)
 ])
 def test_tensor_memory_gemm(dev, orc, kind, rows, cols, m):
     """Many activation rows take the tcgen05 kernel (weights dequantised into 128-byte-swizzled
     shared-memory tiles, f32 accumulator in tensor memory): f32 outputs use exact hi + lo products,
-    bf16 outputs the product rounded once to bf16."""
+    bf16 outputs the product rounded once to bf16; int8-per-row weights are exact with a single term."""
     import tang_b200 as tb
 
     rng = np.random.default_rng(900 + rows + m)
