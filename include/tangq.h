@@ -131,6 +131,14 @@ TQ_API int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x
  * f32 (on the device, after upload).  Synchronises. */
 TQ_API int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m);
 
+/* The same call without the final wait, for a caller with several matvecs to run (a list of layers, a batch of
+ * independent requests): the upload, the kernel and the read-back are queued on the context's stream in call
+ * order, and ONE tq_sync after the last call makes every y_host valid (and reports a device-side failure).  Both
+ * vectors must stay alive and untouched until that tq_sync; pageable vectors make the copies themselves block, so
+ * pinned ones (cudaHostAlloc / cudaHostRegister) are what this form is for -- a pinned y_host is written by the
+ * kernel directly.  The reference has no asynchronous form: this replaces a loop of quantize.rs:256 calls. */
+TQ_API int tq_q_matvec_host_async(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m);
+
 /* Launch-shape override for tq_qlinear, for tuning runs: rows-per-CTA = 16*wr, K slices = wk,
  * ring depth = stages, 128-k tiles per warp and stage = tiles_per_warp.  wr = 0 restores the
  * built-in choice. */

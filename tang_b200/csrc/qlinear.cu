@@ -602,7 +602,10 @@ int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x_dtype,
   return TQ_OK;
 }
 
-int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m) {
+}  // extern "C"
+
+// The host-vector call; `wait` = return only when y_host holds the result.
+static int matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m, bool wait) {
   if (int st = bind(ctx)) return st;
   TQ_REQUIRE(ctx, w != nullptr, "tq_q_matvec_host: null weight");
   TQ_REQUIRE(ctx, dtype == TQ_F64 || dtype == TQ_F32 || dtype == TQ_BF16, "tq_q_matvec_host: dtype must be f64, f32 or bf16");
@@ -630,7 +633,7 @@ int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void*
     cudaPointerAttributes attr;
     if (cudaPointerGetAttributes(&attr, y_host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer) {
       if (int st = tq_qlinear(ctx, w, xd, dev_dt, 0, m, attr.devicePointer, dev_dt, 0, nullptr)) return st;
-      return tq_sync(ctx);
+      return wait ? tq_sync(ctx) : TQ_OK;
     }
     cudaGetLastError();   // an unregistered pointer is not an error here
   }
@@ -641,7 +644,17 @@ int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void*
     yd = s + off_y2;
   }
   TQ_CUDA(ctx, cudaMemcpyAsync(y_host, yd, ny * es, cudaMemcpyDeviceToHost, ctx->stream));
-  return tq_sync(ctx);
+  return wait ? tq_sync(ctx) : TQ_OK;
+}
+
+extern "C" {
+
+int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m) {
+  return matvec_host(ctx, w, x_host, y_host, dtype, m, true);
+}
+
+int tq_q_matvec_host_async(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m) {
+  return matvec_host(ctx, w, x_host, y_host, dtype, m, false);
 }
 
 }  // extern "C"

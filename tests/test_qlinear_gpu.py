@@ -311,3 +311,35 @@ def test_host_matvec_into_pinned_memory(dev, orc):
         y_pageable = dev._matvec_host(w, x_np.copy(), 1)
         y_pinned = yh.view(torch.int16).numpy().view(np.uint16) if dt == tb.BF16 else yh.numpy()
         assert np.array_equal(y_pinned, y_pageable)
+
+
+def test_host_matvec_async_queue(dev, orc):
+    """Several host-vector calls queued without a wait, one tq_sync at the end: every pinned result equals the
+    waiting call's, bit for bit, whatever mix of weights and vector types was queued."""
+    import ctypes as C
+
+    import torch
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(32)
+    cols = 1024
+    ws = []
+    for i, rows in enumerate((256, 512, 384)):
+        sc, pay = make_weight(rng, 1, rows, cols)
+        ws.append((_upload(dev, 1, sc, pay, rows, cols), rows))
+    jobs = []
+    for rep in range(2):
+        for w, rows in ws:
+            dt, tdt = ((tb.F32, torch.float32), (tb.BF16, torch.bfloat16))[rep]
+            xh = torch.from_numpy(rng.standard_normal(cols).astype(np.float32)).to(tdt).pin_memory()
+            yh = torch.zeros(rows, dtype=tdt).pin_memory()
+            jobs.append((w, dt, xh, yh))
+    for w, dt, xh, yh in jobs:
+        dev._check(dev._L.tq_q_matvec_host_async(dev._ctx, C.c_void_p(w.handle), C.c_void_p(xh.data_ptr()),
+                                                 C.c_void_p(yh.data_ptr()), dt, 1))
+    dev.sync()
+    for w, dt, xh, yh in jobs:
+        want = torch.zeros_like(yh).pin_memory()
+        dev._check(dev._L.tq_q_matvec_host(dev._ctx, C.c_void_p(w.handle), C.c_void_p(xh.data_ptr()), C.c_void_p(want.data_ptr()), dt, 1))
+        assert torch.equal(yh.view(torch.int16) if dt == tb.BF16 else yh, want.view(torch.int16) if dt == tb.BF16 else want)
+        assert float(want.float().abs().max()) > 0
