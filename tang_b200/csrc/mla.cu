@@ -6,12 +6,14 @@
 // are also the value.  q_lat = W_qk[h] q_nope and o = W_uv[h] o_lat are per-head int8 GEMVs
 // (tq_mla_absorb_q / tq_mla_unabsorb, grouped launches of the quantised linear kernel).
 //
-// Kernel: grid = (splits, heads/16, batch).  A CTA owns 16 heads (one MMA row tile) and streams
-// 64-position cache tiles through a cp.async double buffer.  Per tile, warp w scores positions
-// 16w..16w+15 (Q fragments by ldmatrix from shared memory, 36 k-steps), the four warps agree on
-// the row maxima through shared memory, write P (two bf16 terms) to shared memory, and warp w then
-// accumulates the value columns 128w..128w+127 for all 64 positions.  Splits are merged by
-// mla_combine_kernel with the usual max-rescaled sum.
+// Kernel: grid = (splits, heads/(16 HT), batch).  A CTA owns HT = 1 or 2 tiles of 16 heads (one MMA row tile
+// each, four warps per tile) and streams 64-position cache tiles, shared by its head tiles, through a cp.async
+// double buffer.  Per cache tile, warp w of a head tile scores positions 16w..16w+15 (Q fragments by ldmatrix
+// from shared memory, 36 k-steps), the four warps agree on the row maxima through shared memory, write P (two bf16
+// terms: with one, a sharply peaked softmax showed errors of 1e-2 of the output rms after the un-absorb GEMV)
+// to shared memory, and warp w then accumulates the value columns 128w..128w+127 for all 64 positions.  Two
+// head tiles per CTA double the warps that hide the latency of the legacy MMA path and halve the cache bytes
+// read through L2.  Splits are merged by mla_combine_kernel with the usual max-rescaled sum.
 #include <cuda_bf16.h>
 
 #include <cfloat>
@@ -30,7 +32,7 @@ constexpr int kC = 512, kR = 64, kRow = kC + kR;         // latent, rope, cache 
 constexpr int kMlaTile = 64;
 constexpr int kMlaRowBytes = kRow * 2 + 16;               // 1168: conflict-free ldmatrix rows
 constexpr int kPRowBytes = kMlaTile * 2 + 16;             // 144
-constexpr int kMlaThreads = 128;
+constexpr int kMlaThreads = 128;                          // per head tile
 constexpr float kLog2eM = 1.4426950408889634f;
 
 struct MlaParams {
@@ -65,27 +67,30 @@ __device__ __forceinline__ uint32_t mla_pack(float lo, float hi) {
 constexpr size_t kMlaSmemQ = 16 * kMlaRowBytes;
 constexpr size_t kMlaSmemKV = 2 * (size_t)kMlaTile * kMlaRowBytes;
 constexpr size_t kMlaSmemP = 2 * 16 * kPRowBytes;
-constexpr size_t kMlaSmem = kMlaSmemQ + kMlaSmemKV + kMlaSmemP + 4 * 16 * sizeof(float);
+constexpr size_t mla_smem(int ht) { return ht * (kMlaSmemQ + kMlaSmemP + 4 * 16 * sizeof(float)) + kMlaSmemKV; }
 
-__global__ void __launch_bounds__(kMlaThreads) mla_decode_kernel(const MlaParams p) {
+template <int HT>
+__global__ void __launch_bounds__(kMlaThreads * HT) mla_decode_kernel(const MlaParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* q_s = smem;
-  uint8_t* kv_s = q_s + kMlaSmemQ;
-  uint8_t* p_s = kv_s + kMlaSmemKV;                          // [hi|lo][16 rows][144 B]
-  float* mw = reinterpret_cast<float*>(p_s + kMlaSmemP);     // [4 warps][16 rows] tile maxima
+  constexpr int kThreads = kMlaThreads * HT;
+  const int ht = threadIdx.x >> 7;                            // head tile of this warp
+  uint8_t* kv_s = smem + HT * kMlaSmemQ;
+  uint8_t* q_s = smem + ht * kMlaSmemQ;
+  uint8_t* p_s = kv_s + kMlaSmemKV + ht * kMlaSmemP;         // [hi|lo][16 rows][144 B]
+  float* mw = reinterpret_cast<float*>(kv_s + kMlaSmemKV + HT * kMlaSmemP) + ht * 64;   // [4 warps][16 rows] tile maxima
 
-  const int split = blockIdx.x, hg = blockIdx.y, b = blockIdx.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x, hg = blockIdx.y * HT + ht, b = blockIdx.z;
+  const int warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int len = p.lens[b];
   const int k_begin = split * p.chunk;
   const int k_end = min(len, k_begin + p.chunk);
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + kMlaTile - 1) / kMlaTile : 0;
   const __nv_bfloat16* cbase = p.cache + (size_t)b * p.seq_stride;
 
-  // Q of this head group -> shared memory (16 rows x 72 chunks)
+  // Q of this head tile -> shared memory (16 rows x 72 chunks)
   {
     const __nv_bfloat16* qg = p.q + ((size_t)b * p.n_heads + (size_t)hg * 16) * kRow;
-    for (int c = threadIdx.x; c < 16 * 72; c += kMlaThreads) {
+    for (int c = threadIdx.x & 127; c < 16 * 72; c += kMlaThreads) {
       const int row = c / 72, ch = c % 72;
       *reinterpret_cast<uint4*>(q_s + (size_t)row * kMlaRowBytes + ch * 16) =
           *reinterpret_cast<const uint4*>(qg + (size_t)row * kRow + ch * 8);
@@ -94,7 +99,7 @@ __global__ void __launch_bounds__(kMlaThreads) mla_decode_kernel(const MlaParams
 
   auto load_tile = [&](int tile, int buf) {
     const int key0 = k_begin + tile * kMlaTile;
-    for (int c = threadIdx.x; c < kMlaTile * 72; c += kMlaThreads) {
+    for (int c = threadIdx.x; c < kMlaTile * 72; c += kThreads) {
       const int row = c / 72, ch = c % 72;
       const int key = key0 + row;
       const bool valid = key < k_end;
@@ -326,7 +331,8 @@ int tq_mla_decode(tq_ctx* ctx, const void* q_full_bf16_dev, const void* cache_bf
   TQ_REQUIRE(ctx, kv_lora == (size_t)kC && rope_dim == (size_t)kR, "tq_mla_decode: kv_lora must be %d and rope_dim %d", kC, kR);
   TQ_REQUIRE(ctx, n_heads > 0 && n_heads % 16 == 0, "tq_mla_decode: heads (per rank) must be a multiple of 16");
   TQ_REQUIRE(ctx, max_len > 0, "tq_mla_decode: max_len must bound the sequence lengths");
-  const int B = (int)batch, HG = (int)(n_heads / 16);
+  const int HT = n_heads % 32 == 0 ? 2 : 1;   // head tiles per CTA
+  const int B = (int)batch, HG = (int)(n_heads / (16 * HT));
   const int tiles = ((int)max_len + kMlaTile - 1) / kMlaTile;
   int want = (2 * ctx->sm_count + B * HG - 1) / (B * HG);
   int max_splits = (tiles + 1) / 2;
@@ -353,13 +359,15 @@ int tq_mla_decode(tq_ctx* ctx, const void* q_full_bf16_dev, const void* cache_bf
     p.part_o = static_cast<float*>(ctx->scratch);
     p.part_ml = p.part_o + n_part * kC;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    TQ_CUDA(ctx, cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMlaSmem));
-    attr_set = true;
+  static thread_local int attr_dev = -1;   // the attribute is per device
+  if (attr_dev != ctx->device) {
+    TQ_CUDA(ctx, cudaFuncSetAttribute(mla_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mla_smem(1)));
+    TQ_CUDA(ctx, cudaFuncSetAttribute(mla_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mla_smem(2)));
+    attr_dev = ctx->device;
   }
   dim3 grid((unsigned)n_splits, (unsigned)HG, (unsigned)B);
-  mla_decode_kernel<<<grid, kMlaThreads, kMlaSmem, ctx->stream>>>(p);
+  if (HT == 2) mla_decode_kernel<2><<<grid, 2 * kMlaThreads, mla_smem(2), ctx->stream>>>(p);
+  else mla_decode_kernel<1><<<grid, kMlaThreads, mla_smem(1), ctx->stream>>>(p);
   ctx->launches++;
   TQ_CUDA(ctx, cudaGetLastError());
   if (n_splits > 1) {
