@@ -133,17 +133,15 @@ __global__ void __launch_bounds__(kMlaThreads * HT) mla_decode_kernel(const MlaP
     for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
     {
       const uint8_t* qrow = q_s + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * kMlaRowBytes + 16 * (lane >> 4);
-      const uint8_t* krow = kt + (size_t)(16 * warp + g) * kMlaRowBytes + 4 * t;
+      // the key fragments of both 8-position halves in one ldmatrix: matrix i = (half i / 2, k 8 (i % 2) .. + 7)
+      const uint8_t* krow = kt + (size_t)(16 * warp + 8 * (lane >> 4) + (lane & 7)) * kMlaRowBytes + 16 * ((lane >> 3) & 1);
 #pragma unroll 4
       for (int ks = 0; ks < kRow / 16; ++ks) {
-        uint32_t a[4];
+        uint32_t a[4], kb[4];
         ldsm_x4(a, qrow + 32 * ks);
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + (size_t)8 * nt * kMlaRowBytes + 32 * ks);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + (size_t)8 * nt * kMlaRowBytes + 32 * ks + 16);
-          mma_bf16_16816(s[nt], a[0], a[1], a[2], a[3], b0, b1);
-        }
+        ldsm_x4(kb, krow + 32 * ks);
+        mma_bf16_16816(s[0], a[0], a[1], a[2], a[3], kb[0], kb[1]);
+        mma_bf16_16816(s[1], a[0], a[1], a[2], a[3], kb[2], kb[3]);
       }
     }
     // scaled, masked; sc[r][i]: row r (g / g+8), position key0 + 8*(i/2) + 2t + (i%2)
