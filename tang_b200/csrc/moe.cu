@@ -118,13 +118,58 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
     for (int i = threadIdx.x; i < E; i += blockDim.x) lg[i] = __ldcg(logits_out + (size_t)t * E + i);
   }
   __syncthreads();
-  // softmax terms in parallel (one f64 exp per thread), their sum in index order by one thread
+  // softmax terms in parallel (one f64 exp per thread), their sum in index order by one thread; the maximum and
+  // the top-k selection by the first warp (lane l owns experts l, l + 32, ...): the rule is "highest logit first,
+  // lowest index on ties, exactly top_k", which a (value, index) tournament reproduces for ordered values.  A NaN
+  // logit has no order; then one thread runs the comparison loop as written.
   __shared__ double ex[kMaxExperts];
   __shared__ double mx_s;
-  if (threadIdx.x == 0) {
+  __shared__ int pick[kMaxTopK];
+  if (warp == 0) {
     double mx = lg[0];
-    for (int i = 1; i < E; ++i) mx = fmax(mx, lg[i]);
-    mx_s = mx;
+    bool any_nan = false;
+    for (int i = lane; i < E; i += 32) {
+      mx = fmax(mx, lg[i]);
+      any_nan |= lg[i] != lg[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    any_nan = __any_sync(0xffffffffu, any_nan);
+    if (lane == 0) mx_s = mx;
+    if (!any_nan) {
+      unsigned taken = 0;                                  // bit j: expert lane + 32 j is chosen
+      for (int s = 0; s < top_k; ++s) {
+        double bv = 0.0;
+        int bi = -1;
+        for (int j = 0, i = lane; i < E; ++j, i += 32)
+          if (!((taken >> j) & 1u) && (bi < 0 || lg[i] > bv)) {   // ascending i: '>' keeps the lower index
+            bv = lg[i];
+            bi = i;
+          }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+          if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) {
+            bv = ov;
+            bi = oi;
+          }
+        }
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        if (lane == 0) pick[s] = bi;
+      }
+    } else if (lane == 0) {
+      unsigned long long taken[kMaxExperts / 64] = {0, 0, 0, 0};
+      for (int s = 0; s < top_k; ++s) {
+        int best = -1;
+        for (int i = 0; i < E; ++i) {
+          if ((taken[i >> 6] >> (i & 63)) & 1ull) continue;
+          if (best < 0 || lg[i] > lg[best]) best = i;   // strict '>' keeps the lower index on ties
+        }
+        taken[best >> 6] |= 1ull << (best & 63);
+        pick[s] = best;
+      }
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < E; i += blockDim.x) ex[i] = exp(lg[i] - mx_s);
@@ -132,23 +177,14 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
   if (threadIdx.x == 0) {
     double sum = 0.0;
     for (int i = 0; i < E; ++i) sum += ex[i];
-    unsigned long long taken[kMaxExperts / 64] = {0, 0, 0, 0};
     double chosen = 0.0;
     double pw[kMaxTopK];
-    int pi[kMaxTopK];
     for (int s = 0; s < top_k; ++s) {
-      int best = -1;
-      for (int i = 0; i < E; ++i) {
-        if ((taken[i >> 6] >> (i & 63)) & 1ull) continue;
-        if (best < 0 || lg[i] > lg[best]) best = i;   // strict '>' keeps the lower index on ties
-      }
-      taken[best >> 6] |= 1ull << (best & 63);
-      pi[s] = best;
-      pw[s] = ex[best] / sum;
+      pw[s] = ex[pick[s]] / sum;
       chosen += pw[s];
     }
     for (int s = 0; s < top_k; ++s) {
-      idx_out[(size_t)t * top_k + s] = pi[s];
+      idx_out[(size_t)t * top_k + s] = pick[s];
       w_out[(size_t)t * top_k + s] = (float)(renorm ? pw[s] / chosen : pw[s]);
     }
   }
