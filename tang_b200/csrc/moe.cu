@@ -37,8 +37,8 @@ bool umma_grouped_supported(const tq_qweight* w, int n_groups);
 // One CTA of eight warps per token; warp w computes the logits of experts w, w + 8, ...
 // The reference order is one f64 addition per k, ascending, of products that are exact in f64 (bf16 x
 // bf16).  A warp-parallel sum gives the SAME BITS whenever no addition can round, whatever the order:
-// every product is a multiple of q = 2^qexp and the sum of |products| stays below 2^52 q, so every
-// partial sum of every subset is exactly representable.  The warp certifies this from the exponents
+// every product is a multiple of q = 2^qexp and the sum of |products| stays below 2^53 q, so every
+// partial sum of every subset is an integer below 2^53 times q: exactly representable.  The warp certifies this from the exponents
 // (qexp = min over non-zero products of the operands' unit-in-the-last-place exponents, sum |p| with
 // a factor two of slack); an expert that fails the test is redone by one lane in the reference order.
 __device__ __forceinline__ int bf16_ulp_exp(unsigned short bits) {   // value is a multiple of 2^this
@@ -93,11 +93,23 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
       qmin = min(qmin, __shfl_xor_sync(0xffffffffu, qmin, o));
     }
     // NaN or infinity anywhere fails the comparison and takes the reference order as well
-    const bool exact = qmin == (1 << 20) || ((double)sabs < ldexp(1.0, 50 + qmin));
+    const bool exact = qmin == (1 << 20) || ((double)sabs < ldexp(1.0, 52 + qmin));
     if (!exact && lane == 0) {
+      // the reference order, one addition per k: only the additions depend on one another, so the operands come
+      // eight at a time (16-byte loads) and the products of the next eight are formed while these are added
       acc = 0.0;
-      for (int k = 0; k < d; ++k)
-        acc += (double)__uint_as_float((unsigned)hs[k] << 16) * (double)__uint_as_float((unsigned)wrow[k] << 16);
+      for (int k0 = 0; k0 < d; k0 += 8) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k0), hv = *reinterpret_cast<const uint4*>(hs + k0);
+        const unsigned ww[4] = {wv.x, wv.y, wv.z, wv.w}, hh[4] = {hv.x, hv.y, hv.z, hv.w};
+        double pr[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          pr[2 * j] = (double)__uint_as_float(hh[j] << 16) * (double)__uint_as_float(ww[j] << 16);
+          pr[2 * j + 1] = (double)__uint_as_float(hh[j] & 0xFFFF0000u) * (double)__uint_as_float(ww[j] & 0xFFFF0000u);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += pr[j];
+      }
     }
     if (lane == 0) {
       lg[e] = acc;
