@@ -292,6 +292,11 @@ class QuantComputeDevice:
                                              C.c_void_p(y.ctypes.data), dt, m))
         return y
 
+    def q_matvec_host_async(self, w: QBuffer, x_ptr: int, y_ptr: int, dtype: int, m: int = 1) -> None:
+        """Queues a host-vector matvec without waiting (``tq_q_matvec_host_async``): ``x_ptr`` / ``y_ptr`` are addresses
+        of pinned host vectors of ``dtype`` (F64, F32 or BF16) that must stay alive and untouched until ``sync()``."""
+        self._check(self._L.tq_q_matvec_host_async(self._ctx, C.c_void_p(w.handle), C.c_void_p(x_ptr), C.c_void_p(y_ptr), dtype, m))
+
     def q4_matvec(self, w: QBuffer, x) -> np.ndarray:
         """``q4_matvec(&QuantizedQ4, &[f64]) -> Vec<f64>`` (quantize.rs:256-289), host vectors."""
         if w.kind not in (Q4_F32, Q4_F16):

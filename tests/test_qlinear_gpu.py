@@ -335,8 +335,7 @@ def test_host_matvec_async_queue(dev, orc):
             yh = torch.zeros(rows, dtype=tdt).pin_memory()
             jobs.append((w, dt, xh, yh))
     for w, dt, xh, yh in jobs:
-        dev._check(dev._L.tq_q_matvec_host_async(dev._ctx, C.c_void_p(w.handle), C.c_void_p(xh.data_ptr()),
-                                                 C.c_void_p(yh.data_ptr()), dt, 1))
+        dev.q_matvec_host_async(w, xh.data_ptr(), yh.data_ptr(), dt, 1)
     dev.sync()
     for w, dt, xh, yh in jobs:
         want = torch.zeros_like(yh).pin_memory()
