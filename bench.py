@@ -182,8 +182,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    stream = torch.cuda.Stream()
-    dev = tb.QuantComputeDevice(local_rank, stream=stream.cuda_stream)
+    # The context owns its stream (on a stream of its own the library may let independent matvecs overlap);
+    # torch sees the same stream, so CUDA events recorded through torch time the library's launches.
+    dev = tb.QuantComputeDevice(local_rank)
+    stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local_rank))
     L, m = args.layers, args.m
 
     with torch.cuda.stream(stream):

@@ -139,11 +139,6 @@ TQ_API int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host
  * kernel directly.  The reference has no asynchronous form: this replaces a loop of quantize.rs:256 calls. */
 TQ_API int tq_q_matvec_host_async(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m);
 
-/* Launch-shape override for tq_qlinear, for tuning runs: rows-per-CTA = 16*wr, K slices = wk,
- * ring depth = stages, 128-k tiles per warp and stage = tiles_per_warp.  wr = 0 restores the
- * built-in choice. */
-TQ_API int tq_qlinear_set_config(tq_ctx* ctx, int wr, int wk, int stages, int tiles_per_warp);
-
 /* Row-wise concatenation of weights already on the device (same kind and column count; every part
  * but the last with a multiple of 16 rows): builds the fused [q;k;v] and [gate;up] projections
  * from the reference's separate matrices (weight order [wq, wk, wv, wo, gate, up, down],

@@ -50,7 +50,6 @@ PROTOTYPES = {
     "tq_qlinear": (_i, [_p, _p, _p, _i, _sz, _sz, _p, _i, _sz, _p]),
     "tq_q_matvec_host": (_i, [_p, _p, _p, _p, _i, _sz]),
     "tq_q_matvec_host_async": (_i, [_p, _p, _p, _p, _i, _sz]),
-    "tq_qlinear_set_config": (_i, [_p, _i, _i, _i, _i]),
     "tq_qweight_concat_rows": (_i, [_p, _pp, _sz, _pp]),
     "tq_rms_norm": (_i, [_p, _p, _i, _p, _p, _i, _sz, _sz, C.c_float, _p, _i, _p]),
     "tq_rope_tables": (_i, [_p, _sz, _sz, C.c_double, _p, _p]),

@@ -104,8 +104,9 @@ int tq_ctx_create(int device, void* stream, tq_ctx** out) {
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(TQ_ECUDA);
     ctx->owns_stream = true;
   }
-  if (cudaMalloc(&ctx->dev_err, (1 + kTileCounters) * sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
-  if (cudaMemsetAsync(ctx->dev_err, 0, (1 + kTileCounters) * sizeof(int), ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMalloc(&ctx->dev_err, (1 + kTileCounters + kGemvSets * kGemvMaxGrid * 2) * sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMemsetAsync(ctx->dev_err, 0, (1 + kTileCounters + kGemvSets * kGemvMaxGrid * 2) * sizeof(int), ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMalloc(&ctx->gemv_ws, (size_t)kGemvSets * kGemvMaxGrid * 2 * 128 * sizeof(float)) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_err), sizeof(int), cudaHostAllocDefault) != cudaSuccess) return bail(TQ_ECUDA);
   *ctx->host_err = 0;
   if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
@@ -121,6 +122,7 @@ int tq_ctx_destroy(tq_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->splitk) cudaFree(ctx->splitk);
   if (ctx->dev_err) cudaFree(ctx->dev_err);
+  if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
   if (ctx->host_err) cudaFreeHost(ctx->host_err);
   if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
@@ -138,7 +140,7 @@ int tq_sync(tq_ctx* ctx) {
   TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   const int code = *ctx->host_err;
   if (code != 0) {
-    cudaMemset(ctx->dev_err, 0, sizeof(int));
+    cudaMemset(ctx->dev_err, 0, (1 + kTileCounters + kGemvSets * kGemvMaxGrid * 2) * sizeof(int));   // a kernel that gave up may have left tile counters half counted
     return fail(ctx, TQ_ETIMEOUT, "a kernel gave up a bounded wait (device code %d)", code);
   }
   return TQ_OK;

@@ -130,6 +130,8 @@ int tq_comm_world(const tq_comm* comm) { return comm ? comm->world : 1; }
 
 int tq_all_reduce_f32(tq_ctx* ctx, tq_comm* comm, float* buf_dev, size_t n) {
   if (int st = bind(ctx)) return st;
+  ctx->inflight_unknown = true;   // a library kernel follows: later launches assume nothing about what runs
+  ctx->n_inflight = 0;
   if (!comm || comm->world == 1 || n == 0) return TQ_OK;
   TQ_REQUIRE(ctx, buf_dev != nullptr && comm->comm != nullptr, "tq_all_reduce_f32: null buffer or aborted communicator");
   TQ_NCCL(ctx, api().AllReduce(buf_dev, buf_dev, n, ncclFloat, ncclSum, comm->comm, ctx->stream));
@@ -138,6 +140,8 @@ int tq_all_reduce_f32(tq_ctx* ctx, tq_comm* comm, float* buf_dev, size_t n) {
 
 int tq_all_gather(tq_ctx* ctx, tq_comm* comm, const void* send_dev, void* recv_dev, size_t bytes_per_rank) {
   if (int st = bind(ctx)) return st;
+  ctx->inflight_unknown = true;   // a library kernel follows: later launches assume nothing about what runs
+  ctx->n_inflight = 0;
   if (bytes_per_rank == 0) return TQ_OK;
   TQ_REQUIRE(ctx, send_dev && recv_dev, "tq_all_gather: null buffer");
   if (!comm || comm->world == 1) {
@@ -152,6 +156,8 @@ int tq_all_gather(tq_ctx* ctx, tq_comm* comm, const void* send_dev, void* recv_d
 
 int tq_all_to_all(tq_ctx* ctx, tq_comm* comm, const void* send_dev, void* recv_dev, size_t bytes_per_peer) {
   if (int st = bind(ctx)) return st;
+  ctx->inflight_unknown = true;   // a library kernel follows: later launches assume nothing about what runs
+  ctx->n_inflight = 0;
   if (bytes_per_peer == 0) return TQ_OK;
   TQ_REQUIRE(ctx, send_dev && recv_dev, "tq_all_to_all: null buffer");
   if (!comm || comm->world == 1) {

@@ -20,6 +20,8 @@ int tq_graph_begin(tq_ctx* ctx) {
   TQ_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
   ctx->capturing = true;
   ctx->launches_at_capture = ctx->launches;
+  ctx->inflight_unknown = true;   // a graph starts after everything before it: its first kernel assumes nothing
+  ctx->n_inflight = 0;
   return TQ_OK;
 }
 
@@ -29,6 +31,8 @@ int tq_graph_end(tq_ctx* ctx, tq_graph** out) {
   *out = nullptr;
   TQ_REQUIRE(ctx, ctx->capturing, "tq_graph_end: no capture is open");
   ctx->capturing = false;
+  ctx->inflight_unknown = true;   // what was recorded has not run: later launches assume nothing about it
+  ctx->n_inflight = 0;
   tq_graph* g = new (std::nothrow) tq_graph();
   if (!g) return fail(ctx, TQ_ENOMEM, "out of host memory");
   g->kernels = ctx->launches - ctx->launches_at_capture;
@@ -50,6 +54,8 @@ int tq_graph_launch(tq_ctx* ctx, tq_graph* g) {
   TQ_REQUIRE(ctx, g && g->exec, "tq_graph_launch: null graph");
   TQ_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
   ctx->launches += g->kernels;
+  ctx->inflight_unknown = true;
+  ctx->n_inflight = 0;
   return TQ_OK;
 }
 

@@ -11,13 +11,19 @@
 #include "../../include/tangq.h"
 
 constexpr int kTileCounters = 1024;
+constexpr int kGemvSets = 4, kGemvMaxGrid = 512;   // flag words of the persistent GEMV: kGemvSets * kGemvMaxGrid * 2
 
 struct tq_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
   bool owns_stream = false;
   int* dev_err = nullptr;        // device status word written by kernels that give up a bounded wait,
-                                 // followed by kTileCounters zeroed tile counters (split-K meets)
+                                 // followed by kTileCounters zeroed tile counters (split-K meets of the tcgen05
+                                 // GEMM and the MoE router) and kTileCounters more for the persistent GEMV
+  float* gemv_ws = nullptr;      // [kGemvSets][kGemvMaxGrid][2][128] f32: the persistent GEMV's partial row blocks;
+                                 // consecutive launches rotate through the sets (at most three kernels ever have
+                                 // resident CTAs at a time: a CTA slot only frees when an older kernel's CTA exits)
+  unsigned gemv_seq = 0;
   int* host_err = nullptr;       // pinned copy target of dev_err: tq_sync reads the status with one stream wait
   void* xprep = nullptr;         // activation staging for tq_qlinear (bf16 copy / 3-way f32 split)
   size_t xprep_bytes = 0;
@@ -26,7 +32,15 @@ struct tq_ctx {
   void* splitk = nullptr;        // f32 partials of split-K GEMMs; separate because callers that carve
   size_t splitk_bytes = 0;       // their own buffers out of `scratch` run linear layers in between
   int sm_count = 148;
-  int cfg_wr = 0, cfg_wk = 0, cfg_stages = 0, cfg_tpw = 0;  // tq_qlinear_set_config override
+  // Kernels that may still be running when the next kernel launched with the programmatic-launch attribute
+  // starts: either exactly the previous one, with unknown outputs (`inflight_unknown`; every kernel but the
+  // persistent GEMV waits for its predecessor before it lets its successor be scheduled), or a run of
+  // persistent GEMVs whose inputs and outputs are the byte ranges listed here.  A GEMV whose activations
+  // overlap none of the outputs reads them without waiting and lets its own successor be scheduled at once; if
+  // its output and residual are clear of everything listed as well, it does not wait at all.
+  bool inflight_unknown = true;
+  int n_inflight = 0;
+  struct Range { uintptr_t lo, hi; bool written; } inflight[96];
   unsigned long long launches = 0;             // kernels launched through this context
   bool pdl = true;                             // programmatic dependent launch for the decode-path kernels
   bool capturing = false;                      // between tq_graph_begin and tq_graph_end
@@ -96,6 +110,8 @@ inline cudaError_t launch_k(tq_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
   ctx->launches++;
+  ctx->inflight_unknown = true;
+  ctx->n_inflight = 0;
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 

@@ -49,7 +49,6 @@ struct QGemmParams {
   const int* g_offsets;
   const int* g_active;    // optional: blockIdx.y indexes this list of group ids (-1 = unused entry)
   long long g_tile_stride, g_x_stride, g_y_stride;
-  int debug;                // tuning aid: 1 = consumers skip the math, 2 = producer re-reads the first K chunk
   int* err;
 };
 
@@ -161,7 +160,7 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
     // The weights do not depend on the previous kernel of the stream, the activations do: the first
     // ring-full of weight tiles is requested before griddepcontrol.wait, the activation rows after.
     auto issue = [&](int it, int s, bool weights, bool acts) {
-      const int kc0 = (p.debug == 2) ? 0 : it * KT;
+      const int kc0 = it * KT;
       const int kcs = min(KT, p.kc_total - kc0);                 // tiles along K in this stage
       const int kxv = max(0, min(KB, p.kx - kc0 * kTileK));       // activation elements in this stage
       const uint32_t wbytes = (uint32_t)(kcs * TB);
@@ -224,7 +223,7 @@ __global__ void __launch_bounds__(288, (NT == 1 ? 4 : (NT == 2 ? 3 : 1))) qgemm_
         atomicCAS(p.err, 0, (int)DERR_FULL_WAIT);
         break;
       }
-      const int nu = (rb_ok && p.debug != 1) ? min(TPW, p.kc_total - kc) : 0;       // tiles of this warp that exist
+      const int nu = rb_ok ? min(TPW, p.kc_total - kc) : 0;       // tiles of this warp that exist
 #pragma unroll 1
       for (int u = 0; u < nu; ++u) {
         const int st = st0 + u * TB;                               // tile u: weights shift by TB, activations by 256 B

@@ -9,6 +9,7 @@
 
 #include "internal.h"
 #include "qgemm_mma.cuh"
+#include "qgemv_sk.cuh"
 
 namespace tq {
 
@@ -179,12 +180,6 @@ static QgConfig choose_config(const tq_ctx* ctx, const tq_qweight* w, int mx, in
   if (c.nt == 8 && c.wk > 2) c.wk = 2;
   c.stages = 4;
   c.tpw = 1;
-  if (ctx->cfg_wr > 0) {
-    c.wr = ctx->cfg_wr;
-    c.wk = ctx->cfg_wk;
-    c.stages = ctx->cfg_stages;
-    c.tpw = ctx->cfg_tpw > 0 ? ctx->cfg_tpw : 1;
-  }
   while (c.wk > 1 && c.wk > w->n_kc) c.wk >>= 1;
   while (c.tpw > 1 && c.wk * c.tpw > w->n_kc) c.tpw >>= 1;
   // shrink until the CTA fits in shared memory
@@ -204,9 +199,111 @@ struct QgGroup {
   int max_active = 0;             // upper bound of how many groups can have rows (sizes gridDim.y)
 };
 
+// ---------------------------------------------------------------------------------------------
+// Persistent GEMV (qgemv_sk.cuh) for up to eight staged activation rows of an ungrouped weight.
+// Returns false when the shape does not fit it (the ring would be shorter than three stages);
+// the caller then uses the general kernel.
+// ---------------------------------------------------------------------------------------------
+constexpr int kSkWarps = 8, kSkTilesPerWarp = 2;
+
+template <int KIND, bool M1>
+static cudaError_t launch_sk_kernel(tq_ctx* ctx, const QGemvParams& p, unsigned grid, size_t smem) {
+  auto kern = qgemv_sk_kernel<KIND, kSkWarps, kSkTilesPerWarp, M1>;
+  static size_t attr_bytes[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
+  const int dev = ctx->device & 63;
+  if (smem > 48 * 1024 && attr_bytes[dev] < smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_bytes[dev] = smem;
+  }
+  return launch_k(ctx, kern, dim3(grid), dim3(32 * (kSkWarps + 2)), smem, p);
+}
+
+static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
+                            void* y, int y_dtype, size_t ldy, const float* residual, int* status) {
+  if (mx > 8) return false;
+  const bool m1 = mx == 1;
+  const int kx = w->n_kc * kTileK;
+  const size_t fixed = sk_fixed_bytes(w->kind, kSkWarps, kx, mx, m1);
+  const size_t stage = (size_t)kSkWarps * kSkTilesPerWarp * qk_tile_bytes(w->kind);
+  // Two CTAs per SM (this layer's and, under programmatic dependent launch, the next layer's) when the
+  // ring can still hold three stages that way; else one CTA with all of the SM's shared memory.
+  const size_t half = 113 * 1024, whole = 226 * 1024;
+  size_t budget = fixed + 3 * stage <= half ? half : whole;
+  if (fixed + 3 * stage > budget) return false;
+  int stages = (int)((budget - fixed) / stage);
+  if (stages > kSkMaxStages) stages = kSkMaxStages;
+  const long long units = (long long)w->n_rb * w->n_kc;
+  long long grid = ctx->sm_count;
+  if (grid > kGemvMaxGrid) grid = kGemvMaxGrid;
+  if (grid > units) grid = units;
+  QGemvParams p;
+  p.tiles = w->tiles;
+  p.row_scales = w->row_scales;
+  p.x = xs;
+  p.y = y;
+  p.residual = residual;
+  p.ldx = (long long)ldxs;
+  p.ldy = (long long)ldy;
+  p.n_units = units;
+  p.n_rows = (int)w->rows;
+  p.n_row_blocks = w->n_rb;
+  p.kc_total = w->n_kc;
+  p.kx = kx;
+  p.mx = mx;
+  p.m_out = mx / combine;
+  p.combine = combine;
+  p.y_bf16 = y_dtype == TQ_BF16;
+  p.stages = stages;
+  // The activations can be read without waiting for the previous kernel when that kernel is known not to write
+  // them.  Only on a stream of the context's own: on an adopted stream a foreign kernel that signals its
+  // dependents early could sit between the two launches.
+  struct R { uintptr_t lo, hi; };
+  const R rx = {(uintptr_t)xs, (uintptr_t)xs + ((size_t)(mx - 1) * ldxs + kx) * 2};
+  const size_t y_bytes = ((size_t)(p.m_out - 1) * ldy + w->rows) * (y_dtype == TQ_BF16 ? 2 : 4);
+  const R ry = {(uintptr_t)y, (uintptr_t)y + y_bytes};
+  const R rr = {(uintptr_t)residual, residual ? (uintptr_t)residual + ((size_t)(p.m_out - 1) * ldy + w->rows) * 4 : (uintptr_t)residual};
+  auto hit = [](const R& a, const tq_ctx::Range& b) { return a.lo < b.hi && b.lo < a.hi; };
+  int mode = (ctx->owns_stream && ctx->pdl && !ctx->inflight_unknown && ctx->n_inflight + 3 <= 96) ? 2 : 0;
+  for (int i = 0; mode && i < ctx->n_inflight; ++i) {
+    const tq_ctx::Range& f = ctx->inflight[i];
+    if (f.written && hit(rx, f)) mode = 0;                                     // x comes from a kernel that may still run
+    else if (hit(ry, f) || (f.written && hit(rr, f))) mode = 1;                // only the stores / the residual have to wait
+  }
+  // Running entirely unordered relies on the rotating workspace sets, i.e. on at most three kernels having
+  // resident CTAs at a time: full-size grids of CTAs so large that two fill an SM.
+  if (mode == 2 && !(grid == ctx->sm_count && fixed + (size_t)stages * stage > 80 * 1024)) mode = 1;
+  p.x_early = mode;
+  const unsigned set = ctx->gemv_seq++ % kGemvSets;
+  p.ws = ctx->gemv_ws + (size_t)set * kGemvMaxGrid * 2 * 128;
+  p.flags = ctx->dev_err + 1 + kTileCounters + set * kGemvMaxGrid * 2;
+  p.err = ctx->dev_err;
+  const size_t smem = fixed + (size_t)stages * stage;
+  cudaError_t e;
+  switch (w->kind) {
+    case TQ_Q4_F32: e = m1 ? launch_sk_kernel<Q4_F32, true>(ctx, p, (unsigned)grid, smem) : launch_sk_kernel<Q4_F32, false>(ctx, p, (unsigned)grid, smem); break;
+    case TQ_Q4_F16: e = m1 ? launch_sk_kernel<Q4_F16, true>(ctx, p, (unsigned)grid, smem) : launch_sk_kernel<Q4_F16, false>(ctx, p, (unsigned)grid, smem); break;
+    case TQ_Q8_F32: e = m1 ? launch_sk_kernel<Q8_F32, true>(ctx, p, (unsigned)grid, smem) : launch_sk_kernel<Q8_F32, false>(ctx, p, (unsigned)grid, smem); break;
+    default: e = m1 ? launch_sk_kernel<I8_ROW, true>(ctx, p, (unsigned)grid, smem) : launch_sk_kernel<I8_ROW, false>(ctx, p, (unsigned)grid, smem); break;
+  }
+  *status = e == cudaSuccess ? TQ_OK : fail(ctx, TQ_ECUDA, "persistent GEMV launch failed: %s", cudaGetErrorString(e));
+  if (e == cudaSuccess) {   // (launch_k has just marked the stream's state unknown)
+    if (mode == 0) ctx->n_inflight = 0;   // this kernel waits for everything before it
+    ctx->inflight_unknown = false;
+    ctx->inflight[ctx->n_inflight++] = {rx.lo, rx.hi, false};
+    ctx->inflight[ctx->n_inflight++] = {ry.lo, ry.hi, true};
+    if (residual) ctx->inflight[ctx->n_inflight++] = {rr.lo, rr.hi, false};
+  }
+  return true;
+}
+
 // One GEMM launch over <= 64 staged activation rows (per group, for grouped launches).
 static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
                         void* y, int y_dtype, size_t ldy, const float* residual, const QgGroup* grp = nullptr) {
+  if (!grp) {
+    int st = TQ_OK;
+    if (launch_qgemv_sk(ctx, w, xs, ldxs, mx, combine, y, y_dtype, ldy, residual, &st)) return st;
+  }
   const int n_groups = grp ? grp->n_groups : 1;
   const int n_rb = w->n_rb / n_groups;
   const size_t rows_g = w->rows / n_groups;
@@ -239,10 +336,6 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
   p.g_tile_stride = (long long)n_rb * w->n_kc * qk_tile_bytes(w->kind);
   p.g_x_stride = grp ? grp->x_stride : 0;
   p.g_y_stride = grp ? grp->y_stride : 0;
-  {
-    static const char* dbg = std::getenv("TQ_QGEMM_DEBUG");
-    p.debug = dbg ? std::atoi(dbg) : 0;
-  }
   const size_t smem = qg_smem_bytes(w->kind, c.nt, c.wr, c.wk, c.tpw, c.stages, mx);
   if (smem > 227 * 1024) return fail(ctx, TQ_EUNSUPPORTED, "tq_qlinear: launch needs %zu bytes of shared memory", smem);
   const int chunk = 8 * c.nt;
@@ -535,21 +628,6 @@ int tq_dequantize(tq_ctx* ctx, const tq_qweight* w, float* out_dev, int8_t* ints
                                                                          w->cols, w->n_kc, out_dev, ints_dev);
   ctx->launches++;
   TQ_CUDA(ctx, cudaGetLastError());
-  return TQ_OK;
-}
-
-int tq_qlinear_set_config(tq_ctx* ctx, int wr, int wk, int stages, int tiles_per_warp) {
-  if (!ctx) return TQ_EINVAL;
-  if (wr == 0) {
-    ctx->cfg_wr = ctx->cfg_wk = ctx->cfg_stages = ctx->cfg_tpw = 0;
-    return TQ_OK;
-  }
-  TQ_REQUIRE(ctx, wr > 0 && wk > 0 && wr * wk <= 8 && stages >= 2 && stages <= 8 && tiles_per_warp >= 1 && tiles_per_warp <= 8,
-             "tq_qlinear_set_config: need wr*wk <= 8, 2 <= stages <= 8, 1 <= tiles_per_warp <= 8");
-  ctx->cfg_wr = wr;
-  ctx->cfg_wk = wk;
-  ctx->cfg_stages = stages;
-  ctx->cfg_tpw = tiles_per_warp;
   return TQ_OK;
 }
 

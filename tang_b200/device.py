@@ -313,9 +313,6 @@ class QuantComputeDevice:
         """m stacked matvecs with host arrays: x [m, cols] -> y [m, rows]."""
         return self._matvec_host(w, x, m).reshape(m, w.rows)
 
-    def set_qlinear_config(self, wr: int = 0, wk: int = 0, stages: int = 0, tiles_per_warp: int = 1) -> None:
-        self._check(self._L.tq_qlinear_set_config(self._ctx, wr, wk, stages, tiles_per_warp))
-
     # ------------------------------------------------------------------ CUDA graphs
     def begin_capture(self) -> None:
         """``begin_capture`` (crates/tang-compute/src/cuda.rs:344)."""
