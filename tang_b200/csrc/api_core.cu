@@ -104,9 +104,11 @@ int tq_ctx_create(int device, void* stream, tq_ctx** out) {
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(TQ_ECUDA);
     ctx->owns_stream = true;
   }
-  if (cudaMalloc(&ctx->dev_err, (1 + kTileCounters + kGemvSets * kGemvMaxGrid * 2) * sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
-  if (cudaMemsetAsync(ctx->dev_err, 0, (1 + kTileCounters + kGemvSets * kGemvMaxGrid * 2) * sizeof(int), ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
-  if (cudaMalloc(&ctx->gemv_ws, (size_t)kGemvSets * kGemvMaxGrid * 2 * 128 * sizeof(float)) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMalloc(&ctx->dev_err, (1 + kTileCounters) * sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMemsetAsync(ctx->dev_err, 0, (1 + kTileCounters) * sizeof(int), ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
+  const size_t ws_bytes = (size_t)kGemvSets * kGemvMaxGrid * 2 * 128 * sizeof(unsigned long long);
+  if (cudaMalloc(&ctx->gemv_ws, ws_bytes) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMemsetAsync(ctx->gemv_ws, 0, ws_bytes, ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_err), sizeof(int), cudaHostAllocDefault) != cudaSuccess) return bail(TQ_ECUDA);
   *ctx->host_err = 0;
   if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
@@ -140,7 +142,8 @@ int tq_sync(tq_ctx* ctx) {
   TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   const int code = *ctx->host_err;
   if (code != 0) {
-    cudaMemset(ctx->dev_err, 0, (1 + kTileCounters + kGemvSets * kGemvMaxGrid * 2) * sizeof(int));   // a kernel that gave up may have left tile counters half counted
+    cudaMemset(ctx->dev_err, 0, (1 + kTileCounters) * sizeof(int));   // a kernel that gave up may have left tile counters half counted
+    cudaMemset(ctx->gemv_ws, 0, (size_t)kGemvSets * kGemvMaxGrid * 2 * 128 * sizeof(unsigned long long));   // ... or parked partial sums
     return fail(ctx, TQ_ETIMEOUT, "a kernel gave up a bounded wait (device code %d)", code);
   }
   return TQ_OK;

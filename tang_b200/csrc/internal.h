@@ -11,7 +11,7 @@
 #include "../../include/tangq.h"
 
 constexpr int kTileCounters = 1024;
-constexpr int kGemvSets = 4, kGemvMaxGrid = 512;   // flag words of the persistent GEMV: kGemvSets * kGemvMaxGrid * 2
+constexpr int kGemvSets = 6, kGemvMaxGrid = 512;
 
 struct tq_ctx {
   int device = 0;
@@ -20,7 +20,8 @@ struct tq_ctx {
   int* dev_err = nullptr;        // device status word written by kernels that give up a bounded wait,
                                  // followed by kTileCounters zeroed tile counters (split-K meets of the tcgen05
                                  // GEMM and the MoE router) and kTileCounters more for the persistent GEMV
-  float* gemv_ws = nullptr;      // [kGemvSets][kGemvMaxGrid][2][128] f32: the persistent GEMV's partial row blocks;
+  unsigned long long* gemv_ws = nullptr;   // [kGemvSets][kGemvMaxGrid][2][128] tagged f32 words: the persistent GEMV's
+                                 // partial row blocks, all zero whenever no GEMV is running;
                                  // consecutive launches rotate through the sets (at most three kernels ever have
                                  // resident CTAs at a time: a CTA slot only frees when an older kernel's CTA exits)
   unsigned gemv_seq = 0;

@@ -6,9 +6,10 @@
 //     the order they lie in HBM, [row block][k chunk]; CTA c of the grid owns units
 //     [c*U/grid, (c+1)*U/grid) — a contiguous byte range, the same size (+-1 tile) on every SM,
 //     so no SM carries a tail.  A row block cut by a range boundary is summed across its CTAs
-//     through a small f32 workspace: the higher CTAs park their partial sums and raise a flag at
-//     the start of their range, the lowest one adds them in CTA order at the end of its own (a
-//     bounded wait on flags set microseconds earlier) and stores, so results are bit-reproducible;
+//     through a small workspace: the higher CTAs park their partial sums (each word carries its own
+//     "present" tag) at the start of their range, the lowest one adds them in CTA order at the end
+//     of its own (a bounded wait on words written microseconds earlier) and stores, so results are
+//     bit-reproducible;
 //   * one elected lane streams the range through an S-stage mbarrier ring, ONE bulk (TMA) copy of
 //     up to G tiles per stage (L2 evict-first); the first ring-full is requested before
 //     griddepcontrol.wait, so under programmatic dependent launch the next layer's weights are
@@ -49,8 +50,8 @@ struct QGemvParams {
   int x_early;              // 1: no kernel that may still be running writes x: load it without waiting;
                             // 2: nor does any of them touch y or the residual, or write x: nothing here waits
                             //    (the workspace pointers below are then this launch's own set)
-  float* ws;                // [gridDim.x][2][128] f32: partial sums of row blocks cut by a range boundary
-  int* flags;               // [gridDim.x][2]: 1 = the partial in that slot is complete; zero between launches
+  unsigned long long* ws;   // [gridDim.x][2][128] (value bits | 1 << 32): partial sums of row blocks cut by a range
+                            // boundary; the tag in the upper half says the value is there; all zero between launches
   int* err;
 };
 
@@ -82,18 +83,20 @@ struct SkWalk {
 __device__ __forceinline__ void dequant_q4_word_offset(uint32_t w, uint32_t (&out)[4]) {
   constexpr uint32_t kMask = 0x000F000Fu, kMagic = 0x43004300u;
   out[0] = lop3_and_or(w, kMask, kMagic);
+  // (the shifts as upper halves of multiplications, to move them off the half-rate ALU pipe, measured slower:
+  // 5.8 -> 7.8 us per launch)
   out[1] = lop3_and_or(w >> 4, kMask, kMagic);
   out[2] = lop3_and_or(w >> 8, kMask, kMagic);
   out[3] = lop3_and_or(w >> 12, kMask, kMagic);
 }
 
-__device__ __forceinline__ int ld_acquire(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -389,7 +392,7 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemv_sk_kernel(const QGem
       }
     };
     // A row block cut by range boundaries belongs to CTAs c_first..c_last.  The higher ones park their partial
-    // sums in the workspace and raise a flag (the block is the first thing they work on); the lowest one, for
+    // sums in the workspace (the block is the first thing they work on); the lowest one, for
     // which the block is the LAST segment of its range, finishes it: it fetches the parked partials while its own
     // warps still compute (from three row blocks before the end, without blocking until the very end).
     const long long last_u = u1 - 1;
@@ -404,24 +407,34 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemv_sk_kernel(const QGem
       const int c_rb0 = (int)((U * c / grid) / p.kc_total);   // first row block of CTA c
       return c * 2 + (c_rb0 == last_rb ? 0 : 1);
     };
+    // A parked partial is 128 words of (value bits | tag << 32), each written with one 64-bit store: a word is
+    // there when its tag is, so neither side needs a fence or a separate flag, and the reader clears what it took.
+    int next_peer = (int)blockIdx.x + 1;
     auto fetch_peers = [&](bool blocking) -> bool {            // false: gave up (only when blocking)
-      for (int c = (int)blockIdx.x + 1; c <= fin_last; ++c) {
-        const int* flag = p.flags + peer_slot(c);
+      while (next_peer <= fin_last) {
+        unsigned long long* part = p.ws + (size_t)peer_slot(next_peer) * 128;
+        unsigned long long got[4];
         uint32_t polls = 0;
-        while (ld_acquire(flag) == 0) {
+        for (;;) {
+          bool ready = true;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            got[i] = 1ull << 32;
+            if (lane + 32 * i < n_out) got[i] = ld_relaxed_u64(part + lane + 32 * i);
+            ready = ready && (got[i] >> 32) != 0;
+          }
+          if (__all_sync(0xffffffffu, ready)) break;
           if (!blocking) return true;                           // not there yet: try again later
           if (++polls > kMaxPolls || *failed) return false;
-          __nanosleep(64);
+          __nanosleep(32);
         }
-      }
-      for (int c = (int)blockIdx.x + 1; c <= fin_last; ++c) {
-        const int slot = peer_slot(c);
-        const float* part = p.ws + (size_t)slot * 128;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          if (lane + 32 * i < n_out) others[i] += __ldcg(part + lane + 32 * i);
-        __syncwarp();
-        if (lane == 0) p.flags[slot] = 0;   // ready for the next launch
+          if (lane + 32 * i < n_out) {
+            others[i] += __uint_as_float((uint32_t)got[i]);     // higher k ranges in CTA order
+            st_relaxed_u64(part + lane + 32 * i, 0ull);         // ready for the next launch that uses this set
+          }
+        ++next_peer;
       }
       fetched = true;
       return true;
@@ -473,13 +486,10 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemv_sk_kernel(const QGem
         store(w.rb, vals);
       } else {
         const int slot = (int)blockIdx.x * 2 + (first_seg ? 0 : 1);
-        float* mine = p.ws + (size_t)slot * 128;
+        unsigned long long* mine = p.ws + (size_t)slot * 128;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          if (lane + 32 * i < n_out) mine[lane + 32 * i] = vals[i];
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) st_release(p.flags + slot, 1);
+          if (lane + 32 * i < n_out) st_relaxed_u64(mine + lane + 32 * i, (1ull << 32) | __float_as_uint(vals[i]));
       }
       first_seg = false;
       w.left -= seg;

@@ -204,11 +204,11 @@ struct QgGroup {
 // Returns false when the shape does not fit it (the ring would be shorter than three stages);
 // the caller then uses the general kernel.
 // ---------------------------------------------------------------------------------------------
-constexpr int kSkWarps = 8, kSkTilesPerWarp = 2;
-
-template <int KIND, bool M1>
+// Two CTA shapes, both with 16 tiles per stage: 8 warps x 2 tiles for a kernel that has an SM to itself (it waits
+// for its activations: only its ring fills early), 4 warps x 4 tiles for kernels that run four to an SM.
+template <int KIND, bool M1, int W, int TPW, int MINB>
 static cudaError_t launch_sk_kernel(tq_ctx* ctx, const QGemvParams& p, unsigned grid, size_t smem) {
-  auto kern = qgemv_sk_kernel<KIND, kSkWarps, kSkTilesPerWarp, M1>;
+  auto kern = qgemv_sk_kernel<KIND, W, TPW, M1, MINB>;
   static size_t attr_bytes[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
   const int dev = ctx->device & 63;
   if (smem > 48 * 1024 && attr_bytes[dev] < smem) {
@@ -216,7 +216,13 @@ static cudaError_t launch_sk_kernel(tq_ctx* ctx, const QGemvParams& p, unsigned 
     if (e != cudaSuccess) return e;
     attr_bytes[dev] = smem;
   }
-  return launch_k(ctx, kern, dim3(grid), dim3(32 * (kSkWarps + 2)), smem, p);
+  return launch_k(ctx, kern, dim3(grid), dim3(32 * (W + 2)), smem, p);
+}
+
+template <int KIND>
+static cudaError_t launch_sk_kind(tq_ctx* ctx, const QGemvParams& p, unsigned grid, size_t smem, bool m1, bool small) {
+  if (small) return m1 ? launch_sk_kernel<KIND, true, 4, 4, 4>(ctx, p, grid, smem) : launch_sk_kernel<KIND, false, 4, 4, 4>(ctx, p, grid, smem);
+  return m1 ? launch_sk_kernel<KIND, true, 8, 2, 3>(ctx, p, grid, smem) : launch_sk_kernel<KIND, false, 8, 2, 3>(ctx, p, grid, smem);
 }
 
 static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
@@ -224,19 +230,49 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   if (mx > 8) return false;
   const bool m1 = mx == 1;
   const int kx = w->n_kc * kTileK;
-  const size_t fixed = sk_fixed_bytes(w->kind, kSkWarps, kx, mx, m1);
-  const size_t stage = (size_t)kSkWarps * kSkTilesPerWarp * qk_tile_bytes(w->kind);
-  // Two CTAs per SM (this layer's and, under programmatic dependent launch, the next layer's) when the
-  // ring can still hold three stages that way; else one CTA with all of the SM's shared memory.
-  const size_t half = 113 * 1024, whole = 226 * 1024;
-  size_t budget = fixed + 3 * stage <= half ? half : whole;
-  if (fixed + 3 * stage > budget) return false;
-  int stages = (int)((budget - fixed) / stage);
-  if (stages > kSkMaxStages) stages = kSkMaxStages;
+  const size_t stage = (size_t)16 * qk_tile_bytes(w->kind);
   const long long units = (long long)w->n_rb * w->n_kc;
   long long grid = ctx->sm_count;
   if (grid > kGemvMaxGrid) grid = kGemvMaxGrid;
   if (grid > units) grid = units;
+  // What may still be running when this kernel starts decides how it is launched: 0 = it waits for its
+  // activations, 1 = it reads them at once and only its stores wait, 2 = nothing in flight touches its operands.
+  // Only on a stream of the context's own: on an adopted stream a foreign kernel that lets its dependents start
+  // early could sit between two of these launches.
+  struct R { uintptr_t lo, hi; };
+  const int m_out = mx / combine;
+  const R rx = {(uintptr_t)xs, (uintptr_t)xs + ((size_t)(mx - 1) * ldxs + kx) * 2};
+  const R ry = {(uintptr_t)y, (uintptr_t)y + ((size_t)(m_out - 1) * ldy + w->rows) * (y_dtype == TQ_BF16 ? 2 : 4)};
+  const R rr = {(uintptr_t)residual, residual ? (uintptr_t)residual + ((size_t)(m_out - 1) * ldy + w->rows) * 4 : (uintptr_t)residual};
+  auto hit = [](const R& a, const tq_ctx::Range& b) { return a.lo < b.hi && b.lo < a.hi; };
+  int mode = (ctx->owns_stream && ctx->pdl && !ctx->inflight_unknown && ctx->n_inflight + 3 <= 96) ? 2 : 0;
+  for (int i = 0; mode && i < ctx->n_inflight; ++i) {
+    const tq_ctx::Range& f = ctx->inflight[i];
+    if (f.written && hit(rx, f)) mode = 0;                                     // x comes from a kernel that may still run
+    else if (hit(ry, f) || (f.written && hit(rr, f))) mode = 1;                // only the stores / the residual have to wait
+  }
+  // Shared memory per CTA.  Kernels that wait for nothing run side by side: four small CTAs per SM (a two-stage
+  // ring each) keep the most copies in flight and the most warps busy (measured per 14336 x 4096 launch: 5.8 us,
+  // against 6.3 us for three CTAs of eight warps and 6.9 us for two).  A kernel that waits for its activations
+  // takes more than half of an SM's shared memory: its ring fills while the small kernels before it run (they
+  // still fit beside it), and no SM can be handed two of its CTAs (a decode step measured 2.48 ms with CTAs
+  // that fit twice, 2.00 ms so).
+  const size_t quarter = 56 * 1024, third = 74 * 1024, half = 113 * 1024, most = 150 * 1024, whole = 226 * 1024;
+  const bool small = mode == 2 && sk_fixed_bytes(w->kind, 4, kx, mx, m1) + 2 * stage <= quarter;
+  const size_t fixed = sk_fixed_bytes(w->kind, small ? 4 : 8, kx, mx, m1);
+  size_t budget = whole;
+  if (small) budget = quarter;
+  else if (mode == 2 && fixed + 3 * stage <= third) budget = third;
+  else if (mode != 0 && fixed + 3 * stage <= half) budget = half;
+  else if (fixed + 3 * stage <= most) budget = most;
+  if (!small && fixed + 3 * stage > budget) return false;
+  int stages = (int)((budget - fixed) / stage);
+  if (stages > kSkMaxStages) stages = kSkMaxStages;
+  const size_t smem = fixed + (size_t)stages * stage;
+  // Running entirely unordered relies on the rotating workspace sets: a CTA only leaves once the kernel before
+  // its own has completed, so kernel n and kernel n + kGemvSets can both have resident CTAs only if kGemvSets - 1
+  // whole grids fit beside one more CTA.  Full-size grids and a CTA count per SM below the number of sets rule it out.
+  if (mode == 2 && !(grid == ctx->sm_count && (int)(233472 / (smem + 1024)) + 1 <= kGemvSets)) mode = 1;
   QGemvParams p;
   p.tiles = w->tiles;
   p.row_scales = w->row_scales;
@@ -251,40 +287,20 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   p.kc_total = w->n_kc;
   p.kx = kx;
   p.mx = mx;
-  p.m_out = mx / combine;
+  p.m_out = m_out;
   p.combine = combine;
   p.y_bf16 = y_dtype == TQ_BF16;
   p.stages = stages;
-  // The activations can be read without waiting for the previous kernel when that kernel is known not to write
-  // them.  Only on a stream of the context's own: on an adopted stream a foreign kernel that signals its
-  // dependents early could sit between the two launches.
-  struct R { uintptr_t lo, hi; };
-  const R rx = {(uintptr_t)xs, (uintptr_t)xs + ((size_t)(mx - 1) * ldxs + kx) * 2};
-  const size_t y_bytes = ((size_t)(p.m_out - 1) * ldy + w->rows) * (y_dtype == TQ_BF16 ? 2 : 4);
-  const R ry = {(uintptr_t)y, (uintptr_t)y + y_bytes};
-  const R rr = {(uintptr_t)residual, residual ? (uintptr_t)residual + ((size_t)(p.m_out - 1) * ldy + w->rows) * 4 : (uintptr_t)residual};
-  auto hit = [](const R& a, const tq_ctx::Range& b) { return a.lo < b.hi && b.lo < a.hi; };
-  int mode = (ctx->owns_stream && ctx->pdl && !ctx->inflight_unknown && ctx->n_inflight + 3 <= 96) ? 2 : 0;
-  for (int i = 0; mode && i < ctx->n_inflight; ++i) {
-    const tq_ctx::Range& f = ctx->inflight[i];
-    if (f.written && hit(rx, f)) mode = 0;                                     // x comes from a kernel that may still run
-    else if (hit(ry, f) || (f.written && hit(rr, f))) mode = 1;                // only the stores / the residual have to wait
-  }
-  // Running entirely unordered relies on the rotating workspace sets, i.e. on at most three kernels having
-  // resident CTAs at a time: full-size grids of CTAs so large that two fill an SM.
-  if (mode == 2 && !(grid == ctx->sm_count && fixed + (size_t)stages * stage > 80 * 1024)) mode = 1;
   p.x_early = mode;
   const unsigned set = ctx->gemv_seq++ % kGemvSets;
   p.ws = ctx->gemv_ws + (size_t)set * kGemvMaxGrid * 2 * 128;
-  p.flags = ctx->dev_err + 1 + kTileCounters + set * kGemvMaxGrid * 2;
   p.err = ctx->dev_err;
-  const size_t smem = fixed + (size_t)stages * stage;
   cudaError_t e;
   switch (w->kind) {
-    case TQ_Q4_F32: e = m1 ? launch_sk_kernel<Q4_F32, true>(ctx, p, (unsigned)grid, smem) : launch_sk_kernel<Q4_F32, false>(ctx, p, (unsigned)grid, smem); break;
-    case TQ_Q4_F16: e = m1 ? launch_sk_kernel<Q4_F16, true>(ctx, p, (unsigned)grid, smem) : launch_sk_kernel<Q4_F16, false>(ctx, p, (unsigned)grid, smem); break;
-    case TQ_Q8_F32: e = m1 ? launch_sk_kernel<Q8_F32, true>(ctx, p, (unsigned)grid, smem) : launch_sk_kernel<Q8_F32, false>(ctx, p, (unsigned)grid, smem); break;
-    default: e = m1 ? launch_sk_kernel<I8_ROW, true>(ctx, p, (unsigned)grid, smem) : launch_sk_kernel<I8_ROW, false>(ctx, p, (unsigned)grid, smem); break;
+    case TQ_Q4_F32: e = launch_sk_kind<Q4_F32>(ctx, p, (unsigned)grid, smem, m1, small); break;
+    case TQ_Q4_F16: e = launch_sk_kind<Q4_F16>(ctx, p, (unsigned)grid, smem, m1, small); break;
+    case TQ_Q8_F32: e = launch_sk_kind<Q8_F32>(ctx, p, (unsigned)grid, smem, m1, small); break;
+    default: e = launch_sk_kind<I8_ROW>(ctx, p, (unsigned)grid, smem, m1, small); break;
   }
   *status = e == cudaSuccess ? TQ_OK : fail(ctx, TQ_ECUDA, "persistent GEMV launch failed: %s", cudaGetErrorString(e));
   if (e == cudaSuccess) {   // (launch_k has just marked the stream's state unknown)
