@@ -287,6 +287,12 @@ TQ_API int tq_llama_set_head(tq_llama* model, const void* embed_bf16_dev, const 
  * can prefill them; seq_stride_elems = elements between sequences. */
 TQ_API int tq_llama_kv_cache(tq_llama* model, size_t layer, void** k_cache_dev, void** v_cache_dev,
                              size_t* seq_stride_elems);
+/* KVCache::trim_to (crates/tang-infer/src/kv_cache.rs:138-149), for every layer and for each of `batch` sequences
+ * at once: seq_lens_io_dev[b] is the number of positions sequence b holds (its next position); a sequence that
+ * holds more than `keep` drops its OLDEST positions -- rows [len - keep, len) of its K and V caches move to
+ * [0, keep) -- and its length becomes `keep`; shorter sequences are untouched.  The K rows keep the rotation of
+ * the positions they were appended at, exactly as the reference's trimmed cache does.  Asynchronous. */
+TQ_API int tq_llama_kv_trim(tq_llama* model, int* seq_lens_io_dev, size_t batch, size_t keep);
 /* The f32 residual stream [max_batch, d_model] after the last tq_llama_decode (before the final
  * norm's residual add is applied to it: it holds h after the last attention block). */
 TQ_API int tq_llama_hidden(tq_llama* model, float** hidden_dev);
@@ -296,6 +302,13 @@ TQ_API int tq_llama_hidden(tq_llama* model, float** hidden_dev);
  * vocabulary slices).  Asynchronous; capturable once run eagerly. */
 TQ_API int tq_llama_decode(tq_llama* model, const int* token_ids_dev, const int* positions_dev, size_t batch,
                            size_t max_len, float* logits_dev);
+/* The same step for caches that have been trimmed (tq_llama_kv_trim): sequence b's K/V are appended at cache row
+ * positions_dev[b] and positions 0..positions_dev[b] are attended, but the rotation of its q and k uses
+ * rope_positions_dev[b], the caller's running position count (model.forward(&[tok], cache, pos) with a cache whose
+ * seq_len is no longer pos, smollm.rs:535 + kv_cache.rs:138-149).  Both stay below max_seq.  NULL rope positions =
+ * tq_llama_decode. */
+TQ_API int tq_llama_decode_at(tq_llama* model, const int* token_ids_dev, const int* positions_dev, const int* rope_positions_dev,
+                              size_t batch, size_t max_len, float* logits_dev);
 /* The same step for a chunk of q_len new tokens per sequence (prompt processing): token_ids [batch][q_len],
  * sequence b's chunk starts at position cache_start[b] (its earlier positions are in the cache already).
  * Appends the chunk's K/V rows, runs causal attention over cache + chunk (tq_gqa_prefill) and the linear layers
@@ -366,7 +379,9 @@ TQ_API int tq_mla_unabsorb(tq_ctx* ctx, const tq_qweight* w_uv_stacked, const vo
  * asynchronous call made on the context between begin and end is recorded instead of run, and
  * replayed by tq_graph_launch.  Calls that allocate or synchronise (uploads, downloads, _host
  * calls, the first tq_qlinear that needs a larger staging buffer) must not be made while
- * capturing: run the sequence once eagerly first. */
+ * capturing: run the sequence once eagerly first.  The recorded kernels hold the addresses of the
+ * context's workspaces; when a later call makes one of them grow (it is freed and reallocated),
+ * tq_graph_launch of a graph recorded before that fails with TQ_EINVAL: record the graph again. */
 typedef struct tq_graph tq_graph;
 TQ_API int tq_graph_begin(tq_ctx* ctx);
 TQ_API int tq_graph_end(tq_ctx* ctx, tq_graph** out);

@@ -383,10 +383,21 @@ def qweight(kind, scales, payload, rows, cols) -> QWeight:
 
 
 def llama_layer_f64(dims: LlamaDims, layer: LlamaLayer, hidden: np.ndarray, k_cache: np.ndarray,
-                    v_cache: np.ndarray, pos: int, threads: int = 0) -> None:
+                    v_cache: np.ndarray, pos: int, threads: int = 0, rope_pos: int | None = None) -> None:
+    """One decode token through one block: appended at cache row `pos`, rotated for position `rope_pos` (= pos unless
+    the cache has been trimmed)."""
     assert hidden.dtype == np.float64 and k_cache.dtype == np.uint16 and v_cache.dtype == np.uint16
-    lib().orc_llama_layer_f64(C.byref(dims), C.byref(layer), _ptr(hidden), _ptr(k_cache), _ptr(v_cache),
-                              C.c_uint64(pos), C.c_int(threads))
+    lib().orc_llama_layer_at_f64(C.byref(dims), C.byref(layer), _ptr(hidden), _ptr(k_cache), _ptr(v_cache),
+                                 C.c_uint64(pos), C.c_uint64(pos if rope_pos is None else rope_pos), C.c_int(threads))
+
+
+def kv_trim_to(rows: np.ndarray, seq_len: int, keep: int) -> int:
+    """``KVCache::trim_to(keep)`` (crates/tang-infer/src/kv_cache.rs:138-149) on one layer's rows [>= seq_len, kv_dim] of
+    16-bit elements, in place; returns the new seq_len."""
+    assert rows.dtype == np.uint16 and rows.ndim == 2 and rows.flags.c_contiguous
+    f = lib().orc_kv_trim_to
+    f.restype = C.c_uint64
+    return int(f(_ptr(rows), C.c_uint64(seq_len), C.c_uint64(rows.shape[1]), C.c_uint64(keep)))
 
 
 def llama_head_f64(dims: LlamaDims, final_norm_bf16: np.ndarray, lm_head: QWeight, hidden: np.ndarray,

@@ -153,8 +153,8 @@ ORC_API void orc_quantize_q8(const float* data, size_t n, float* scales, int8_t*
     for (size_t i = 0; i < kBlock; ++i) out[i] = 0;
     for (size_t i = start; i < end; ++i) {
       float r = std::round(data[i] * inv_scale);
-      r = std::fmin(std::fmax(r, -128.0f), 127.0f);
-      out[i - start] = (int8_t)r;
+      // f32::clamp keeps NaN and `NaN as i8` is 0; fmin/fmax would turn the NaN into a bound
+      out[i - start] = std::isnan(r) ? (int8_t)0 : (int8_t)std::fmin(std::fmax(r, -128.0f), 127.0f);
     }
     scales[b] = scale;
   }
@@ -183,11 +183,11 @@ ORC_API void orc_quantize_q4(const float* data, size_t n, float* scales, uint8_t
       int v0 = 0, v1 = 0;
       if (idx < len) {
         float r = std::round(data[start + idx] * inv_scale);
-        v0 = (int)std::fmin(std::fmax(r, -8.0f), 7.0f);
+        v0 = std::isnan(r) ? 0 : (int)std::fmin(std::fmax(r, -8.0f), 7.0f);   // `NaN.clamp(..) as i8` is 0
       }
       if (idx + 1 < len) {
         float r = std::round(data[start + idx + 1] * inv_scale);
-        v1 = (int)std::fmin(std::fmax(r, -8.0f), 7.0f);
+        v1 = std::isnan(r) ? 0 : (int)std::fmin(std::fmax(r, -8.0f), 7.0f);
       }
       packed[b * (kBlock / 2) + i] = (uint8_t)((uint8_t)(v0 + 8) | ((uint8_t)(v1 + 8) << 4));
     }

@@ -72,8 +72,16 @@ struct OrcLlamaDims {
 // k_cache / v_cache are this layer's bf16 caches, [max_seq, n_kv_heads*head_dim] row-major
 // (crates/tang-infer/src/kv_cache.rs:12-24); row `pos` is written (append, kv_cache.rs:76-107)
 // and rows 0..=pos are attended.
+// After KVCache::trim_to (kv_cache.rs:138-149) the row a token is appended at (the cache's seq_len, `pos` here)
+// and the position its rotation uses (the caller's running count, `rope_pos`) are no longer the same number.
+ORC_API void orc_llama_layer_at_f64(const OrcLlamaDims* dims, const OrcLlamaLayer* L, double* hidden,
+                                    uint16_t* k_cache, uint16_t* v_cache, uint64_t pos, uint64_t rope_pos, int threads);
 ORC_API void orc_llama_layer_f64(const OrcLlamaDims* dims, const OrcLlamaLayer* L, double* hidden,
                                  uint16_t* k_cache, uint16_t* v_cache, uint64_t pos, int threads) {
+  orc_llama_layer_at_f64(dims, L, hidden, k_cache, v_cache, pos, pos, threads);
+}
+ORC_API void orc_llama_layer_at_f64(const OrcLlamaDims* dims, const OrcLlamaLayer* L, double* hidden,
+                                    uint16_t* k_cache, uint16_t* v_cache, uint64_t pos, uint64_t rope_pos, int threads) {
   const size_t d = dims->d_model, nh = dims->n_heads, nkv = dims->n_kv_heads, hd = dims->head_dim;
   const size_t kv_dim = nkv * hd, q_dim = nh * hd, ffn = dims->ffn;
 
@@ -86,8 +94,8 @@ ORC_API void orc_llama_layer_f64(const OrcLlamaDims* dims, const OrcLlamaLayer* 
   orc_qmatmul(L->wq.kind, L->wq.scales, L->wq.payload, q_dim, d, normed.data(), 1, q.data(), threads);
   orc_qmatmul(L->wk.kind, L->wk.scales, L->wk.payload, kv_dim, d, normed.data(), 1, k.data(), threads);
   orc_qmatmul(L->wv.kind, L->wv.scales, L->wv.payload, kv_dim, d, normed.data(), 1, v.data(), threads);
-  orc_rope_heads_f64(q.data(), qr.data(), nh, hd, pos, dims->rope_base);
-  orc_rope_heads_f64(k.data(), kr.data(), nkv, hd, pos, dims->rope_base);
+  orc_rope_heads_f64(q.data(), qr.data(), nh, hd, rope_pos, dims->rope_base);
+  orc_rope_heads_f64(k.data(), kr.data(), nkv, hd, rope_pos, dims->rope_base);
   round_bf16_inplace(qr);  // bf16 query entering attention
 
   for (size_t i = 0; i < kv_dim; ++i) {  // cache.append: bf16 storage
@@ -119,6 +127,15 @@ ORC_API void orc_llama_layer_f64(const OrcLlamaDims* dims, const OrcLlamaLayer* 
   round_bf16_inplace(act);  // bf16 activation entering down
   orc_qmatmul(L->down.kind, L->down.scales, L->down.payload, d, ffn, act.data(), 1, dn.data(), threads);
   for (size_t i = 0; i < d; ++i) hidden[i] += dn[i];
+}
+
+// KVCache::trim_to (crates/tang-infer/src/kv_cache.rs:138-149) on one layer's cache rows [seq_len, kv_dim] (any 16-bit
+// element): the first seq_len - keep rows are drained, the rest move to the front.  Returns the new seq_len.
+ORC_API uint64_t orc_kv_trim_to(uint16_t* rows, uint64_t seq_len, uint64_t kv_dim, uint64_t keep) {
+  if (seq_len <= keep) return seq_len;
+  const uint64_t drop_elems = (seq_len - keep) * kv_dim;
+  std::memmove(rows, rows + drop_elems, keep * kv_dim * sizeof(uint16_t));
+  return keep;
 }
 
 // smollm.rs:255-296 tail: final RMSNorm, then the LM head on the (single) last row.

@@ -77,6 +77,8 @@ PROTOTYPES = {
     "tq_llama_set_layer": (_i, [_p, _sz, _p, _p, _p, _p, _p, _p]),
     "tq_llama_set_head": (_i, [_p, _p, _p, _p]),
     "tq_llama_kv_cache": (_i, [_p, _sz, _pp, _pp, C.POINTER(_sz)]),
+    "tq_llama_decode_at": (_i, [_p, _p, _p, _p, _sz, _sz, _p]),
+    "tq_llama_kv_trim": (_i, [_p, _p, _sz, _sz]),
     "tq_llama_hidden": (_i, [_p, _pp]),
     "tq_llama_decode": (_i, [_p, _p, _p, _sz, _sz, _p]),
     "tq_llama_prefill": (_i, [_p, _p, _p, _sz, _sz, _p]),

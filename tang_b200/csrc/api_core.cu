@@ -18,6 +18,7 @@ int ensure_xprep(tq_ctx* ctx, size_t bytes) {
     TQ_CUDA(ctx, cudaFree(ctx->xprep));
     ctx->xprep = nullptr;
     ctx->xprep_bytes = 0;
+    ctx->ws_generation++;
   }
   size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
   TQ_CUDA(ctx, cudaMalloc(&ctx->xprep, want));
@@ -34,6 +35,7 @@ int ensure_scratch(tq_ctx* ctx, size_t bytes) {
     TQ_CUDA(ctx, cudaFree(ctx->scratch));
     ctx->scratch = nullptr;
     ctx->scratch_bytes = 0;
+    ctx->ws_generation++;
   }
   size_t want = bytes < (4u << 20) ? (4u << 20) : bytes;
   TQ_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
@@ -50,6 +52,7 @@ int ensure_splitk(tq_ctx* ctx, size_t bytes) {
     TQ_CUDA(ctx, cudaFree(ctx->splitk));
     ctx->splitk = nullptr;
     ctx->splitk_bytes = 0;
+    ctx->ws_generation++;
   }
   size_t want = bytes < (8u << 20) ? (8u << 20) : bytes;
   TQ_CUDA(ctx, cudaMalloc(&ctx->splitk, want));
@@ -144,6 +147,8 @@ int tq_sync(tq_ctx* ctx) {
   if (code != 0) {
     cudaMemset(ctx->dev_err, 0, (1 + kTileCounters) * sizeof(int));   // a kernel that gave up may have left tile counters half counted
     cudaMemset(ctx->gemv_ws, 0, (size_t)kGemvSets * kGemvMaxGrid * 2 * 128 * sizeof(unsigned long long));   // ... or parked partial sums
+    if (code == 6)   // DERR_POSITION
+      return fail(ctx, TQ_EINVAL, "a sequence position outside the KV cache reached a kernel (the access was skipped): positions must stay below max_seq");
     return fail(ctx, TQ_ETIMEOUT, "a kernel gave up a bounded wait (device code %d)", code);
   }
   return TQ_OK;

@@ -75,11 +75,11 @@ __global__ void __launch_bounds__(kAttnThreads) gqa_decode_kernel(const GqaParam
   pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int len = p.lens[b];
+  const size_t row_elems = (size_t)p.n_kv * kHD;
+  const int len = min(p.lens[b], (int)(p.seq_stride / row_elems));   // never past the sequence's rows
   const int k_begin = split * p.chunk;
   const int k_end = min(len, k_begin + p.chunk);
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
-  const size_t row_elems = (size_t)p.n_kv * kHD;
   const __nv_bfloat16* kbase = p.k_cache + (size_t)b * p.seq_stride + (size_t)kvh * kHD;
   const __nv_bfloat16* vbase = p.v_cache + (size_t)b * p.seq_stride + (size_t)kvh * kHD;
 
@@ -301,6 +301,7 @@ struct PrefillParams {
   float scale;
   void* out;                     // [B][q_len][n_heads*kHD]
   int out_f32;
+  int* err;                      // the context's status word
 };
 
 __global__ void __launch_bounds__(kAttnThreads) gqa_prefill_kernel(const PrefillParams p) {
@@ -313,11 +314,17 @@ __global__ void __launch_bounds__(kAttnThreads) gqa_prefill_kernel(const Prefill
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int pos_per_cta = 64 / p.group;
   const int pos0 = blockIdx.x * pos_per_cta;                     // first query position of this CTA
+  const size_t row_elems = (size_t)p.n_kv * kHD;
   const int start = p.cache_start[b];
+  // The chunk must lie inside the sequence's cache rows (cache_start comes from device memory): if not, nothing
+  // is read or written for this sequence and the status word says why.
+  if (start < 0 || (size_t)start + (size_t)p.q_len > p.seq_stride / row_elems) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && kvh == 0) atomicCAS(p.err, 0, (int)DERR_POSITION);
+    return;
+  }
   const int last_pos = min(p.q_len, pos0 + pos_per_cta) - 1;     // last live query position
   const int k_end = start + last_pos + 1;                        // keys this CTA needs (causal)
   const int n_tiles = (k_end + kTileKeys - 1) / kTileKeys;
-  const size_t row_elems = (size_t)p.n_kv * kHD;
   const __nv_bfloat16* kbase = p.k_cache + (size_t)b * p.seq_stride + (size_t)kvh * kHD;
   const __nv_bfloat16* vbase = p.v_cache + (size_t)b * p.seq_stride + (size_t)kvh * kHD;
 
@@ -551,10 +558,10 @@ int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const voi
     p.part_ml = p.part_o + n_part * kHD;
   }
   const size_t smem = 4 * (size_t)kTileKeys * kRowBytes;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
+  if (!attr_set[ctx->device & 63]) {
     TQ_CUDA(ctx, cudaFuncSetAttribute(gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
+    attr_set[ctx->device & 63] = true;
   }
   dim3 grid((unsigned)n_splits, (unsigned)n_kv, (unsigned)B);
   TQ_CUDA(ctx, launch_k(ctx, gqa_decode_kernel, grid, dim3(kAttnThreads), smem, p));
@@ -605,11 +612,12 @@ int tq_gqa_prefill(tq_ctx* ctx, const void* q_dev, const void* k_cache_dev, cons
   p.scale = 1.0f / sqrtf((float)head_dim);
   p.out = out_dev;
   p.out_f32 = out_dtype == TQ_F32;
+  p.err = ctx->dev_err;
   const size_t smem = 4 * (size_t)kTileKeys * kRowBytes;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};   // per device, as above
+  if (!attr_set[ctx->device & 63]) {
     TQ_CUDA(ctx, cudaFuncSetAttribute(gqa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
+    attr_set[ctx->device & 63] = true;
   }
   const size_t pos_per_cta = 64 / group;
   dim3 grid((unsigned)((q_len + pos_per_cta - 1) / pos_per_cta), (unsigned)n_kv_heads, (unsigned)batch);

@@ -18,6 +18,7 @@ enum DeviceErr : int {
   DERR_SCALE_WAIT = 3,   // gave up waiting for the scale rows
   DERR_PEER_WAIT = 4,    // gave up waiting for a peer rank's flag
   DERR_TMEM = 5,         // tensor-memory allocation / MMA completion wait gave up
+  DERR_POSITION = 6,     // a sequence position outside the cache (or the RoPE tables): the access was skipped
 };
 
 // Upper bound on polls of one barrier before a kernel records an error and moves on.  Each poll

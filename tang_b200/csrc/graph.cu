@@ -8,6 +8,7 @@ struct tq_graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   unsigned long long kernels = 0;  // kernels recorded between begin and end
+  unsigned long long ws_generation = 0;  // the context's workspace generation when the graph was recorded
 };
 
 using namespace tq;
@@ -36,6 +37,7 @@ int tq_graph_end(tq_ctx* ctx, tq_graph** out) {
   tq_graph* g = new (std::nothrow) tq_graph();
   if (!g) return fail(ctx, TQ_ENOMEM, "out of host memory");
   g->kernels = ctx->launches - ctx->launches_at_capture;
+  g->ws_generation = ctx->ws_generation;
   ctx->launches = ctx->launches_at_capture;  // nothing ran yet; replays are counted by tq_graph_launch
   cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
   if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
@@ -52,6 +54,10 @@ int tq_graph_end(tq_ctx* ctx, tq_graph** out) {
 int tq_graph_launch(tq_ctx* ctx, tq_graph* g) {
   if (int st = bind(ctx)) return st;
   TQ_REQUIRE(ctx, g && g->exec, "tq_graph_launch: null graph");
+  // The recorded kernels hold the addresses of the context's workspaces (attention partials, staged activations,
+  // split-K partials).  A later call that needed a larger workspace freed the old one: replaying would write there.
+  TQ_REQUIRE(ctx, g->ws_generation == ctx->ws_generation,
+             "tq_graph_launch: a workspace of this context was reallocated after the graph was recorded; record it again");
   TQ_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
   ctx->launches += g->kernels;
   ctx->inflight_unknown = true;

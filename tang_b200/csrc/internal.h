@@ -42,6 +42,8 @@ struct tq_ctx {
   bool inflight_unknown = true;
   int n_inflight = 0;
   struct Range { uintptr_t lo, hi; bool written; } inflight[96];
+  unsigned long long ws_generation = 0;        // bumped whenever a workspace is freed and reallocated: graphs recorded
+                                               // before that hold the old addresses and refuse to launch
   unsigned long long launches = 0;             // kernels launched through this context
   bool pdl = true;                             // programmatic dependent launch for the decode-path kernels
   bool capturing = false;                      // between tq_graph_begin and tq_graph_end

@@ -26,17 +26,50 @@ extern "C" int tq_comm_world(const tq_comm*);
 extern "C" int tq_comm_rank(const tq_comm*);
 
 namespace tq {
-int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const float* sin_t, const int* positions, int B,
-                    int n_heads, int n_kv, int hd, int max_seq, void* q_out, void* k_cache, void* v_cache,
-                    size_t seq_stride, int q_len);
+int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const float* sin_t, const int* positions,
+                    const int* rope_positions, int B, int n_heads, int n_kv, int hd, int max_seq, void* q_out, void* k_cache,
+                    void* v_cache, size_t seq_stride, int q_len);
 int launch_gqa_decode(tq_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, const int* lens, int B,
                       int n_heads, int n_kv, int head_dim, size_t seq_stride, int max_len, void* out, int out_dtype);
 
-__global__ void lens_kernel(const int* positions, int* lens, int n) {
+// Attention length of each sequence: its new token's position + 1, kept inside the cache whatever the position
+// says (a position outside 0 .. max_seq-1 is reported through the status word by the kernel that appends K/V).
+__global__ void lens_kernel(const int* positions, int* lens, int n, int max_seq) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) lens[i] = positions[i] + 1;
+  if (i < n) lens[i] = min(max(positions[i] + 1, 0), max_seq);
+}
+
+// KVCache::trim_to (crates/tang-infer/src/kv_cache.rs:138-149) for one layer's K and V caches: a sequence that
+// holds more than `keep` positions drops its OLDEST ones, i.e. rows [len - keep, len) move to [0, keep).  The move
+// is in place: each thread owns one 16-byte column of a sequence's rows and walks it front to back, eight rows at
+// a time (read eight, then write eight), so a row is always read before the same column's writes reach it.
+__global__ void kv_trim_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache, const int* lens, int keep, int max_seq,
+                               size_t row_elems, size_t seq_stride) {
+  const int b = blockIdx.y;
+  __nv_bfloat16* base = (blockIdx.z ? v_cache : k_cache) + (size_t)b * seq_stride;
+  const int len = min(max(lens[b], 0), max_seq);
+  const int drop = len - keep;
+  if (drop <= 0) return;
+  const size_t vecs = row_elems / 8;                       // 16-byte columns per row
+  const size_t col = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= vecs) return;
+  uint4* p = reinterpret_cast<uint4*>(base) + col;
+  for (int r = 0; r < keep; r += 8) {
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (r + i < keep) v[i] = p[(size_t)(r + i + drop) * vecs];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (r + i < keep) p[(size_t)(r + i) * vecs] = v[i];
+  }
+}
+
+__global__ void kv_trim_lens_kernel(int* lens, int n, int keep, int max_seq) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) lens[i] = min(min(max(lens[i], 0), max_seq), keep);
 }
 }  // namespace tq
 
@@ -229,6 +262,31 @@ int tq_llama_kv_cache(tq_llama* m, size_t layer, void** k_cache_dev, void** v_ca
   return TQ_OK;
 }
 
+int tq_llama_kv_trim(tq_llama* m, int* seq_lens_io_dev, size_t batch, size_t keep) {
+  if (!m) return TQ_EINVAL;
+  tq_ctx* ctx = m->ctx;
+  if (int st = bind(ctx)) return st;
+  const tq_llama_config& c = m->cfg;
+  TQ_REQUIRE(ctx, seq_lens_io_dev != nullptr, "tq_llama_kv_trim: null lengths");
+  TQ_REQUIRE(ctx, batch > 0 && batch <= c.max_batch, "tq_llama_kv_trim: batch must be 1..%u", c.max_batch);
+  if (keep >= c.max_seq) return TQ_OK;   // no sequence can hold more than max_seq positions: nothing to drop
+  const size_t row_elems = (size_t)m->kv_l * c.head_dim, seq_stride = (size_t)c.max_seq * row_elems;
+  TQ_REQUIRE(ctx, row_elems % 8 == 0, "tq_llama_kv_trim: cache rows must be a multiple of 16 bytes");
+  if (keep > 0) {
+    const unsigned gx = (unsigned)((row_elems / 8 + 127) / 128);
+    for (auto& L : m->layers) {
+      kv_trim_kernel<<<dim3(gx, (unsigned)batch, 2), 128, 0, ctx->stream>>>(L.k_cache, L.v_cache, seq_lens_io_dev, (int)keep,
+                                                                          (int)c.max_seq, row_elems, seq_stride);
+      ctx->launches++;
+    }
+    TQ_CUDA(ctx, cudaGetLastError());
+  }
+  kv_trim_lens_kernel<<<(unsigned)((batch + 63) / 64), 64, 0, ctx->stream>>>(seq_lens_io_dev, (int)batch, (int)keep, (int)c.max_seq);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
+  return TQ_OK;
+}
+
 int tq_llama_hidden(tq_llama* m, float** hidden_dev) {
   if (!m || !hidden_dev) return TQ_EINVAL;
   *hidden_dev = m->h;
@@ -237,6 +295,11 @@ int tq_llama_hidden(tq_llama* m, float** hidden_dev) {
 
 int tq_llama_decode(tq_llama* m, const int* token_ids_dev, const int* positions_dev, size_t batch, size_t max_len,
                     float* logits_dev) {
+  return tq_llama_decode_at(m, token_ids_dev, positions_dev, nullptr, batch, max_len, logits_dev);
+}
+
+int tq_llama_decode_at(tq_llama* m, const int* token_ids_dev, const int* positions_dev, const int* rope_positions_dev,
+                       size_t batch, size_t max_len, float* logits_dev) {
   if (!m) return TQ_EINVAL;
   tq_ctx* ctx = m->ctx;
   if (int st = bind(ctx)) return st;
@@ -254,7 +317,7 @@ int tq_llama_decode(tq_llama* m, const int* token_ids_dev, const int* positions_
 #define TQ_STEP(expr) \
   if ((st = (expr)) != TQ_OK) return st;
 
-  TQ_CUDA(ctx, launch_k(ctx, lens_kernel, dim3((B + 63) / 64), dim3(64), 0, positions_dev, m->lens, B));
+  TQ_CUDA(ctx, launch_k(ctx, lens_kernel, dim3((B + 63) / 64), dim3(64), 0, positions_dev, m->lens, B, (int)c.max_seq));
   TQ_STEP(tq_embedding(ctx, m->embed, TQ_BF16, token_ids_dev, B, d, c.vocab, m->h, TQ_F32));
 
   bool have_delta = false;  // true once `delta` holds a projection output not yet added to h
@@ -264,7 +327,7 @@ int tq_llama_decode(tq_llama* m, const int* token_ids_dev, const int* positions_
     TQ_STEP(tq_rms_norm(ctx, have_delta ? (const void*)m->delta : (const void*)m->h, TQ_F32, have_delta ? m->h : nullptr,
                         L.attn_norm, TQ_BF16, B, d, c.eps, m->xn, TQ_BF16, have_delta ? m->h : nullptr));
     TQ_STEP(tq_qlinear(ctx, L.wqkv, m->xn, TQ_BF16, d, B, m->qkv, TQ_F32, q_dim + 2 * kv_dim, nullptr));
-    TQ_STEP(launch_qkv_post(ctx, m->qkv, m->cos_t, m->sin_t, positions_dev, B, m->heads_l, m->kv_l, (int)hd, (int)c.max_seq,
+    TQ_STEP(launch_qkv_post(ctx, m->qkv, m->cos_t, m->sin_t, positions_dev, rope_positions_dev, B, m->heads_l, m->kv_l, (int)hd, (int)c.max_seq,
                             m->qb, L.k_cache, L.v_cache, seq_stride, 1));
     TQ_STEP(launch_gqa_decode(ctx, m->qb, L.k_cache, L.v_cache, m->lens, B, m->heads_l, m->kv_l, (int)hd, seq_stride,
                               (int)max_len, m->attn, TQ_BF16));
@@ -309,6 +372,7 @@ int tq_llama_prefill(tq_llama* m, const int* token_ids_dev, const int* cache_sta
   if (R > m->pre_rows) {   // (re)size the chunk's workspaces
     TQ_REQUIRE(ctx, !ctx->capturing, "tq_llama_prefill: workspaces must be sized before graph capture (run once eagerly)");
     TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->ws_generation++;   // graphs recorded over the old chunk buffers must not be replayed
     void** slots[] = {(void**)&m->p_h, (void**)&m->p_delta, (void**)&m->p_qkv, (void**)&m->p_gu, (void**)&m->p_xn,
                       (void**)&m->p_qb, (void**)&m->p_attn, (void**)&m->p_act, (void**)&m->p_last};
     const size_t bytes[] = {R * d * 4, R * d * 4, R * (q_dim + 2 * kv_dim) * 4, R * 2 * m->ffn_l * 4, R * d * 2,
@@ -335,7 +399,7 @@ int tq_llama_prefill(tq_llama* m, const int* token_ids_dev, const int* cache_sta
     TQ_STEP(tq_rms_norm(ctx, have_delta ? (const void*)m->p_delta : (const void*)m->p_h, TQ_F32, have_delta ? m->p_h : nullptr,
                         L.attn_norm, TQ_BF16, R, d, c.eps, m->p_xn, TQ_BF16, have_delta ? m->p_h : nullptr));
     TQ_STEP(tq_qlinear(ctx, L.wqkv, m->p_xn, TQ_BF16, d, R, m->p_qkv, TQ_F32, q_dim + 2 * kv_dim, nullptr));
-    TQ_STEP(launch_qkv_post(ctx, m->p_qkv, m->cos_t, m->sin_t, cache_start_dev, Ri, m->heads_l, m->kv_l, (int)hd, (int)c.max_seq,
+    TQ_STEP(launch_qkv_post(ctx, m->p_qkv, m->cos_t, m->sin_t, cache_start_dev, nullptr, Ri, m->heads_l, m->kv_l, (int)hd, (int)c.max_seq,
                             m->p_qb, L.k_cache, L.v_cache, seq_stride, (int)q_len));
     TQ_STEP(tq_gqa_prefill(ctx, m->p_qb, L.k_cache, L.v_cache, cache_start_dev, batch, q_len, m->heads_l, m->kv_l, hd, seq_stride,
                            m->p_attn, TQ_BF16));

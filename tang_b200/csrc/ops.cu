@@ -177,9 +177,13 @@ __global__ void embedding_kernel(const void* weight, int w_dt, const int* ids, s
 //   k_cache[b, pos_b, :] = bf16(rot(k)),  v_cache[b, pos_b, :] = bf16(v).
 // Cache layout per sequence is [max_seq, n_kv*hd] (crates/tang-infer/src/kv_cache.rs:12-24).
 // With q_len > 1 (prefill) the rows are [sequence][i] and row i of sequence b sits at position positions[b] + i.
-__global__ void qkv_post_kernel(const float* qkv, const float* cos_t, const float* sin_t, const int* positions, int B,
+// `rope_positions` (optional) gives the position each sequence's rotation uses when that is not its cache row any
+// more (after KVCache::trim_to, crates/tang-infer/src/kv_cache.rs:138-149, rows move to the front of the cache
+// while the caller's position count runs on).
+__global__ void qkv_post_kernel(const float* qkv, const float* cos_t, const float* sin_t, const int* positions,
+                                const int* rope_positions, int B,
                                 int n_heads, int n_kv, int hd, int max_seq, __nv_bfloat16* q_out,
-                                __nv_bfloat16* k_cache, __nv_bfloat16* v_cache, size_t seq_stride, int q_len) {
+                                __nv_bfloat16* k_cache, __nv_bfloat16* v_cache, size_t seq_stride, int q_len, int* err) {
   pdl_wait();
   pdl_launch_dependents();
   const int half = hd / 2;
@@ -191,32 +195,39 @@ __global__ void qkv_post_kernel(const float* qkv, const float* cos_t, const floa
   const int head = pr / half, i = pr % half;
   const int b = row / q_len;
   const int pos = positions[b] + row % q_len;
+  // The position comes from device memory (a generation loop advances it inside a replayed graph): one outside
+  // the cache / the tables is not followed.  The row's outputs stay unwritten and the status word says why.
+  const int rpos = rope_positions ? rope_positions[b] + row % q_len : pos;
+  if (pos < 0 || pos >= max_seq || rpos < 0 || rpos >= max_seq) {
+    if (pr == 0) atomicCAS(err, 0, (int)DERR_POSITION);
+    return;
+  }
   const size_t src = (size_t)row * (n_heads + 2 * n_kv) * hd + (size_t)head * hd + 2 * i;
   const float x0 = qkv[src], x1 = qkv[src + 1];
   if (head < n_heads + n_kv) {
-    const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+    const float c = cos_t[(size_t)rpos * half + i], s = sin_t[(size_t)rpos * half + i];
     const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
     const __nv_bfloat162 pk = __floats2bfloat162_rn(r0, r1);
     if (head < n_heads) {
       *reinterpret_cast<__nv_bfloat162*>(q_out + (size_t)row * n_heads * hd + (size_t)head * hd + 2 * i) = pk;
-    } else if (pos < max_seq) {
+    } else {
       const int kh = head - n_heads;
       *reinterpret_cast<__nv_bfloat162*>(k_cache + (size_t)b * seq_stride + (size_t)pos * n_kv * hd + (size_t)kh * hd + 2 * i) = pk;
     }
-  } else if (pos < max_seq) {
+  } else {
     const int vh = head - n_heads - n_kv;
     *reinterpret_cast<__nv_bfloat162*>(v_cache + (size_t)b * seq_stride + (size_t)pos * n_kv * hd + (size_t)vh * hd + 2 * i) =
         __floats2bfloat162_rn(x0, x1);
   }
 }
 
-int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const float* sin_t, const int* positions, int B,
-                    int n_heads, int n_kv, int hd, int max_seq, void* q_out, void* k_cache, void* v_cache,
-                    size_t seq_stride, int q_len) {
+int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const float* sin_t, const int* positions,
+                    const int* rope_positions, int B, int n_heads, int n_kv, int hd, int max_seq, void* q_out, void* k_cache,
+                    void* v_cache, size_t seq_stride, int q_len) {
   const size_t n = (size_t)B * (n_heads + 2 * n_kv) * (hd / 2);
-  TQ_CUDA(ctx, launch_k(ctx, qkv_post_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, qkv, cos_t, sin_t, positions, B,
+  TQ_CUDA(ctx, launch_k(ctx, qkv_post_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, qkv, cos_t, sin_t, positions, rope_positions, B,
                         n_heads, n_kv, hd, max_seq, static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
-                        static_cast<__nv_bfloat16*>(v_cache), seq_stride, q_len));
+                        static_cast<__nv_bfloat16*>(v_cache), seq_stride, q_len, ctx->dev_err));
   return TQ_OK;
 }
 

@@ -464,10 +464,11 @@ __global__ void quantize_rows_kernel(const void* src, int src_dtype, size_t ld, 
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   const float scale = amax == 0.f ? 1.0f : __fdiv_rn(amax, is4 ? 7.0f : 127.0f);
   const float inv = __fdiv_rn(1.0f, scale);
-  float q = roundf(__fmul_rn(v, inv));                   // ties away from zero, like f32::round
+  const float pr = __fmul_rn(v, inv);                    // NaN for a NaN weight, and for inf * 0 in a block with an infinity
+  float q = roundf(pr);                                  // ties away from zero, like f32::round
   q = fminf(fmaxf(q, is4 ? -8.0f : -128.0f), is4 ? 7.0f : 127.0f);
-  int qi = live ? (int)q : 0;                            // a NaN product casts to 0 in Rust as well
-  if (!(q == q)) qi = 0;
+  // Rust's `NaN.round().clamp(..) as i8` is 0; fminf/fmaxf would have turned the NaN into a bound, so test the product
+  int qi = (live && pr == pr) ? (int)q : 0;
   if (is4) {
     const int hi = __shfl_down_sync(0xffffffffu, qi, 1);
     if ((lane & 1) == 0) pay[blk * 16 + (lane >> 1)] = (uint8_t)((qi + 8) | ((hi + 8) << 4));

@@ -87,10 +87,19 @@ class LlamaModel:
         n = self.cfg.max_batch * s
         return (Buffer(self.dev, k, n, _lib.BF16, owns=False), Buffer(self.dev, v, n, _lib.BF16, owns=False), s)
 
-    def decode(self, token_ids: Buffer, positions: Buffer, batch: int, max_len: int, logits: Buffer) -> None:
-        """``model.forward(&[tok], cache, pos)`` for `batch` sequences (smollm.rs:535); asynchronous."""
-        self.dev._check(self.dev._L.tq_llama_decode(C.c_void_p(self.handle), C.c_void_p(token_ids.ptr),
-                                                    C.c_void_p(positions.ptr), batch, max_len, C.c_void_p(logits.ptr)))
+    def trim_to(self, seq_lens: Buffer, batch: int, keep: int) -> None:
+        """``KVCache::trim_to(keep)`` (crates/tang-infer/src/kv_cache.rs:138-149) for `batch` sequences: each keeps its
+        last `keep` positions (moved to the front of its cache rows); `seq_lens` (int32, device) is updated in place."""
+        self.dev._check(self.dev._L.tq_llama_kv_trim(C.c_void_p(self.handle), C.c_void_p(seq_lens.ptr), batch, keep))
+
+    def decode(self, token_ids: Buffer, positions: Buffer, batch: int, max_len: int, logits: Buffer,
+               rope_positions: Buffer | None = None) -> None:
+        """``model.forward(&[tok], cache, pos)`` for `batch` sequences (smollm.rs:535); asynchronous.  `positions` are the
+        cache rows the new tokens are appended at; `rope_positions` the positions their rotation uses when that differs
+        (a trimmed cache)."""
+        self.dev._check(self.dev._L.tq_llama_decode_at(C.c_void_p(self.handle), C.c_void_p(token_ids.ptr), C.c_void_p(positions.ptr),
+                                                       C.c_void_p(rope_positions.ptr if rope_positions is not None else 0),
+                                                       batch, max_len, C.c_void_p(logits.ptr)))
 
     def prefill(self, token_ids: Buffer, cache_start: Buffer, batch: int, q_len: int, logits: Buffer) -> None:
         """``model.forward(&tokens, cache, pos)`` for a chunk of `q_len` tokens per sequence (prompt processing): appends the

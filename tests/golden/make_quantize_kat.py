@@ -31,13 +31,21 @@ def round_half_away(v):
 def quant_block(chunk, qmax, lo, hi):
     amax = F(0)
     for v in chunk:
-        amax = max(amax, abs(F(v)))
+        a = abs(F(v))
+        if a > amax:                      # f32::max(acc, NaN) keeps acc: a NaN never becomes the maximum
+            amax = a
     scale = F(1.0) if amax == 0 else F(amax / F(qmax))
     inv = F(F(1.0) / scale)
     q = []
     for v in chunk:
-        r = round_half_away(F(F(v) * inv))
-        q.append(int(min(max(r, lo), hi)))
+        with np.errstate(invalid="ignore"):
+            pr = F(F(v) * inv)
+        if pr != pr:                      # `NaN.round().clamp(lo, hi) as i8` is 0 in Rust (a NaN weight, or inf * 0)
+            q.append(0)
+        elif math.isinf(pr):
+            q.append(hi if pr > 0 else lo)
+        else:
+            q.append(int(min(max(round_half_away(pr), lo), hi)))
     return scale, q
 
 
@@ -83,6 +91,8 @@ def main():
         "zero_block": [0.0] * 32,                                               # scale must be 1.0
         "ragged_40": [math.sin(0.37 * i) * (1 + i % 5) for i in range(40)],      # second block has 8 values
         "tie_and_clamp": [7.0, 3.5, -3.5, 0.5, -0.5, 2.5, -7.0, 6.5] + [0.25 * i - 3 for i in range(24)],
+        "nan_in_block": [1.0, float("nan"), -2.0, 3.5] + [0.5 * i - 4 for i in range(28)],      # NaN -> code 0, scale from the rest
+        "inf_in_block": [1.0, float("inf"), -2.0, float("-inf")] + [0.5 * i - 4 for i in range(28)],  # scale inf: finite -> 0, inf*0 = NaN -> 0
     }
     out = {"quantize": {}, "matvec": {}}
     for name, data in cases.items():

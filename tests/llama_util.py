@@ -26,8 +26,9 @@ class HostLlama:
         self.lm_head = make_weight(rng, KIND, vocab, d) + (vocab, d)
 
     # ------------------------------------------------------------------ oracle side
-    def oracle_decode(self, orc, token, k_caches, v_caches, pos, threads=0):
-        """k_caches / v_caches: per layer uint16 [max_seq, kv_dim] (updated in place).  Returns f64 logits."""
+    def oracle_decode(self, orc, token, k_caches, v_caches, pos, threads=0, rope_pos=None):
+        """k_caches / v_caches: per layer uint16 [max_seq, kv_dim] (updated in place).  Returns f64 logits.
+        `pos` is the cache row of the new token; `rope_pos` its position for the rotation when that differs."""
         dims = orc.LlamaDims(self.d, self.n_heads, self.n_kv, self.hd, self.ffn, self.rope_base, self.eps)
         hidden = ((self.embed[token].astype(np.uint32) << 16).view(np.float32)).astype(np.float64)
         for li, L in enumerate(self.layers):
@@ -37,7 +38,7 @@ class HostLlama:
                 setattr(ol, name, orc.qweight(KIND, sc, pay, r, c))
             ol.attn_norm_bf16 = L["attn_norm"].ctypes.data
             ol.ffn_norm_bf16 = L["ffn_norm"].ctypes.data
-            orc.llama_layer_f64(dims, ol, hidden, k_caches[li], v_caches[li], pos, threads)
+            orc.llama_layer_f64(dims, ol, hidden, k_caches[li], v_caches[li], pos, threads, rope_pos)
         sc, pay, r, c = self.lm_head
         return orc.llama_head_f64(dims, self.final_norm, orc.qweight(KIND, sc, pay, r, c), hidden, threads)
 

@@ -1,5 +1,7 @@
 """GPU parity of the Llama-shaped decode step against the oracle's restatement of the reference
 decode loop (crates/tang-train/examples/smollm.rs:215-296) with the quantised matvec."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -174,3 +176,185 @@ def test_prefill_chunk_equals_token_by_token(dev, orc):
     assert logits_err(lg2.to_vec().reshape(B, host.vocab), got) < TOL_LOGITS
     model.destroy()
     m2.destroy()
+
+
+def test_positions_outside_the_cache_are_reported_not_followed(dev, orc):
+    """A position of max_seq or -1 (device-resident, e.g. one replay too many of a generation graph) must not become
+    an access outside the cache or the RoPE tables: the row is skipped, the cache keeps its contents, and the next
+    tq_sync reports the bad position."""
+    import tang_b200 as tb
+
+    host = HostLlama(np.random.default_rng(11), n_layers=1, d=256, n_heads=4, n_kv=2, hd=128, ffn=512, vocab=1024)
+    max_seq, B = 32, 2
+    kv_dim = host.n_kv * host.hd
+    model = host.to_device(dev, max_seq, B)
+    kbuf, vbuf, _ = model.kv_buffers(0)
+    fill = np.full((B, max_seq, kv_dim), 0x3F80, np.uint16)          # bf16 1.0 everywhere
+    for buf in (kbuf, vbuf):
+        dev._check(dev._L.tq_upload(dev._ctx, buf.ptr, fill.ctypes.data, fill.nbytes))
+    logits = dev.alloc(B * host.vocab, tb.F32)
+    tokens = dev.upload(np.array([1, 2], np.int32), tb.I32)
+    for bad in (max_seq, -1, max_seq + 1000):
+        pos = dev.upload(np.array([3, bad], np.int32), tb.I32)
+        model.decode(tokens, pos, B, max_seq, logits)
+        with pytest.raises(tb.TangqError) as e:
+            dev.sync()
+        assert e.value.status == tb._lib.TQ_EINVAL and "position" in str(e.value)
+        kd = kbuf.to_vec().reshape(B, max_seq, kv_dim)
+        assert np.all(kd[1] == 0x3F80)                               # sequence 1: nothing appended anywhere
+        assert np.any(kd[0, 3] != 0x3F80)                            # sequence 0 went through
+        fill_row = np.full(kv_dim, 0x3F80, np.uint16)                # put sequence 0's row back for the next round
+        kd[0, 3] = fill_row
+        dev._check(dev._L.tq_upload(dev._ctx, kbuf.ptr, kd.ctypes.data, kd.nbytes))
+    # a good step afterwards works and the status is clean
+    model.decode(tokens, dev.upload(np.array([3, 4], np.int32), tb.I32), B, max_seq, logits)
+    dev.sync()
+    # prefill: a chunk that would run past the cache is refused the same way
+    ids = dev.upload(np.zeros((B, 8), np.int32), tb.I32)
+    model.prefill(ids, dev.upload(np.array([0, max_seq - 4], np.int32), tb.I32), B, 8, logits)
+    with pytest.raises(tb.TangqError) as e:
+        dev.sync()
+    assert e.value.status == tb._lib.TQ_EINVAL
+    model.destroy()
+
+
+def test_graph_recorded_before_a_workspace_grew_refuses_to_launch(dev, orc):
+    """The kernels of a recorded graph hold the addresses of the context's workspaces; once a later call has made a
+    workspace grow (free + allocate) the graph must not be replayed."""
+    import tang_b200 as tb
+
+    d2 = tb.QuantComputeDevice(0)            # a context of its own: its workspaces start small
+    rng = np.random.default_rng(5)
+    B, nh, nkv, hd, L = 2, 8, 2, 128, 600
+    q = d2.upload(bf16_round(rng.standard_normal((B, nh * hd)).astype(np.float32))[0], tb.BF16)
+    kv = d2.upload(bf16_round(rng.standard_normal((B, L, nkv * hd)).astype(np.float32))[0], tb.BF16)
+    lens = d2.upload(np.array([L, L // 2], np.int32), tb.I32)
+    out = d2.alloc(B * nh * hd, tb.BF16)
+
+    def attend():          # the raw call: nothing in it allocates or synchronises, so it can be recorded
+        d2._check(d2._L.tq_gqa_decode(d2._ctx, C.c_void_p(q.ptr), C.c_void_p(kv.ptr), C.c_void_p(kv.ptr), C.c_void_p(lens.ptr),
+                                      B, nh, nkv, hd, L * nkv * hd, L, C.c_void_p(out.ptr), tb.BF16))
+
+    attend()               # eager: sizes the partials' workspace
+    d2.sync()
+    d2.begin_capture()
+    attend()
+    g = d2.end_capture()
+    g.launch()
+    d2.sync()
+    first = out.to_vec().copy()
+    # a call that needs a larger workspace makes it grow (freed and allocated anew): 600 host vectors of 1024
+    # doubles through the reference-shaped matvec call stage about 15 MB in the same workspace
+    from util import make_weight
+
+    sc, pay = make_weight(rng, 1, 1024, 1024)
+    w = d2.upload_qarrays(1, pay, sc, 1024, 1024)
+    d2.q_matmul_host(w, rng.standard_normal((600, 1024)), 600)
+    d2.sync()
+    with pytest.raises(tb.TangqError) as e:
+        g.launch()
+    assert e.value.status == tb._lib.TQ_EINVAL and "record" in str(e.value)
+    # recording it again works and gives the same numbers
+    d2.memset(out)
+    d2.begin_capture()
+    attend()
+    g2 = d2.end_capture()
+    g2.launch()
+    d2.sync()
+    assert np.array_equal(out.to_vec(), first)
+    d2.close()
+
+
+@pytest.mark.parametrize("B", [16, 64])
+def test_llama3_8b_width_decode_batches(dev, orc, B):
+    """The benchmark's decode batches at full Llama-3-8B layer widths (two layers, context 2048): from 24 rows on
+    every linear layer of the step runs on the tcgen05 GEMM (split K for the narrow ones), which the small batches
+    above never reach.  The oracle checks a seeded sample of the sequences."""
+    import tang_b200 as tb
+
+    host = HostLlama(np.random.default_rng(3), n_layers=2, d=4096, n_heads=32, n_kv=8, hd=128, ffn=14336, vocab=128256)
+    rng = np.random.default_rng(700 + B)
+    max_seq = 2049
+    kv_dim = host.n_kv * host.hd
+    model = host.to_device(dev, max_seq, B)
+    sample = np.sort(rng.choice(B, 3, replace=False))
+    pos = rng.integers(1500, 2049, B).astype(np.int32)
+    pos[sample[0]] = 2048
+    ok, ov = {}, {}
+    for li in range(host.n_layers):
+        kbuf, vbuf, stride = model.kv_buffers(li)
+        for b in range(B):       # sequence by sequence keeps the host arrays small
+            kb = bf16_round(rng.standard_normal((max_seq, kv_dim)).astype(np.float32))[0]
+            vb = bf16_round(rng.standard_normal((max_seq, kv_dim)).astype(np.float32))[0]
+            dev._check(dev._L.tq_upload(dev._ctx, kbuf.ptr + b * stride * 2, kb.ctypes.data, kb.nbytes))
+            dev._check(dev._L.tq_upload(dev._ctx, vbuf.ptr + b * stride * 2, vb.ctypes.data, vb.nbytes))
+            if b in sample:
+                ok[(li, b)], ov[(li, b)] = kb, vb
+    tokens = rng.integers(0, host.vocab, B).astype(np.int32)
+    logits = dev.alloc(B * host.vocab, tb.F32)
+    model.decode(dev.upload(tokens, tb.I32), dev.upload(pos, tb.I32), B, 2049, logits)
+    dev.sync()
+    got = logits.to_vec().reshape(B, host.vocab)
+    assert np.all(np.isfinite(got))
+    for b in sample:
+        want = host.oracle_decode(orc, int(tokens[b]), [ok[(li, b)] for li in range(host.n_layers)],
+                                  [ov[(li, b)] for li in range(host.n_layers)], int(pos[b]))
+        assert logits_err(got[b], want) < TOL_LOGITS, b
+    model.destroy()
+
+
+def test_trimmed_cache_keeps_the_last_tokens(dev, orc):
+    """KVCache::trim_to (crates/tang-infer/src/kv_cache.rs:138-149): every sequence keeps its LAST `keep` positions, moved
+    to the front of its cache rows in every layer; shorter sequences are untouched.  The device cache after
+    tq_llama_kv_trim equals the oracle's trimmed rows bit for bit, and a decode step on top of it (appended at row
+    `keep`, rotated for the running position) matches the oracle run on the trimmed rows."""
+    import tang_b200 as tb
+
+    host = HostLlama(np.random.default_rng(21), n_layers=2, d=256, n_heads=4, n_kv=2, hd=128, ffn=512, vocab=1024)
+    rng = np.random.default_rng(22)
+    B, max_seq, keep = 3, 160, 64
+    lens = np.array([131, 20, 65], np.int32)            # 131 and 65 are trimmed to 64, 20 stays
+    kv_dim = host.n_kv * host.hd
+    model = host.to_device(dev, max_seq, B)
+    ok, ov = [], []
+    for li in range(host.n_layers):
+        kb = bf16_round(rng.standard_normal((B, max_seq, kv_dim)).astype(np.float32))[0]
+        vb = bf16_round(rng.standard_normal((B, max_seq, kv_dim)).astype(np.float32))[0]
+        kbuf, vbuf, _ = model.kv_buffers(li)
+        dev._check(dev._L.tq_upload(dev._ctx, kbuf.ptr, kb.ctypes.data, kb.nbytes))
+        dev._check(dev._L.tq_upload(dev._ctx, vbuf.ptr, vb.ctypes.data, vb.nbytes))
+        ok.append(kb.copy())
+        ov.append(vb.copy())
+    lens_dev = dev.upload(lens, tb.I32)
+    model.trim_to(lens_dev, B, keep)
+    dev.sync()
+    new_lens = lens_dev.to_vec()
+    want_lens = []
+    for b in range(B):
+        want_lens.append(orc.kv_trim_to(ok[0][b], int(lens[b]), keep))
+        orc.kv_trim_to(ov[0][b], int(lens[b]), keep)
+        for li in range(1, host.n_layers):
+            orc.kv_trim_to(ok[li][b], int(lens[b]), keep)
+            orc.kv_trim_to(ov[li][b], int(lens[b]), keep)
+    assert list(new_lens) == want_lens == [64, 20, 64]
+    for li in range(host.n_layers):
+        kbuf, vbuf, _ = model.kv_buffers(li)
+        kd = kbuf.to_vec().reshape(B, max_seq, kv_dim)
+        vd = vbuf.to_vec().reshape(B, max_seq, kv_dim)
+        for b in range(B):
+            n = want_lens[b]
+            assert np.array_equal(kd[b, :n], ok[li][b, :n]) and np.array_equal(vd[b, :n], ov[li][b, :n]), (li, b)
+    # one decode step on the trimmed caches: cache row = new length, rotation = the running position
+    tokens = rng.integers(0, host.vocab, B).astype(np.int32)
+    logits = dev.alloc(B * host.vocab, tb.F32)
+    model.decode(dev.upload(tokens, tb.I32), lens_dev, B, keep + 1, logits, rope_positions=dev.upload(lens, tb.I32))
+    dev.sync()
+    got = logits.to_vec().reshape(B, host.vocab)
+    for b in range(B):
+        want = host.oracle_decode(orc, int(tokens[b]), [k[b] for k in ok], [v[b] for v in ov], want_lens[b], rope_pos=int(lens[b]))
+        assert logits_err(got[b], want) < TOL_LOGITS, b
+    # keep >= every length: nothing moves
+    model.trim_to(lens_dev, B, max_seq)
+    dev.sync()
+    assert list(lens_dev.to_vec()) == want_lens
+    model.destroy()

@@ -91,3 +91,41 @@ def test_head_shards_concatenate_to_the_full_result(dev, orc):
     full = run(0, H)
     halves = np.concatenate([run(0, H // 2), run(H // 2, H)], axis=1)
     assert np.array_equal(full, halves)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ctx,B", [(16384, 1), (32768, 1), (16384, 16)])
+def test_mla_decode_long_contexts(dev, orc, ctx, B):
+    """The benchmark's long contexts with all 128 heads; the oracle checks a seeded sample of the sequences."""
+    import tang_b200 as tb
+
+    H = 128
+    rng = np.random.default_rng(ctx + B)
+    max_seq = ctx
+    w_qk = rng.integers(-127, 128, (H * C_, NOPE), dtype=np.int8)
+    s_qk = rng.uniform(0.001, 0.01, H * C_).astype(np.float32)
+    w_uv = rng.integers(-127, 128, (H * VD, C_), dtype=np.int8)
+    s_uv = rng.uniform(0.001, 0.01, H * VD).astype(np.float32)
+    qn = bf16_round(rng.standard_normal((B, H, NOPE)).astype(np.float32))
+    qr = bf16_round(rng.standard_normal((B, H, R_)).astype(np.float32))
+    lens = [ctx] + [int(v) for v in rng.integers(ctx // 2, ctx + 1, B - 1)]
+    sample = [0] if B == 1 else [0, int(rng.integers(1, B))]
+    cbuf = dev.alloc(B * max_seq * (C_ + R_), tb.BF16)
+    kept = {}
+    for b in range(B):                                         # sequence by sequence keeps the host arrays small
+        cb = bf16_round(rng.standard_normal((max_seq, C_ + R_)).astype(np.float32))[0]
+        dev._check(dev._L.tq_upload(dev._ctx, cbuf.ptr + b * max_seq * (C_ + R_) * 2, cb.ctypes.data, cb.nbytes))
+        if b in sample:
+            kept[b] = cb
+    wq = dev.upload_qarrays(tb.I8_ROW, w_qk, s_qk, H * C_, NOPE)
+    wu = dev.upload_qarrays(tb.I8_ROW, w_uv, s_uv, H * VD, C_)
+    out = tb.mla_decode(dev, wq, wu, dev.upload(qn[0], tb.BF16), dev.upload(qr[0], tb.BF16), cbuf,
+                        np.array(lens, np.int32), B, H, NOPE, VD, max_seq * (C_ + R_), max(lens))
+    dev.sync()
+    got = out.to_vec().reshape(B, H * VD)
+    assert np.all(np.isfinite(got))
+    dims = orc.MlaDims(H, C_, NOPE, R_, VD)
+    for b in sample:
+        want = orc.mla_decode_f64(dims, qn[1][b].astype(np.float64), qr[1][b].astype(np.float64), kept[b], lens[b],
+                                  w_qk, s_qk, w_uv, s_uv, absorbed=True)
+        assert rel_err(got[b], want, floor_frac=1.0) < 2e-3, (b, lens[b])

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from moe_util import HostMoe
-from util import bf16_round, rel_err
+from util import bf16_round, rel_err, rel_err_profile
 
 pytestmark = pytest.mark.gpu
 
@@ -16,6 +16,18 @@ def dev():
     d = tang_b200.QuantComputeDevice(0)
     yield d
     d.close()
+
+
+def assert_moe_close(got, want, T):
+    """The f32 bar, 1e-3 against max(|ref|, rms(ref)), with one stated exception.  The SwiGLU output is rounded to bf16
+    on both sides (the oracle defines the layer that way); where that value lies within an f32-vs-f64 difference of a
+    rounding tie, the two sides round it to neighbouring bf16 numbers, and ONE such flip of a large activation moves
+    the whole output row of that token by up to 0.3 % of the rms (seen: one token of 130, 58 of 33 280 elements between
+    1e-3 and 2.6e-3).  So: at most 0.5 % of the elements may exceed 1e-3, and none may exceed 1e-2 (half the bf16
+    bar).  Small batches, which see few activations, must meet 1e-3 everywhere."""
+    worst, frac = rel_err_profile(got, want, floor_frac=1.0)
+    assert worst < (1e-3 if T < 24 else 1e-2), (T, worst)
+    assert frac < 5e-3, (T, frac)
 
 
 def check(dev, orc, host, T, seed):
@@ -34,11 +46,7 @@ def check(dev, orc, host, T, seed):
     dev.sync()
     assert np.array_equal(idx.to_vec().reshape(T, host.k), idx_o)
     got = out.to_vec().reshape(T, host.d)
-    # the SwiGLU output is rounded to bf16 on both sides; an f32-vs-f64 difference ahead of that rounding can
-    # flip single elements by one bf16 ulp, so the bar is taken against max(|ref|, rms(ref)).  From 24 tokens
-    # on, the shared experts' bf16-output linears run on the tensor-memory GEMM, which rounds each product
-    # q*scale to bf16 once (relative 2^-9, the step of the bf16 output itself): observed 2.6e-3.
-    assert rel_err(got, want, floor_frac=1.0) < (1e-3 if T < 24 else 5e-3), T
+    assert_moe_close(got, want, T)
     layer.destroy()
 
 
@@ -88,5 +96,33 @@ def test_dispatch_variant_on_one_rank_equals_the_oracle(dev, orc, T):
     out, idx, _w = layer.forward_dispatch(dev.upload(hb, tb.BF16), T, want_routing=True)
     dev.sync()
     assert np.array_equal(idx.to_vec().reshape(T, host.k), idx_o)
-    assert rel_err(out.to_vec().reshape(T, host.d), want, floor_frac=1.0) < (1e-3 if T < 24 else 5e-3)
+    assert_moe_close(out.to_vec().reshape(T, host.d), want, T)
+    layer.destroy()
+
+
+@pytest.mark.parametrize("T", [256, 4096])
+def test_deepseek_v2_lite_shape_large_batches(dev, orc, T):
+    """The benchmark's larger token batches at the DeepSeek-V2-Lite shape: the router's selection is compared for EVERY
+    token (bit-exact logits and choices), the layer output on a seeded sample of tokens (the oracle is a per-token
+    loop)."""
+    import tang_b200 as tb
+
+    host = HostMoe(np.random.default_rng(7), d=2048, ffn=1408, n_experts=64, top_k=6, n_shared=2)
+    rng = np.random.default_rng(500 + T)
+    hb, hf = bf16_round(rng.standard_normal((T, host.d)).astype(np.float32))
+    hbuf = dev.upload(hb, tb.BF16)
+    idx_d, w_d, lg_d = tb.moe_router(dev, hbuf, dev.upload(host.wg_bits, tb.BF16), T, host.d, host.E, host.k, host.renorm)
+    wg64 = host.wg.astype(np.float64)
+    for t in range(T):
+        idx_o, w_o, lg_o = orc.router_f64(hf[t].astype(np.float64), wg64, host.E, host.k, host.renorm)
+        assert np.array_equal(lg_d[t], lg_o) and np.array_equal(idx_d[t], idx_o), t
+    layer = host.to_device(dev)
+    out, idx, w = layer.forward(hbuf, T, want_routing=True)
+    dev.sync()
+    assert np.array_equal(idx.to_vec().reshape(T, host.k), idx_d)
+    got = out.to_vec().reshape(T, host.d)
+    assert np.all(np.isfinite(got))
+    sample = np.sort(rng.choice(T, 6, replace=False))
+    want, _, _, _ = host.oracle(orc, hf[sample])
+    assert_moe_close(got[sample], want, T)
     layer.destroy()

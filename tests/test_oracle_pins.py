@@ -335,3 +335,17 @@ def test_sampler_rules_read_from_the_source(orc):
         p = np.exp(logits - logits.max())
         p /= p.sum()
         assert tok == int(np.searchsorted(np.cumsum(p), r, side="right"))
+
+
+def test_kv_cache_trim_reference_case(orc):
+    """kv_cache.rs:228-252 (kv_cache_trim): five tokens whose rows hold 0..4, trim_to(3) keeps tokens 2, 3, 4 at rows
+    0..2; trimming to at least the current length changes nothing (kv_cache.rs:139-141)."""
+    kv_dim = 4
+    rows = np.zeros((16, kv_dim), np.uint16)
+    for i in range(5):
+        rows[i] = i
+    assert orc.kv_trim_to(rows, 5, 3) == 3
+    assert [int(rows[r, 0]) for r in range(3)] == [2, 3, 4]
+    before = rows.copy()
+    assert orc.kv_trim_to(rows, 3, 3) == 3 and orc.kv_trim_to(rows, 3, 7) == 3
+    assert np.array_equal(rows, before)

@@ -186,9 +186,9 @@ def test_config0_int8_gemv_full_size(dev, orc):
     assert rel_err(dev.q8_matvec(wb, x), want) < TOL_F32
 
 
-@pytest.mark.parametrize("m", [1, 8, 32, 64])
+@pytest.mark.parametrize("m", [1, 8, 32, 64, 512, 2048])
 def test_config1_int4_full_size(dev, orc, m):
-    """int4 group-32, f16 scales, K=4096, N=14336, bf16 activations."""
+    """int4 group-32, f16 scales, K=4096, N=14336, bf16 activations, every M of the benchmark configuration."""
     import tang_b200 as tb
 
     rng = np.random.default_rng(43)
@@ -269,6 +269,10 @@ def test_device_quantizer_is_bit_exact(dev, orc, kind, rows, cols, src):
         w[1, 32] = -qmax                                     # amax = qmax: scale 1, inv_scale 1
         w[1, 33:40] = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 3.5], np.float32)   # ties
         w[1, 40] = qmax                                      # +qmax stays, -qmax-1 never appears for Q8; Q4 clamps at -8
+    if rows >= 3 and cols >= 64:
+        w[2, 5] = np.nan                                     # a NaN weight: code 0, scale from the rest of the block
+        w[2, 40] = np.inf                                    # an infinity: scale inf, every code of the block 0
+        w[2, 41] = -np.inf
     if src == "bf16":
         bits, w = bf16_round(w)
         buf = dev.upload(bits, tb.BF16)
@@ -288,7 +292,9 @@ def test_device_quantizer_is_bit_exact(dev, orc, kind, rows, cols, src):
             want_v = orc.dequantize_q8(sc, vals)[:cols]
         assert sc.size == bpr
         assert np.array_equal(ints[r], want_i), r
-        assert np.array_equal(deq[r].view(np.uint32), want_v.view(np.uint32)), r
+        finite = np.isfinite(want_v)                         # (0 * inf is NaN on both sides; NaN payload bits are not compared)
+        assert np.array_equal(np.isnan(deq[r]), np.isnan(want_v)), r
+        assert np.array_equal(deq[r][finite].view(np.uint32), want_v[finite].view(np.uint32)), r
 
 
 def test_host_matvec_into_pinned_memory(dev, orc):

@@ -49,18 +49,27 @@ def test_noalloc_matches_allocating_entry_point_twice():
         a, b = got.to_vec(), ref.to_vec()
         assert np.all(np.isfinite(a))
         assert rel_err(a, b) < 1e-3          # same kernels, same split rule: in practice bit-identical
-    # A request whose partials do not fit the fixed array is refused with a message, not served:
-    # 400 sequences x 8 heads x 2 splits x 520 B = 3.3 MB > 3 MiB.  The buffers are real, so the call
-    # would also be valid on a GPU whose SM count makes the split rule ask for less.
-    B, nh, nkv, max_len = 400, 8, 1, 256
+    # A request whose partials do not fit the fixed array is refused with a message, not served.  The number of
+    # splits follows the GPU's SM count (the library aims at four CTAs per SM), so the test recomputes it with the
+    # library's rule and picks a batch that needs at least two splits on any GPU with 98 SMs or more:
+    # 390 sequences x 8 heads x >= 2 splits x 520 B >= 3.24 MB > 3 MiB.
+    import torch
+
+    B, nh, nkv, max_len = 390, 8, 1, 256
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    tiles = (max_len + 63) // 64
+    want = max(1, -(-4 * sms // (B * nkv)))
+    n_splits = min(want, max(1, (tiles + 1) // 2))
+    per_split = -(-tiles // n_splits)
+    n_splits = -(-tiles // per_split)
+    assert n_splits >= 2 and B * nh * n_splits * (hd + 2) * 4 > 3 << 20, (sms, n_splits)
     q = dev.alloc(B * nh * hd, tb.BF16)
     kv = dev.alloc(B * max_len * nkv * hd, tb.BF16)
     dev.memset(q)
     dev.memset(kv)
     ln = dev.upload(np.full(B, max_len, np.int32), tb.I32)
     st, _ = _call(dev, L.tq_gqa_decode_noalloc, q, kv, kv, ln, B, nh, nkv, hd, max_len * nkv * hd, max_len)
-    if st != 0:
-        assert st == tb._lib.TQ_EINVAL and b"static" in L.tq_last_error(dev._ctx)
+    assert st == tb._lib.TQ_EINVAL and b"static" in L.tq_last_error(dev._ctx)
     dev.sync()
     st, _ = _call(dev, L.tq_gqa_decode, q, kv, kv, ln, B, nh, nkv, hd, max_len * nkv * hd, max_len)
     assert st == 0                             # the allocating entry point serves the same request

@@ -37,3 +37,12 @@ def make_weight(rng, kind, rows, cols):
     vals = rng.integers(-127, 128, (rows, cols), dtype=np.int8)
     sc = rng.uniform(0.001, 0.01, rows).astype(np.float32)
     return sc, vals
+
+
+def rel_err_profile(got, want, floor_frac=1.0):
+    """(max, fraction of elements above 1e-3) of |got-want| / max(|want_i|, floor_frac * rms(want))."""
+    got = np.asarray(got, np.float64).reshape(-1)
+    want = np.asarray(want, np.float64).reshape(-1)
+    rms = float(np.sqrt(np.mean(want * want))) or 1.0
+    e = np.abs(got - want) / np.maximum(np.abs(want), floor_frac * rms)
+    return float(e.max()), float(np.mean(e > 1e-3))
