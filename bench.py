@@ -36,9 +36,9 @@ sys.path.insert(0, ROOT)
 N_OUT, K_IN, GROUP = 14336, 4096, 32
 METRIC, UNIT = "int4_gemv_hbm_tbps", "TB/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# capture summarised in profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 33_105_000   # 33.08 MB read + 28 KB written (profiles/qgemm_mma_q4f16_m1_n14336_k4096.md)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu
+# capture of this command with 8 layers and 1 step (33.08 MB read; the 28 KB of results stay in L2).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 33_084_160
 
 
 def algorithmic_bytes(m: int) -> int:
@@ -110,16 +110,19 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_matvec_rate(scales_f16_bits, packed, m_x, threads: int, budget_s: float):
-    """Times the oracle's q4 matvec (f16 scales) on the host: returns (TB/s, reps, seconds)."""
+def cpu_matvec_rate(weights, m_x, threads: int, budget_s: float):
+    """Times the oracle's q4 matvec (f16 scales) on the host over `weights`, a list of distinct (scales, packed)
+    matrices visited in turn (four of them are 132 MB, more than the host's caches): returns (TB/s, reps, seconds)."""
     import oracle
 
     oracle.build()
     x = m_x.astype(np.float64)
-    oracle.qmatmul(oracle.KIND_Q4_F16, scales_f16_bits, packed, N_OUT, K_IN, x, threads)  # warm
+    for sc, pk in weights:
+        oracle.qmatmul(oracle.KIND_Q4_F16, sc, pk, N_OUT, K_IN, x, threads)  # warm
     reps, t0 = 0, time.perf_counter()
     while True:
-        oracle.qmatmul(oracle.KIND_Q4_F16, scales_f16_bits, packed, N_OUT, K_IN, x, threads)
+        sc, pk = weights[reps % len(weights)]
+        oracle.qmatmul(oracle.KIND_Q4_F16, sc, pk, N_OUT, K_IN, x, threads)
         reps += 1
         dt = time.perf_counter() - t0
         if dt >= budget_s:
@@ -143,18 +146,21 @@ def run_reference(args, rank: int) -> None:
 
     oracle.build()
     threads = oracle.max_threads()
-    scales, packed = host_weight(43)
+    per_step = args.ref_sample
+    weights = [host_weight(43 + i) for i in range(per_step)]      # distinct matrices: the step streams them, as the GPU arm does
     rng = np.random.default_rng(44)
     x = rng.standard_normal((args.m, K_IN)).astype(np.float32).astype(np.float64)
-    per_step = args.ref_sample
     for _ in range(max(args.warmup, 1)):
-        oracle.qmatmul(oracle.KIND_Q4_F16, scales, packed, N_OUT, K_IN, x, threads)
+        for sc, pk in weights:
+            oracle.qmatmul(oracle.KIND_Q4_F16, sc, pk, N_OUT, K_IN, x, threads)
     t0 = time.perf_counter()
-    for _ in range(args.steps * per_step):
-        oracle.qmatmul(oracle.KIND_Q4_F16, scales, packed, N_OUT, K_IN, x, threads)
+    for _ in range(args.steps):
+        for sc, pk in weights:
+            oracle.qmatmul(oracle.KIND_Q4_F16, sc, pk, N_OUT, K_IN, x, threads)
     dt = time.perf_counter() - t0
     value = algorithmic_bytes(args.m) * args.steps * per_step / dt / 1e12
-    sample = f"{per_step} of the {args.layers} matvecs of a step per timed step, M={args.m}, {threads} threads"
+    sample = (f"each timed step = {per_step} distinct matrices ({per_step * algorithmic_bytes(args.m) / 1e6:.0f} MB) of the "
+              f"{args.layers} a full step streams, M={args.m}, {threads} threads; the reference itself is single-threaded")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -260,29 +266,35 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     # ---- end to end: the reference-shaped host call, pinned host vectors, copies inside the timing.  A step queues
     # the L matvecs (upload of x, kernel, result written to its own pinned vector) and waits once for all of them;
     # the second timing waits after every call, as a loop over the reference's q4_matvec does.
-    xh = torch.empty((m, K_IN), dtype=torch.bfloat16).pin_memory()
-    xh.copy_(x.cpu())
+    # Every matrix of the step gets its own pinned input vector (a layer's input differs from the next one's).
+    xh = torch.empty((L, m, K_IN), dtype=torch.bfloat16).pin_memory()
+    xh.copy_(torch.randn((L, m, K_IN), generator=torch.Generator().manual_seed(7 + rank)).bfloat16())
     yh = torch.empty((L, m, N_OUT), dtype=torch.bfloat16).pin_memory()
 
     def e2e_pass(call):
         for i in range(L):
-            dev._check(call(dev._ctx, handles[i], C.c_void_p(xh.data_ptr()), C.c_void_p(yh[i].data_ptr()), tb.BF16, m))
+            dev._check(call(dev._ctx, handles[i], C.c_void_p(xh[i].data_ptr()), C.c_void_p(yh[i].data_ptr()), tb.BF16, m))
 
+    # Timed on the host clock, from the first call to the return of the last wait (the clock an end-to-end caller
+    # sees); the CUDA-event time of the same region is kept beside it.
     e2e_steps = max(1, min(args.steps, 20))
-    e2e_times = []
+    e2e_times, e2e_event_times = [], []
     for call, wait in ((L_.tq_q_matvec_host, False), (L_.tq_q_matvec_host_async, True)):
         e2e_pass(call)
         dev.sync()
         barrier()
         with torch.cuda.stream(stream):
             ev0.record(stream)
+            t0 = time.perf_counter()
             for _ in range(e2e_steps):
                 e2e_pass(call)
                 if wait:
                     dev.sync()          # the step's results are read here: one wait per step
+            t1 = time.perf_counter()
             ev1.record(stream)
         barrier()
-        e2e_times.append(ev0.elapsed_time(ev1))
+        e2e_times.append((t1 - t0) * 1e3)
+        e2e_event_times.append(ev0.elapsed_time(ev1))
     e2e_sync_ms, e2e_ms = e2e_times
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
 
@@ -337,9 +349,14 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             import oracle
 
             threads = oracle.max_threads()
-            v, reps, dt = cpu_matvec_rate(host_w[0], host_w[1], host_w[2], threads, args.cpu_budget)
+            weights = [(host_w[0], host_w[1])] + [host_weight(900 + i) for i in range(3)]
+            v, reps, dt = cpu_matvec_rate(weights, host_w[2], threads, args.cpu_budget)
+            # the reference runs this loop on one thread (README: "single-threaded"): that figure beside the all-core one
+            v1, reps1, dt1 = cpu_matvec_rate(weights, host_w[2], 1, args.cpu_budget)
             cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                   "sample": f"{reps} matvecs of one K={K_IN} N={N_OUT} matrix, M={m}, in {dt:.1f} s"}
+                   "sample": f"{reps} matvecs over 4 distinct K={K_IN} N={N_OUT} matrices, M={m}, in {dt:.1f} s",
+                   "single_thread": {"value": v1, "unit": UNIT, "cores": 1,
+                                     "sample": f"{reps1} matvecs over the same 4 matrices in {dt1:.1f} s"}}
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -352,7 +369,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                          "avg_launch_us": ms_per_step * 1e3 / L},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": L * m * K_IN * 2,
                     "d2h_bytes_per_step": L * m * N_OUT * 2, "steps": e2e_steps,
-                    "call": "tq_q_matvec_host_async per matrix + one tq_sync per step (host vectors, weights resident)",
+                    "call": "tq_q_matvec_host_async per matrix + one tq_sync per step (host vectors, one per matrix, weights resident)",
+                    "clock": "host wall clock around the calls and their final wait",
+                    "value_cuda_events": world * L * bytes_launch / (e2e_event_times[1] / e2e_steps * 1e-3) / 1e12,
                     "value_wait_per_call": world * L * bytes_launch / (e2e_sync_ms / e2e_steps * 1e-3) / 1e12,
                     "call_wait_per_call": "tq_q_matvec_host (q4_matvec: returns when the result is on the host)"},
             "cpu_baseline": cpu, "gpu_launches": int(gpu_launches), "clocks": clocks,
@@ -562,6 +581,87 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
             t = (torch.randn(shape, device="cuda", generator=gen) * std).bfloat16()
         stream.synchronize()
         return t
+
+    # ---- the int8 GEMV of the CPU-runnable configuration: [4096, 4096] int8, one f32 scale per output row (and the same
+    # integers as tang-infer's native Q8 blocks, one f32 scale per 32 weights), f32 activations, f32 results;
+    # 16 distinct matrices per graph (268 MB > L2)
+    def q8_blocks(rows, cols):
+        with torch.cuda.stream(stream):
+            pay = torch.randint(-127, 128, (rows, cols), dtype=torch.int8, device="cuda", generator=gen)
+            sc = (torch.rand((rows, cols // 32), device="cuda", generator=gen) * 0.009 + 0.001)
+        stream.synchronize()
+        w = dev.qweight_from_device(tb.Q8_F32, pay.data_ptr(), sc.data_ptr(), rows, cols)
+        dev.sync()
+        return w
+
+    int8 = []
+    n8 = 16
+    for name, make, byt in (("int8 per-row scale", i8, 4096 * 4096 + 4096 * 4 + 4096 * 4 + 4096 * 4),
+                            ("Q8 blocks (f32 scale per 32)", q8_blocks, 4096 * 4096 + 4096 * 128 * 4 + 4096 * 4 + 4096 * 4)):
+        w8 = [make(4096, 4096) for _ in range(n8)]
+        with torch.cuda.stream(stream):
+            x32 = torch.randn((1, 4096), device="cuda", generator=gen)
+        xb16 = x32.bfloat16()
+        y32 = torch.empty((n8, 1, 4096), dtype=torch.float32, device="cuda")
+        stream.synchronize()
+        row = {"layout": name, "algorithmic_bytes": byt}
+        for tag, xt, xdt in (("f32_x", x32, tb.F32), ("bf16_x", xb16, tb.BF16)):
+            def one8():
+                for i, w in enumerate(w8):
+                    dev._check(L_.tq_qlinear(dev._ctx, C.c_void_p(w.handle), C.c_void_p(xt.data_ptr()), xdt, 0, 1,
+                                             C.c_void_p(y32[i].data_ptr()), tb.F32, 0, None))
+            one8()
+            dev.sync()
+            dev.begin_capture()
+            one8()
+            g = dev.end_capture()
+            us = _time_ms(torch, stream, dev, g.launch, 10, 3) * 1e3 / n8
+            g.free()
+            row[tag] = {"us_per_launch": us, "gbs": byt / us / 1e3, "frac_of_hbm_peak": byt / us / 1e3 / peak_gbs}
+        int8.append(row)
+        for w in w8:
+            w.free()
+    out["int8_gemv_4096"] = int8
+
+    # ---- the reference's one published number for this path: quantize/q8_matvec_576x576, 207 992 ns on an Apple M4 Max,
+    # one thread (crates/tang-bench/benches/cpu_training.rs:267-275).  Here: the oracle port on one host thread, the
+    # reference-shaped host call (f64 vectors in and out, waits), and the kernel alone from a graph.
+    import oracle
+
+    oracle.build()
+    rng = np.random.default_rng(576)
+    wf = (rng.standard_normal((576, 576)) * 0.05).astype(np.float32)
+    s8, v8 = oracle.quantize_matrix_q8(wf, 576, 576)
+    xq = rng.standard_normal(576)
+    t0 = time.perf_counter()
+    n_cpu = 200
+    for _ in range(n_cpu):
+        oracle.q8_matvec(s8, v8, 576, 576, xq, 1)
+    cpu_ns = (time.perf_counter() - t0) / n_cpu * 1e9
+    w576 = dev.upload_q8(tb.QuantizedQ8(s8.reshape(-1), v8.reshape(-1), (576, 576)))
+    dev.q8_matvec(w576, xq)
+    t0 = time.perf_counter()
+    for _ in range(200):
+        dev.q8_matvec(w576, xq)
+    host_call_ns = (time.perf_counter() - t0) / 200 * 1e9
+    with torch.cuda.stream(stream):
+        x576 = torch.randn((1, 576), device="cuda", generator=gen)
+    y576 = torch.empty((1, 576), dtype=torch.float32, device="cuda")
+    stream.synchronize()
+
+    def one576():
+        dev._check(L_.tq_qlinear(dev._ctx, C.c_void_p(w576.handle), C.c_void_p(x576.data_ptr()), tb.F32, 0, 1,
+                                 C.c_void_p(y576.data_ptr()), tb.F32, 0, None))
+    one576()
+    dev.sync()
+    dev.begin_capture()
+    for _ in range(20):
+        one576()
+    g = dev.end_capture()
+    kern_ns = _time_ms(torch, stream, dev, g.launch, 10, 3) * 1e6 / 20
+    g.free()
+    out["q8_matvec_576x576"] = {"reference_published_ns_m4max_1thread": 207992, "oracle_port_1thread_ns": cpu_ns,
+                                "host_call_f64_ns": host_call_ns, "device_launches_from_graph_ns": kern_ns}
 
     # ---- int4 GEMM: M sweep over 16 distinct matrices (528 MB > L2), bf16 results, one CUDA graph per M
     n_mat = 16

@@ -34,8 +34,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     if not force and not stale():
         return LIB
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    extra = os.environ.get("TQ_NVCC_EXTRA", "").split()     # e.g. -DTQ_UMMA_PROFILE for a profiling build
-    cmd = [nvcc, *NVCC_FLAGS, *extra, "-o", LIB, *sources()]
+    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB, *sources()]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -95,13 +95,6 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       for (int t0 = 0; t0 < kc_len && !*failed; t0 += KT) {
         const uint32_t kcs = (uint32_t)min(KT, kc_len - t0);
         if (!mbar_wait_spin(&raw_empty[r], rph ^ 1u)) { give_up(DERR_EMPTY_WAIT); break; }
-#ifdef TQ_UMMA_PROFILE
-        if (p.dbg & 4) {
-          mbar_arrive(&raw_full[r]);
-          if (++r == RS) { r = 0; rph ^= 1u; }
-          continue;
-        }
-#endif
         mbar_arrive_expect_tx(&raw_full[r], 8u * kcs * TB);
         for (int i = 0; i < 8; ++i)
           bulk_g2s(raw_s + ((size_t)(r * 8 + i) * KT) * TB, tile_base + ((size_t)(rb0 + i) * p.kc_total + kc_begin + t0) * TB,
@@ -119,13 +112,6 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       uint32_t ph = 0;
       for (int kb = 0; kb < n_kb && !*failed; ++kb) {
         if (!mbar_wait_spin(&empty[s], ph ^ 1u)) { give_up(DERR_EMPTY_WAIT); break; }
-#ifdef TQ_UMMA_PROFILE
-        if (p.dbg & 8) {
-          mbar_arrive(&x_full[s]);
-          if (++s == S) { s = 0; ph ^= 1u; }
-          continue;
-        }
-#endif
         mbar_arrive_expect_tx(&x_full[s], (uint32_t)p.ntok * 128u);
         tma_load_2d(tiles_s + (size_t)s * stage_bytes + (size_t)TERMS * kUmmaRows * 128, &x_map,
                     (kc_begin * 2 + kb) * kUmmaK, m0, &x_full[s]);
@@ -154,22 +140,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     int s = odd;
     uint32_t ph = 0;
     uint32_t tok_x = mbar_test(&x_full[s], 0), tok_a = mbar_test(&a_full[s], 0);
-#ifdef TQ_UMMA_PROFILE
-    long long prof_acc[3] = {0, 0, 0};
-#endif
 #pragma unroll 1
     for (int kb = odd; kb < n_kb; kb += 2) {
-#ifdef TQ_UMMA_PROFILE
-      const long long t0 = clock64();
-      ok = !*failed && mbar_wait_token(&x_full[s], ph, tok_x);
-      const long long t1 = clock64();
-      ok = ok && mbar_wait_token(&a_full[s], ph, tok_a);
-      const long long t2 = clock64();
-      prof_acc[0] += t1 - t0;
-      prof_acc[1] += t2 - t1;
-#else
       ok = !*failed && mbar_wait_token(&x_full[s], ph, tok_x) && mbar_wait_token(&a_full[s], ph, tok_a);
-#endif
       if (!ok) { give_up(DERR_FULL_WAIT); break; }
       tc_fence_after();
       const uint64_t ad = desc0 + (uint64_t)((uint32_t)s * stage_u);
@@ -179,9 +152,6 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         s -= S;
         ph ^= 1u;
       }
-#ifdef TQ_UMMA_PROFILE
-      if (!(p.dbg & 2))
-#endif
       if (leader) {
 #pragma unroll
         for (int k16 = 0; k16 < kUmmaK / 16; ++k16) {
@@ -196,16 +166,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       // thread issues nothing, and here the tensor core already has this step's work.
       tok_x = mbar_test(&x_full[s], ph);
       tok_a = mbar_test(&a_full[s], ph);
-#ifdef TQ_UMMA_PROFILE
-      prof_acc[2] += clock64() - t2;
-#endif
     }
     if (leader) umma_commit(acc_full);           // arrives when every MMA issued so far has completed
     __syncwarp();
-#ifdef TQ_UMMA_PROFILE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && p.prof && lane == 0 && !odd)
-      for (int i = 0; i < 3; ++i) p.prof[i] = prof_acc[i];
-#endif
   } else {
     // ------------------------------------------------------------------ dequant warps
     // Everything that does not change from step to step (which words of the packed tiles this thread
@@ -238,23 +201,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       ph ^= 1u;
     }
     uint32_t tok_raw = mbar_test(&raw_full[r], rph), tok_empty = mbar_test(&empty[s], ph ^ 1u);
-#ifdef TQ_UMMA_PROFILE
-    long long dq_acc[4] = {0, 0, 0, 0};
-    const long long dq_start = clock64();
-#endif
 #pragma unroll 1
     for (int kb = group; kb < n_kb && ok; kb += kUmmaGroups) {
-#ifdef TQ_UMMA_PROFILE
-      const long long t0 = clock64();
-      ok = !*failed && mbar_wait_token(&raw_full[r], rph, tok_raw);
-      const long long t1 = clock64();
-      ok = ok && mbar_wait_token(&empty[s], ph ^ 1u, tok_empty);
-      const long long t2 = clock64();
-      dq_acc[0] += t1 - t0;
-      dq_acc[1] += t2 - t1;
-#else
       ok = !*failed && mbar_wait_token(&raw_full[r], rph, tok_raw) && mbar_wait_token(&empty[s], ph ^ 1u, tok_empty);
-#endif
       if (!ok) { give_up(DERR_FULL_WAIT); break; }
       const int s_cur = s, r_cur = r, within_cur = within;
       s += kUmmaGroups;
@@ -274,9 +223,6 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       uint8_t* a_hi = tiles_s + (size_t)s_cur * stage_bytes;
       uint8_t* a_lo = a_hi + kUmmaRows * 128;
       const uint8_t* raw = raw_s + ((size_t)r_cur * 8 * KT + within_cur) * TB;
-#ifdef TQ_UMMA_PROFILE
-      if (!(p.dbg & 1))
-#endif
 #pragma unroll
       for (int i = 0; i < kCombos; ++i) {
         if constexpr (KIND == I8_ROW) {
@@ -318,10 +264,6 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
           if (TERMS == 2) *reinterpret_cast<uint4*>(a_lo + dst_off[i][jj]) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
       }
-#ifdef TQ_UMMA_PROFILE
-      const long long t3 = clock64();
-      dq_acc[2] += t3 - t2;
-#endif
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
       __syncwarp();
       if (lane == 0) {                                                // one arrival per warp
@@ -332,16 +274,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         tok_raw = leaves ? mbar_test(&raw_full[r], rph) : 1u;
         tok_empty = mbar_test(&empty[s], ph ^ 1u);
       }
-#ifdef TQ_UMMA_PROFILE
-      dq_acc[3] += clock64() - t3;
-#endif
     }
-#ifdef TQ_UMMA_PROFILE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && p.prof && threadIdx.x == 32 * kUmmaFirstDqWarp) {
-      for (int i = 0; i < 4; ++i) p.prof[4 + i] = dq_acc[i];
-      p.prof[8] = clock64() - dq_start;
-    }
-#endif
     // ---- epilogue: D[128 features x ntok tokens] -> y[token][feature]
     if (ok && !*failed) ok = mbar_wait_spin(acc_full, 0);
     if (!ok) give_up(DERR_TMEM);
@@ -549,27 +482,11 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
     if (e != cudaSuccess) return e;
     return launch_k(ctx, kern, grid, dim3(kUmmaThreads), smem, map, p);
   };
-#ifdef TQ_UMMA_PROFILE
-  static long long* prof_dev = nullptr;
-  if (!prof_dev) cudaMalloc(&prof_dev, 16 * sizeof(long long));
-  cudaMemset(prof_dev, 0, 16 * sizeof(long long));
-  p.prof = prof_dev;
-  p.dbg = getenv("TQ_UMMA_DBG") ? atoi(getenv("TQ_UMMA_DBG")) : 0;
-#endif
   cudaError_t e;
   if (w->kind == TQ_I8_ROW) e = go(qgemm_umma_kernel<I8_ROW, 1>);
   else if (w->kind == TQ_Q4_F16) e = terms == 2 ? go(qgemm_umma_kernel<Q4_F16, 2>) : go(qgemm_umma_kernel<Q4_F16, 1>);
   else e = terms == 2 ? go(qgemm_umma_kernel<Q4_F32, 2>) : go(qgemm_umma_kernel<Q4_F32, 1>);
   TQ_CUDA(ctx, e);
-#ifdef TQ_UMMA_PROFILE
-  {
-    long long h[16];
-    cudaStreamSynchronize(ctx->stream);
-    cudaMemcpy(h, prof_dev, sizeof(h), cudaMemcpyDeviceToHost);
-    fprintf(stderr, "umma profile (cycles, CTA 0, %d steps): mma wait_x %lld wait_a %lld issue %lld | dq wait_raw %lld wait_empty %lld work %lld fence+arrive %lld total %lld\n",
-            p.kc_total * 2, h[0], h[1], h[2], h[4], h[5], h[6], h[7], h[8]);
-  }
-#endif
   return TQ_OK;
 }
 

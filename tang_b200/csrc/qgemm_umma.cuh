@@ -63,10 +63,6 @@ struct UmmaParams {
   const int* g_active;    // optional list of group ids with rows (-1 = unused entry); blockIdx.z indexes it
   long long g_tile_stride;   // bytes between the groups' fragment tiles
   int* err;
-#ifdef TQ_UMMA_PROFILE
-  long long* prof;      // cycle counters of CTA 0 (profiling builds only)
-  int dbg;              // bit 0: no dequant math, 1: no MMA, 2: no weight copies, 3: no activation copies
-#endif
 };
 
 // Host-side description of a grouped launch (device arrays come from the router's bookkeeping kernels).

@@ -395,15 +395,8 @@ struct UmmaGroups;
 int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
                       size_t ldy, int terms, const UmmaGroups* grp);
 
-// Activation rows from which the tcgen05 kernel takes over from the mma.sync kernel (TQ_UMMA_MIN_M
-// overrides; 0 disables the tcgen05 path).
-static int umma_min_m() {
-  static int v = [] {
-    const char* e = std::getenv("TQ_UMMA_MIN_M");
-    return e ? std::atoi(e) : 24;
-  }();
-  return v;
-}
+// Activation rows from which the tcgen05 kernel takes over from the mma.sync kernel.
+static int umma_min_m() { return 24; }
 
 }  // namespace tq
 
