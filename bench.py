@@ -325,6 +325,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             ids = [tb.Comm.unique_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             comm = tb.Comm(dev, ids[0], rank, world)
+            comm.enable_peer(64 * 4096)      # the row-parallel sums of a decode step (<= 64 x 4096 f32) go over peer memory
         decode = run_decode(dev, tb, torch, stream, comm, rank, world, args, barrier)
         if comm:
             comm.destroy()
@@ -438,7 +439,8 @@ def build_llama(dev, tb, torch, stream, comm, rank, world, n_layers, max_batch):
         return tb.Buffer(dev, t.data_ptr(), t.numel(), tb.BF16, owns=False)
 
     for l in range(n_layers):
-        model.set_layer(l, tb.LlamaLayerWeights(qw((hl + 2 * kl) * hd, d), qw(d, hl * hd), qw(2 * fl, d), qw(d, fl),
+        # gate/up in the interleaved row order: the SwiGLU becomes the projection's epilogue
+        model.set_layer(l, tb.LlamaLayerWeights(qw((hl + 2 * kl) * hd, d), qw(d, hl * hd), dev.interleave_gate_up(qw(2 * fl, d)), qw(d, fl),
                                                 bf16_vec(d), bf16_vec(d)))
         kbuf, vbuf, _ = model.kv_buffers(l)
         with torch.cuda.stream(stream):     # prefill the cache with bf16 N(0,1), in slices to bound the temporary

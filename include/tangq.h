@@ -145,6 +145,14 @@ TQ_API int tq_q_matvec_host_async(tq_ctx* ctx, const tq_qweight* w, const void* 
  * crates/tang-mesh/src/inference.rs:1306-1413). */
 TQ_API int tq_qweight_concat_rows(tq_ctx* ctx, const tq_qweight* const* parts, size_t n_parts, tq_qweight** out);
 
+/* A fused [gate; up] projection (gate rows, then the same number of up rows) regrouped so that every 16-row block
+ * holds eight gate rows and the eight up rows of the same outputs.  In that order the decode step applies
+ * swiglu_fused_buf (crates/tang-compute/src/device.rs:727-736) inside the projection kernel and the 2 x ffn f32
+ * intermediate never reaches HBM; tq_llama_set_layer accepts either order.  tq_qlinear on the result yields the
+ * outputs in the regrouped order.  Integer codes and scale bits are copied unchanged; the source can be freed
+ * after the next tq_sync. */
+TQ_API int tq_qweight_interleave_gate_up(tq_ctx* ctx, const tq_qweight* w_gate_up, tq_qweight** out);
+
 /* ---- small operators of the decode step ------------------------------------------------------
  * dtypes are TQ_F32 or TQ_BF16 throughout. */
 
@@ -254,7 +262,25 @@ TQ_API int tq_comm_destroy(tq_ctx* ctx, tq_comm* comm);
 TQ_API int tq_comm_abort(tq_comm* comm);
 TQ_API int tq_comm_rank(const tq_comm* comm);
 TQ_API int tq_comm_world(const tq_comm* comm);
+/* Sum of buf_dev [n] f32 over the ranks, in place (the coordinator's sum of crates/tang-mesh/src/allreduce.rs:43-70,
+ * with every rank ending up with the result).  NCCL, unless the communicator has the peer-memory path below and
+ * n fits it: then one kernel per rank stores its partial into every rank's buffer, waits (bounded) for the others'
+ * flags and adds the partials in rank order -- every rank gets the same bits.  A peer that never arrives turns
+ * into TQ_ETIMEOUT at the next tq_sync, with buf_dev left as this rank's own partial. */
 TQ_API int tq_all_reduce_f32(tq_ctx* ctx, tq_comm* comm, float* buf_dev, size_t n);
+/* Gives the communicator the peer-memory path for sums of up to max_elems floats (a multiple of 4): allocates
+ * this rank's buffer, exchanges CUDA IPC handles through the communicator and maps every peer's buffer.  Collective:
+ * every rank calls it with the same max_elems.  Ranks must be separate processes on GPUs with peer access (NVLink).
+ * With world = 1 or more than 8 ranks it does nothing.  No reference counterpart (tang-mesh sums over QUIC). */
+TQ_API int tq_comm_enable_peer(tq_ctx* ctx, tq_comm* comm, size_t max_elems);
+/* The same path over buffers the caller has already made visible to this GPU (its own symmetric-memory
+ * allocator, or a test): peer_bufs_dev[r] is rank r's buffer as addressed from this device, each of
+ * tq_comm_peer_bytes(world, max_elems) bytes, zeroed before the first sum.  The communicator only supports
+ * tq_all_reduce_f32 of at most max_elems floats. */
+TQ_API int tq_comm_peer_local(tq_ctx* ctx, int rank, int world, void* const* peer_bufs_dev, size_t max_elems, tq_comm** out);
+TQ_API size_t tq_comm_peer_bytes(int world, size_t max_elems);
+/* How many times the peer path looks at a peer's flag before it gives up (default 4 Mi looks, a few seconds). */
+TQ_API int tq_comm_set_wait_limit(tq_comm* comm, unsigned polls);
 TQ_API int tq_all_gather(tq_ctx* ctx, tq_comm* comm, const void* send_dev, void* recv_dev, size_t bytes_per_rank);
 TQ_API int tq_all_to_all(tq_ctx* ctx, tq_comm* comm, const void* send_dev, void* recv_dev, size_t bytes_per_peer);
 
@@ -293,8 +319,7 @@ TQ_API int tq_llama_kv_cache(tq_llama* model, size_t layer, void** k_cache_dev, 
  * [0, keep) -- and its length becomes `keep`; shorter sequences are untouched.  The K rows keep the rotation of
  * the positions they were appended at, exactly as the reference's trimmed cache does.  Asynchronous. */
 TQ_API int tq_llama_kv_trim(tq_llama* model, int* seq_lens_io_dev, size_t batch, size_t keep);
-/* The f32 residual stream [max_batch, d_model] after the last tq_llama_decode (before the final
- * norm's residual add is applied to it: it holds h after the last attention block). */
+/* The f32 residual stream [max_batch, d_model] after the last tq_llama_decode (the input of the final norm). */
 TQ_API int tq_llama_hidden(tq_llama* model, float** hidden_dev);
 /* One decode step: sequence b consumes token_ids_dev[b] at position positions_dev[b] (its k, v are
  * appended there) and attends positions 0..positions_dev[b].  max_len > every position.

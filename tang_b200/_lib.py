@@ -50,6 +50,7 @@ PROTOTYPES = {
     "tq_qlinear": (_i, [_p, _p, _p, _i, _sz, _sz, _p, _i, _sz, _p]),
     "tq_q_matvec_host": (_i, [_p, _p, _p, _p, _i, _sz]),
     "tq_q_matvec_host_async": (_i, [_p, _p, _p, _p, _i, _sz]),
+    "tq_qweight_interleave_gate_up": (_i, [_p, _p, _pp]),
     "tq_qweight_concat_rows": (_i, [_p, _pp, _sz, _pp]),
     "tq_rms_norm": (_i, [_p, _p, _i, _p, _p, _i, _sz, _sz, C.c_float, _p, _i, _p]),
     "tq_rope_tables": (_i, [_p, _sz, _sz, C.c_double, _p, _p]),
@@ -69,6 +70,10 @@ PROTOTYPES = {
     "tq_comm_abort": (_i, [_p]),
     "tq_comm_rank": (_i, [_p]),
     "tq_comm_world": (_i, [_p]),
+    "tq_comm_enable_peer": (_i, [_p, _p, _sz]),
+    "tq_comm_peer_local": (_i, [_p, _i, _i, _pp, _sz, _pp]),
+    "tq_comm_peer_bytes": (_sz, [_i, _sz]),
+    "tq_comm_set_wait_limit": (_i, [_p, C.c_uint]),
     "tq_all_reduce_f32": (_i, [_p, _p, _p, _sz]),
     "tq_all_gather": (_i, [_p, _p, _p, _p, _sz]),
     "tq_all_to_all": (_i, [_p, _p, _p, _p, _sz]),

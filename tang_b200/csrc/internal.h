@@ -59,6 +59,7 @@ struct tq_qweight {
   uint8_t* tiles = nullptr;    // fragment tiles (csrc/qlayout.cuh), owned
   size_t tile_bytes = 0;
   float* row_scales = nullptr; // TQ_I8_ROW only, owned
+  bool gate_up_interleaved = false;  // rows 16b..16b+7 are gate rows 8b..8b+7, rows 16b+8..16b+15 the matching up rows
 };
 
 namespace tq {
@@ -91,6 +92,24 @@ inline int bind(tq_ctx* ctx) {
   TQ_CUDA(ctx, cudaSetDevice(ctx->device));
   return TQ_OK;
 }
+
+// The decode step's fused forms of the quantised linear layer (qlinear.cu).  `norm`: the activations are
+// rms_norm(h + delta) * gain instead of x, and h + delta goes to h_out (another buffer than h).  `swiglu`: the weight
+// is a gate/up matrix in the interleaved row order and y receives silu(gate) * up, rows / 2 values per activation row.
+// Up to eight rows run as one kernel; larger batches fall back to the separate operators (xn_tmp / gu_tmp).
+struct QlinearNorm {
+  const float* h = nullptr;
+  const float* delta = nullptr;
+  const void* gain_bf16 = nullptr;
+  float* h_out = nullptr;
+  float eps = 0.f;
+  void* xn_tmp = nullptr;      // bf16 [m][cols]: the normalised rows, when the fused kernel does not apply
+};
+int qlinear_fused(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, const QlinearNorm* norm, size_t m, void* y, int y_dtype,
+                  size_t ldy, bool swiglu, float* gu_tmp);
+
+// silu(gate) * up over the f32 output of a gate/up projection in the interleaved row order: gu [rows][2n] -> out [rows][n].
+int launch_swiglu_interleaved(tq_ctx* ctx, const float* gu, size_t rows, size_t n, void* out, int out_dtype);
 
 int ensure_xprep(tq_ctx* ctx, size_t bytes);
 int ensure_scratch(tq_ctx* ctx, size_t bytes);

@@ -14,6 +14,7 @@
 #include <cuda_bf16.h>
 
 #include <new>
+#include <utility>
 #include <vector>
 
 #include "internal.h"
@@ -24,6 +25,7 @@ extern "C" int tq_all_reduce_f32(tq_ctx*, tq_comm*, float*, size_t);
 extern "C" int tq_all_gather(tq_ctx*, tq_comm*, const void*, void*, size_t);
 extern "C" int tq_comm_world(const tq_comm*);
 extern "C" int tq_comm_rank(const tq_comm*);
+extern "C" int tq_comm_enable_peer(tq_ctx*, tq_comm*, size_t);
 
 namespace tq {
 int launch_qkv_post(tq_ctx* ctx, const float* qkv, const float* cos_t, const float* sin_t, const int* positions,
@@ -91,7 +93,8 @@ struct tq_llama {
   tq_comm* comm = nullptr;
   float *cos_t = nullptr, *sin_t = nullptr;
   // activations
-  float *h = nullptr, *delta = nullptr, *qkv = nullptr, *gu = nullptr, *logits_l = nullptr;
+  float *h = nullptr, *h2 = nullptr, *delta = nullptr, *qkv = nullptr, *gu = nullptr, *logits_l = nullptr;
+  float* h_last = nullptr;   // which of h / h2 holds the residual stream after the last decode step
   __nv_bfloat16 *xn = nullptr, *qb = nullptr, *attn = nullptr, *act = nullptr;
   int* lens = nullptr;
   // prefill workspaces (rows = sequences x chunk length), grown on demand by tq_llama_prefill
@@ -187,6 +190,7 @@ int tq_llama_create(tq_ctx* ctx, const tq_llama_config* cfg, tq_comm* comm, tq_l
   A((void**)&m->cos_t, (size_t)cfg->max_seq * (hd / 2) * 4);
   A((void**)&m->sin_t, (size_t)cfg->max_seq * (hd / 2) * 4);
   A((void**)&m->h, B * d * 4);
+  A((void**)&m->h2, B * d * 4);
   A((void**)&m->delta, B * d * 4);
   A((void**)&m->qkv, B * (q_dim + 2 * kv_dim) * 4);
   A((void**)&m->gu, B * 2 * m->ffn_l * 4);
@@ -289,7 +293,7 @@ int tq_llama_kv_trim(tq_llama* m, int* seq_lens_io_dev, size_t batch, size_t kee
 
 int tq_llama_hidden(tq_llama* m, float** hidden_dev) {
   if (!m || !hidden_dev) return TQ_EINVAL;
-  *hidden_dev = m->h;
+  *hidden_dev = m->h_last ? m->h_last : m->h;
   return TQ_OK;
 }
 
@@ -320,35 +324,62 @@ int tq_llama_decode_at(tq_llama* m, const int* token_ids_dev, const int* positio
   TQ_CUDA(ctx, launch_k(ctx, lens_kernel, dim3((B + 63) / 64), dim3(64), 0, positions_dev, m->lens, B, (int)c.max_seq));
   TQ_STEP(tq_embedding(ctx, m->embed, TQ_BF16, token_ids_dev, B, d, c.vocab, m->h, TQ_F32));
 
+  // The residual stream alternates between two buffers: every pre-norm is fused into the projection that follows it
+  // (each CTA of that kernel forms rms_norm(h + delta) itself), and the kernel's first CTA writes h + delta to the
+  // OTHER buffer while its siblings still read the old one.  With a gate/up weight in the interleaved row order the
+  // SwiGLU is the projection's epilogue.  Per layer: qkv (+norm), RoPE/append, attention, merge, o, gate/up (+norm,
+  // +SwiGLU), down.  Batches above eight rows take the same path through the separate operators.
+  float *h_cur = m->h, *h_nxt = m->h2;
   bool have_delta = false;  // true once `delta` holds a projection output not yet added to h
   for (size_t l = 0; l < m->layers.size(); ++l) {
     const LlamaLayerW& L = m->layers[l];
-    // pre-norm (+ the residual add of the previous block's MLP output)
-    TQ_STEP(tq_rms_norm(ctx, have_delta ? (const void*)m->delta : (const void*)m->h, TQ_F32, have_delta ? m->h : nullptr,
-                        L.attn_norm, TQ_BF16, B, d, c.eps, m->xn, TQ_BF16, have_delta ? m->h : nullptr));
-    TQ_STEP(tq_qlinear(ctx, L.wqkv, m->xn, TQ_BF16, d, B, m->qkv, TQ_F32, q_dim + 2 * kv_dim, nullptr));
+    QlinearNorm n1;
+    n1.h = h_cur;
+    n1.delta = have_delta ? m->delta : nullptr;
+    n1.gain_bf16 = L.attn_norm;
+    n1.h_out = h_nxt;
+    n1.eps = c.eps;
+    n1.xn_tmp = m->xn;
+    TQ_STEP(qlinear_fused(ctx, L.wqkv, nullptr, &n1, B, m->qkv, TQ_F32, q_dim + 2 * kv_dim, false, nullptr));
+    std::swap(h_cur, h_nxt);
     TQ_STEP(launch_qkv_post(ctx, m->qkv, m->cos_t, m->sin_t, positions_dev, rope_positions_dev, B, m->heads_l, m->kv_l, (int)hd, (int)c.max_seq,
                             m->qb, L.k_cache, L.v_cache, seq_stride, 1));
     TQ_STEP(launch_gqa_decode(ctx, m->qb, L.k_cache, L.v_cache, m->lens, B, m->heads_l, m->kv_l, (int)hd, seq_stride,
                               (int)max_len, m->attn, TQ_BF16));
     TQ_STEP(tq_qlinear(ctx, L.wo, m->attn, TQ_BF16, q_dim, B, m->delta, TQ_F32, d, nullptr));
     TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->delta, (size_t)B * d));
-    // h += attention output; pre-norm of the MLP
-    TQ_STEP(tq_rms_norm(ctx, m->delta, TQ_F32, m->h, L.ffn_norm, TQ_BF16, B, d, c.eps, m->xn, TQ_BF16, m->h));
-    TQ_STEP(tq_qlinear(ctx, L.wgu, m->xn, TQ_BF16, d, B, m->gu, TQ_F32, 2 * (size_t)m->ffn_l, nullptr));
-    TQ_STEP(tq_swiglu(ctx, m->gu, m->gu + m->ffn_l, TQ_F32, 2 * (size_t)m->ffn_l, B, m->ffn_l, m->act, TQ_BF16));
+    // h += attention output; pre-norm of the MLP; gate/up; SwiGLU
+    QlinearNorm n2 = n1;
+    n2.h = h_cur;
+    n2.delta = m->delta;
+    n2.gain_bf16 = L.ffn_norm;
+    n2.h_out = h_nxt;
+    if (L.wgu->gate_up_interleaved) {
+      TQ_STEP(qlinear_fused(ctx, L.wgu, nullptr, &n2, B, m->act, TQ_BF16, m->ffn_l, true, m->gu));
+    } else {
+      TQ_STEP(qlinear_fused(ctx, L.wgu, nullptr, &n2, B, m->gu, TQ_F32, 2 * (size_t)m->ffn_l, false, nullptr));
+      TQ_STEP(tq_swiglu(ctx, m->gu, m->gu + m->ffn_l, TQ_F32, 2 * (size_t)m->ffn_l, B, m->ffn_l, m->act, TQ_BF16));
+    }
+    std::swap(h_cur, h_nxt);
     TQ_STEP(tq_qlinear(ctx, L.wdown, m->act, TQ_BF16, m->ffn_l, B, m->delta, TQ_F32, d, nullptr));
     TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->delta, (size_t)B * d));
     have_delta = true;
   }
-  // final norm (adds the last MLP output), LM head on every row (each row is a sequence's last token)
-  TQ_STEP(tq_rms_norm(ctx, m->delta, TQ_F32, m->h, m->final_norm, TQ_BF16, B, d, c.eps, m->xn, TQ_BF16, m->h));
+  // final norm (adds the last MLP output) fused into the LM head, which sees every row (each is a sequence's last token)
+  QlinearNorm nf;
+  nf.h = h_cur;
+  nf.delta = have_delta ? m->delta : nullptr;
+  nf.gain_bf16 = m->final_norm;
+  nf.h_out = h_nxt;
+  nf.eps = c.eps;
+  nf.xn_tmp = m->xn;
+  m->h_last = h_nxt;   // the head kernel writes the full residual stream (h + the last MLP output) there
   if (m->tp == 1) {
-    TQ_STEP(tq_qlinear(ctx, m->lm_head, m->xn, TQ_BF16, d, B, logits_dev, TQ_F32, c.vocab, nullptr));
+    TQ_STEP(qlinear_fused(ctx, m->lm_head, nullptr, &nf, B, logits_dev, TQ_F32, c.vocab, false, nullptr));
   } else {
     // column-parallel head: this rank's vocabulary slice, gathered rank-major: logits_dev is
     // [tp][B][vocab/tp]
-    TQ_STEP(tq_qlinear(ctx, m->lm_head, m->xn, TQ_BF16, d, B, m->logits_l, TQ_F32, m->vocab_l, nullptr));
+    TQ_STEP(qlinear_fused(ctx, m->lm_head, nullptr, &nf, B, m->logits_l, TQ_F32, m->vocab_l, false, nullptr));
     TQ_STEP(tq_all_gather(ctx, m->comm, m->logits_l, logits_dev, (size_t)B * m->vocab_l * sizeof(float)));
   }
 #undef TQ_STEP
@@ -407,7 +438,11 @@ int tq_llama_prefill(tq_llama* m, const int* token_ids_dev, const int* cache_sta
     TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->p_delta, R * d));
     TQ_STEP(tq_rms_norm(ctx, m->p_delta, TQ_F32, m->p_h, L.ffn_norm, TQ_BF16, R, d, c.eps, m->p_xn, TQ_BF16, m->p_h));
     TQ_STEP(tq_qlinear(ctx, L.wgu, m->p_xn, TQ_BF16, d, R, m->p_gu, TQ_F32, 2 * (size_t)m->ffn_l, nullptr));
-    TQ_STEP(tq_swiglu(ctx, m->p_gu, m->p_gu + m->ffn_l, TQ_F32, 2 * (size_t)m->ffn_l, R, m->ffn_l, m->p_act, TQ_BF16));
+    if (L.wgu->gate_up_interleaved) {
+      TQ_STEP(launch_swiglu_interleaved(ctx, m->p_gu, R, m->ffn_l, m->p_act, TQ_BF16));
+    } else {
+      TQ_STEP(tq_swiglu(ctx, m->p_gu, m->p_gu + m->ffn_l, TQ_F32, 2 * (size_t)m->ffn_l, R, m->ffn_l, m->p_act, TQ_BF16));
+    }
     TQ_STEP(tq_qlinear(ctx, L.wdown, m->p_act, TQ_BF16, m->ffn_l, R, m->p_delta, TQ_F32, d, nullptr));
     TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->p_delta, R * d));
     have_delta = true;

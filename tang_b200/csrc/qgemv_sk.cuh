@@ -50,6 +50,18 @@ struct QGemvParams {
   int x_early;              // 1: no kernel that may still be running writes x: load it without waiting;
                             // 2: nor does any of them touch y or the residual, or write x: nothing here waits
                             //    (the workspace pointers below are then this launch's own set)
+  // Fused prologue (norm_w != nullptr; x is then not read): the activations are rms_norm(h + delta) * norm_w, formed by
+  // every CTA from the f32 residual stream (crates/tang-compute/src/device.rs:546-575, rms_norm_residual), and CTA 0
+  // writes h + delta to h_out, a buffer other than h.
+  const float* nh;              // [mx][ld_h]
+  const float* ndelta;          // optional [mx][ld_h]
+  const __nv_bfloat16* norm_w;  // [kx]
+  float* nh_out;                // optional [mx][ld_h]
+  long long ld_h;
+  float norm_eps;
+  // Fused epilogue: rows 0..7 of every 16-row block are gate rows and rows 8..15 the matching up rows; what is stored
+  // is silu(gate) * up (crates/tang-compute/src/device.rs:727-736), n_rows / 2 values per activation row.
+  int swiglu;
   unsigned long long* ws;   // [gridDim.x][2][128] (value bits | 1 << 32): partial sums of row blocks cut by a range
                             // boundary; the tag in the upper half says the value is there; all zero between launches
   int* err;
@@ -186,10 +198,10 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemv_sk_kernel(const QGem
           bulk_g2s(smem + x_off + (size_t)m * x_stride, p.x + (size_t)m * p.ldx, (uint32_t)p.kx * 2u, x_bar, pol_x);
       };
       // The weights never depend on the previous kernel of the stream; the activations usually do.
-      if (p.x_early) load_x();
+      if (p.x_early && !p.norm_w) load_x();
       int issued = 0;
       while (w.left > 0 && issued < S) issue(issued++);
-      if (!p.x_early) {
+      if (!p.x_early && !p.norm_w) {
         pdl_wait();
         load_x();
       }
@@ -207,7 +219,52 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemv_sk_kernel(const QGem
   } else if (warp < W) {
     // ------------------------------------------------------------------ consumer warps
     const int g = lane >> 2, t = lane & 3;
-    bool ok = mbar_wait_bounded(x_bar, 0u, failed, p.err, DERR_FULL_WAIT);
+    bool ok = true;
+    if (p.norm_w) {
+      // ---- fused rms_norm_residual: two passes over h (+ delta), both from L2; every CTA forms the same activations
+      if (p.x_early == 0) pdl_wait();          // h and delta are the previous kernels' outputs
+      float* scratch = reinterpret_cast<float*>(smem + red_off);   // the hand-over buffers are idle until the first flush
+      const int nthr = 32 * W;
+      for (int m = 0; m < p.mx; ++m) {
+        const float* hrow = p.nh + (size_t)m * p.ld_h;
+        const float* drow = p.ndelta ? p.ndelta + (size_t)m * p.ld_h : nullptr;
+        float sq = 0.f;
+        for (int k = 4 * threadIdx.x; k < p.kx; k += 4 * nthr) {
+          float4 v = __ldcg(reinterpret_cast<const float4*>(hrow + k));
+          if (drow) {
+            const float4 d = __ldcg(reinterpret_cast<const float4*>(drow + k));
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+          }
+          sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        sq = warp_sum(sq);
+        if (lane == 0) scratch[warp] = sq;
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * W) : "memory");
+        float total = 0.f;
+#pragma unroll
+        for (int q = 0; q < W; ++q) total += scratch[q];
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * W) : "memory");   // (scratch is reused by the next row)
+        const float inv = 1.0f / sqrtf(total / (float)p.kx + p.norm_eps);
+        uint8_t* xrow_s = smem + x_off + (size_t)m * x_stride;
+        for (int k = 4 * threadIdx.x; k < p.kx; k += 4 * nthr) {
+          float4 v = __ldcg(reinterpret_cast<const float4*>(hrow + k));
+          if (drow) {
+            const float4 d = __ldcg(reinterpret_cast<const float4*>(drow + k));
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+          }
+          const uint2 gw = *reinterpret_cast<const uint2*>(p.norm_w + k);
+          const float g0 = bf16_bits_to_float(gw.x & 0xFFFFu), g1 = bf16_bits_to_float(gw.x >> 16);
+          const float g2 = bf16_bits_to_float(gw.y & 0xFFFFu), g3 = bf16_bits_to_float(gw.y >> 16);
+          const __nv_bfloat162 a = __floats2bfloat162_rn(v.x * inv * g0, v.y * inv * g1);
+          const __nv_bfloat162 b = __floats2bfloat162_rn(v.z * inv * g2, v.w * inv * g3);
+          *reinterpret_cast<uint2*>(xrow_s + 2 * k) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+          if (p.nh_out && blockIdx.x == 0) *reinterpret_cast<float4*>(p.nh_out + (size_t)m * p.ld_h + k) = v;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * W) : "memory");
+    } else {
+      ok = mbar_wait_bounded(x_bar, 0u, failed, p.err, DERR_FULL_WAIT);
+    }
     if constexpr (!kIs8) {
       // offset table: -136 * (sum of the block's 32 activations), per activation row
       const int nblk = p.kx / 32;
@@ -376,6 +433,26 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemv_sk_kernel(const QGem
     const int n_out = p.m_out * 16;            // (row, output row of x) pairs of a row block, <= 128
     const long long grid = gridDim.x;
     auto store = [&](int rb, const float (&vals)[4]) {
+      if (p.swiglu) {
+        // rows 0..7 of the block hold gate values, rows 8..15 the up values of the same eight outputs
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int idx = lane + 32 * i;
+          const float up = __shfl_down_sync(0xffffffffu, vals[i], 8);    // lane l + 8 holds row (l & 15) + 8 of the same m
+          const int r8 = idx & 15, m = idx >> 4;
+          const int o_col = rb * 8 + r8;
+          if (idx < n_out && r8 < 8 && o_col < p.n_rows / 2) {
+            const float g = vals[i];
+            const float act = g * (1.0f / (1.0f + expf(-g))) * up;   // the formula of swiglu_kernel, term for term
+            const size_t o = (size_t)m * p.ldy + o_col;
+            if (p.y_bf16)
+              reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(act);
+            else
+              reinterpret_cast<float*>(p.y)[o] = act;
+          }
+        }
+        return;
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int idx = lane + 32 * i;

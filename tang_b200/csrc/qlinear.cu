@@ -226,8 +226,10 @@ static cudaError_t launch_sk_kind(tq_ctx* ctx, const QGemvParams& p, unsigned gr
 }
 
 static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
-                            void* y, int y_dtype, size_t ldy, const float* residual, int* status) {
+                            void* y, int y_dtype, size_t ldy, const float* residual, int* status,
+                            const QlinearNorm* norm = nullptr, bool swiglu = false) {
   if (mx > 8) return false;
+  if (norm && (w->cols != (size_t)w->n_kc * kTileK)) return false;   // the fused norm wants whole 128-k chunks
   const bool m1 = mx == 1;
   const int kx = w->n_kc * kTileK;
   const size_t stage = (size_t)16 * qk_tile_bytes(w->kind);
@@ -241,11 +243,12 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   // early could sit between two of these launches.
   struct R { uintptr_t lo, hi; };
   const int m_out = mx / combine;
-  const R rx = {(uintptr_t)xs, (uintptr_t)xs + ((size_t)(mx - 1) * ldxs + kx) * 2};
+  const R rx = norm ? R{(uintptr_t)norm->h, (uintptr_t)norm->h + ((size_t)(mx - 1) * kx + kx) * 4}
+                    : R{(uintptr_t)xs, (uintptr_t)xs + ((size_t)(mx - 1) * ldxs + kx) * 2};
   const R ry = {(uintptr_t)y, (uintptr_t)y + ((size_t)(m_out - 1) * ldy + w->rows) * (y_dtype == TQ_BF16 ? 2 : 4)};
   const R rr = {(uintptr_t)residual, residual ? (uintptr_t)residual + ((size_t)(m_out - 1) * ldy + w->rows) * 4 : (uintptr_t)residual};
   auto hit = [](const R& a, const tq_ctx::Range& b) { return a.lo < b.hi && b.lo < a.hi; };
-  int mode = (ctx->owns_stream && ctx->pdl && !ctx->inflight_unknown && ctx->n_inflight + 3 <= 96) ? 2 : 0;
+  int mode = (ctx->owns_stream && ctx->pdl && !ctx->inflight_unknown && ctx->n_inflight + 3 <= 96 && !norm) ? 2 : 0;
   for (int i = 0; mode && i < ctx->n_inflight; ++i) {
     const tq_ctx::Range& f = ctx->inflight[i];
     if (f.written && hit(rx, f)) mode = 0;                                     // x comes from a kernel that may still run
@@ -291,6 +294,13 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   p.combine = combine;
   p.y_bf16 = y_dtype == TQ_BF16;
   p.stages = stages;
+  p.nh = norm ? norm->h : nullptr;
+  p.ndelta = norm ? norm->delta : nullptr;
+  p.norm_w = norm ? static_cast<const __nv_bfloat16*>(norm->gain_bf16) : nullptr;
+  p.nh_out = norm ? norm->h_out : nullptr;
+  p.ld_h = kx;
+  p.norm_eps = norm ? norm->eps : 0.f;
+  p.swiglu = swiglu ? 1 : 0;
   p.x_early = mode;
   const unsigned set = ctx->gemv_seq++ % kGemvSets;
   p.ws = ctx->gemv_ws + (size_t)set * kGemvMaxGrid * 2 * 128;
@@ -303,7 +313,8 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
     default: e = launch_sk_kind<I8_ROW>(ctx, p, (unsigned)grid, smem, m1, small); break;
   }
   *status = e == cudaSuccess ? TQ_OK : fail(ctx, TQ_ECUDA, "persistent GEMV launch failed: %s", cudaGetErrorString(e));
-  if (e == cudaSuccess) {   // (launch_k has just marked the stream's state unknown)
+  if (e == cudaSuccess && !norm) {   // (launch_k has just marked the stream's state unknown; a fused norm also writes
+                                     // h_out, so what follows it simply waits)
     if (mode == 0) ctx->n_inflight = 0;   // this kernel waits for everything before it
     ctx->inflight_unknown = false;
     ctx->inflight[ctx->n_inflight++] = {rx.lo, rx.hi, false};
@@ -394,6 +405,42 @@ bool umma_supported(const tq_qweight* w, size_t m);
 struct UmmaGroups;
 int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
                       size_t ldy, int terms, const UmmaGroups* grp);
+
+// ---------------------------------------------------------------------------------------------
+// Gate/up weights in the row order the fused SwiGLU epilogue wants: out row block b = gate rows 8b..8b+7 then up
+// rows 8b..8b+7.  A half of a fragment tile (eight rows: its packed weights and its scales) is contiguous, so the
+// regrouping is a copy of half-tiles; no number changes.
+// ---------------------------------------------------------------------------------------------
+__global__ void interleave_gate_up_kernel(const uint8_t* src, uint8_t* dst, int kind, int n_kc, int n_rb_out, int f_rows) {
+  const int tile_bytes = qk_tile_bytes(kind), wb = qk_weight_bytes(kind), sb = qk_scale_bytes(kind);
+  const size_t t = blockIdx.x;                      // (out row block, k chunk)
+  const int rb = (int)(t / n_kc), kc = (int)(t % n_kc);
+  if (rb >= n_rb_out) return;
+  uint8_t* out = dst + t * tile_bytes;
+  for (int h = 0; h < 2; ++h) {
+    const int src_row = (h == 0 ? 0 : f_rows) + 8 * rb;                 // first of the eight source rows
+    const int srb = src_row / 16, sh = (src_row / 8) & 1;
+    const uint8_t* in = src + ((size_t)srb * n_kc + kc) * tile_bytes;
+    for (int i = threadIdx.x * 16; i < wb / 2; i += blockDim.x * 16)
+      *reinterpret_cast<uint4*>(out + h * (wb / 2) + i) = *reinterpret_cast<const uint4*>(in + sh * (wb / 2) + i);
+    for (int i = threadIdx.x * 16; i < sb / 2; i += blockDim.x * 16)
+      *reinterpret_cast<uint4*>(out + wb + h * (sb / 2) + i) = *reinterpret_cast<const uint4*>(in + wb + sh * (sb / 2) + i);
+  }
+}
+
+// silu(gate) * up over a projection output in the interleaved order: gu [rows][2n] f32, out [rows][n].
+__global__ void swiglu_interleaved_kernel(const float* gu, size_t rows, size_t n, void* out, int out_dt) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * n) return;
+  const size_t row = idx / n, i = idx % n;
+  const size_t src = row * 2 * n + (i / 8) * 16 + (i % 8);
+  const float g = gu[src], u = gu[src + 8];
+  const float v = g * (1.0f / (1.0f + expf(-g))) * u;
+  if (out_dt == TQ_BF16) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  else static_cast<float*>(out)[idx] = v;
+}
 
 // Activation rows from which the tcgen05 kernel takes over from the mma.sync kernel.
 static int umma_min_m() { return 24; }
@@ -746,3 +793,83 @@ int tq_q_matvec_host_async(tq_ctx* ctx, const tq_qweight* w, const void* x_host,
 }
 
 }  // extern "C"
+
+
+namespace tq {
+
+int launch_swiglu_interleaved(tq_ctx* ctx, const float* gu, size_t rows, size_t n, void* out, int out_dtype) {
+  TQ_CUDA(ctx, launch_k(ctx, swiglu_interleaved_kernel, dim3((unsigned)((rows * n + 255) / 256)), dim3(256), 0, gu, rows, n, out, out_dtype));
+  return TQ_OK;
+}
+
+int qlinear_fused(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, const QlinearNorm* norm, size_t m, void* y, int y_dtype,
+                  size_t ldy, bool swiglu, float* gu_tmp) {
+  if (int st = bind(ctx)) return st;
+  TQ_REQUIRE(ctx, w && y && (norm || x_bf16), "fused linear: null argument");
+  TQ_REQUIRE(ctx, !swiglu || w->gate_up_interleaved, "fused linear: the SwiGLU epilogue needs a weight from tq_qweight_interleave_gate_up");
+  if (m == 0) return TQ_OK;
+  const size_t cols = w->cols;
+  if (m <= 8 && w->cols == (size_t)w->n_kc * kTileK) {
+    int st = TQ_OK;
+    if (launch_qgemv_sk(ctx, w, static_cast<const __nv_bfloat16*>(x_bf16), cols, (int)m, 1, y, y_dtype, ldy, nullptr, &st, norm, swiglu))
+      return st;
+  }
+  // the separate operators
+  const void* xin = x_bf16;
+  if (norm) {
+    TQ_REQUIRE(ctx, norm->xn_tmp != nullptr, "fused linear: no buffer for the normalised rows");
+    if (int st = tq_rms_norm(ctx, norm->delta ? (const void*)norm->delta : (const void*)norm->h, TQ_F32, norm->delta ? norm->h : nullptr,
+                             norm->gain_bf16, TQ_BF16, m, cols, norm->eps, norm->xn_tmp, TQ_BF16, norm->h_out))
+      return st;
+    xin = norm->xn_tmp;
+  }
+  if (!swiglu) return tq_qlinear(ctx, w, xin, TQ_BF16, cols, m, y, y_dtype, ldy, nullptr);
+  TQ_REQUIRE(ctx, gu_tmp != nullptr, "fused linear: no buffer for the gate/up projection");
+  if (int st = tq_qlinear(ctx, w, xin, TQ_BF16, cols, m, gu_tmp, TQ_F32, w->rows, nullptr)) return st;
+  const size_t n = w->rows / 2;
+  TQ_REQUIRE(ctx, ldy == n, "fused linear: the SwiGLU output must be dense");
+  return launch_swiglu_interleaved(ctx, gu_tmp, m, n, y, y_dtype);
+}
+
+}  // namespace tq
+
+extern "C" int tq_qweight_interleave_gate_up(tq_ctx* ctx, const tq_qweight* w_gate_up, tq_qweight** out) {
+  if (int st = tq::bind(ctx)) return st;
+  TQ_REQUIRE(ctx, w_gate_up && out, "tq_qweight_interleave_gate_up: null argument");
+  *out = nullptr;
+  TQ_REQUIRE(ctx, !w_gate_up->gate_up_interleaved, "tq_qweight_interleave_gate_up: the weight is interleaved already");
+  TQ_REQUIRE(ctx, w_gate_up->rows % 32 == 0, "tq_qweight_interleave_gate_up: gate and up need a multiple of 16 rows each");
+  tq_qweight* w = new (std::nothrow) tq_qweight();
+  if (!w) return tq::fail(ctx, TQ_ENOMEM, "out of host memory");
+  *w = *w_gate_up;
+  w->tiles = nullptr;
+  w->row_scales = nullptr;
+  w->gate_up_interleaved = true;
+  cudaError_t e = cudaMalloc(&w->tiles, w->tile_bytes);
+  if (e == cudaSuccess && w->kind == TQ_I8_ROW) e = cudaMalloc(&w->row_scales, w->rows * sizeof(float));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (w->tiles) cudaFree(w->tiles);
+    delete w;
+    return tq::fail(ctx, TQ_ENOMEM, "tq_qweight_interleave_gate_up: allocation failed");
+  }
+  const int f = (int)(w->rows / 2);
+  tq::interleave_gate_up_kernel<<<(unsigned)((size_t)w->n_rb * w->n_kc), 64, 0, ctx->stream>>>(w_gate_up->tiles, w->tiles, w->kind, w->n_kc,
+                                                                                       w->n_rb, f);
+  ctx->launches++;
+  e = cudaGetLastError();
+  if (e == cudaSuccess && w->kind == TQ_I8_ROW) {
+    // row scales follow their rows: out row 16b + i (i < 8) is gate row 8b + i, out row 16b + 8 + i is up row 8b + i
+    for (int b = 0; b < w->n_rb && e == cudaSuccess; ++b) {
+      e = cudaMemcpyAsync(w->row_scales + 16 * (size_t)b, w_gate_up->row_scales + 8 * (size_t)b, 8 * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream);
+      if (e == cudaSuccess)
+        e = cudaMemcpyAsync(w->row_scales + 16 * (size_t)b + 8, w_gate_up->row_scales + f + 8 * (size_t)b, 8 * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream);
+    }
+  }
+  if (e != cudaSuccess) {
+    tq_qweight_free(ctx, w);
+    return tq::fail(ctx, TQ_ECUDA, "tq_qweight_interleave_gate_up: %s", cudaGetErrorString(e));
+  }
+  *out = w;
+  return TQ_OK;
+}

@@ -442,8 +442,18 @@ def _add_ops(cls):
         self._check(self._L.tq_qweight_concat_rows(self._ctx, arr, len(parts), C.byref(h)))
         return self._wrap_q(h)
 
+    def interleave_gate_up(self, w: QBuffer, free_source: bool = True) -> QBuffer:
+        """A fused [gate; up] weight regrouped for the in-kernel SwiGLU (``tq_qweight_interleave_gate_up``)."""
+        h = C.c_void_p()
+        self._check(self._L.tq_qweight_interleave_gate_up(self._ctx, C.c_void_p(w.handle), C.byref(h)))
+        out = self._wrap_q(h)
+        if free_source:
+            self.sync()
+            w.free()
+        return out
+
     for f in (rms_norm, rms_norm_residual, rope_tables, rope_forward, swiglu_fused, embedding, kv_attention, gqa_decode,
-              gqa_prefill, concat_rows):
+              gqa_prefill, concat_rows, interleave_gate_up):
         setattr(cls, f.__name__, f)
 
 

@@ -35,6 +35,26 @@ class Comm:
             raise _lib.TangqError(st, "tq_comm_unique_id failed (NCCL not loadable?)")
         return buf.raw
 
+    def enable_peer(self, max_elems: int) -> None:
+        """Peer-memory path for all-reduces of up to `max_elems` floats (``tq_comm_enable_peer``); collective."""
+        self.dev._check(self.dev._L.tq_comm_enable_peer(self.dev._ctx, C.c_void_p(self.handle), max_elems))
+
+    @classmethod
+    def peer_local(cls, dev: QuantComputeDevice, rank: int, world: int, bufs, max_elems: int) -> "Comm":
+        """A communicator over buffers already visible to this GPU (``tq_comm_peer_local``): `bufs[r]` is rank r's."""
+        self = cls.__new__(cls)
+        self.dev = dev
+        arr = (C.c_void_p * world)(*[b.ptr for b in bufs])
+        h = C.c_void_p()
+        dev._check(dev._L.tq_comm_peer_local(dev._ctx, rank, world, arr, max_elems, C.byref(h)))
+        self.handle, self.rank, self.world = h.value, rank, world
+        return self
+
+    def set_wait_limit(self, polls: int) -> None:
+        st = self.dev._L.tq_comm_set_wait_limit(C.c_void_p(self.handle), polls)
+        if st != _lib.TQ_OK:
+            raise _lib.TangqError(st, "tq_comm_set_wait_limit: no peer path on this communicator")
+
     def all_reduce(self, buf: Buffer) -> None:
         self.dev._check(self.dev._L.tq_all_reduce_f32(self.dev._ctx, C.c_void_p(self.handle), C.c_void_p(buf.ptr), buf.n))
 

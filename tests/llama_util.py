@@ -70,7 +70,9 @@ class HostLlama:
         head = rows(self.lm_head, rank * vl, (rank + 1) * vl) + (vl, d)
         return out, head
 
-    def to_device(self, dev, max_seq, max_batch, comm=None):
+    def to_device(self, dev, max_seq, max_batch, comm=None, interleave=True):
+        """`interleave`: hand the gate/up weight over in the interleaved row order (SwiGLU fused into the projection);
+        False keeps the reference's [gate; up] order and the separate SwiGLU operator."""
         import tang_b200 as tb
 
         tp = comm.world if comm else 1
@@ -81,7 +83,8 @@ class HostLlama:
         layers, head = self.shard(rank, tp)
         for i, L in enumerate(layers):
             up = lambda w: dev.upload_qarrays(KIND, w[1], w[0], w[2], w[3])
-            model.set_layer(i, tb.LlamaLayerWeights(up(L["wqkv"]), up(L["wo"]), up(L["wgu"]), up(L["wdown"]),
+            wgu = dev.interleave_gate_up(up(L["wgu"])) if interleave else up(L["wgu"])
+            model.set_layer(i, tb.LlamaLayerWeights(up(L["wqkv"]), up(L["wo"]), wgu, up(L["wdown"]),
                                                     dev.upload(L["attn_norm"], tb.BF16), dev.upload(L["ffn_norm"], tb.BF16)))
         model.set_head(dev.upload(self.embed, tb.BF16), dev.upload(self.final_norm, tb.BF16),
                        dev.upload_qarrays(KIND, head[1], head[0], head[2], head[3]))

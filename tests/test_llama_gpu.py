@@ -31,12 +31,12 @@ def dev():
     d.close()
 
 
-def run_case(dev, orc, host, B, ctx_lens, max_seq, steps=1):
+def run_case(dev, orc, host, B, ctx_lens, max_seq, steps=1, interleave=True):
     import tang_b200 as tb
 
     rng = np.random.default_rng(99)
     kv_dim = host.n_kv * host.hd
-    model = host.to_device(dev, max_seq, B)
+    model = host.to_device(dev, max_seq, B, interleave=interleave)
     # prefill caches with bf16 N(0,1) on both sides
     ok, ov = [], []
     for li in range(host.n_layers):
@@ -77,6 +77,13 @@ def run_case(dev, orc, host, B, ctx_lens, max_seq, steps=1):
 def test_small_model_ragged_batch(dev, orc):
     host = HostLlama(np.random.default_rng(1), n_layers=2, d=256, n_heads=4, n_kv=2, hd=128, ffn=512, vocab=1024)
     run_case(dev, orc, host, B=3, ctx_lens=[0, 70, 131], max_seq=160, steps=2)
+
+
+def test_gate_up_in_the_reference_order_takes_the_separate_swiglu(dev, orc):
+    """[gate; up] as the reference concatenates it (no interleaving): same result through the separate operator."""
+    host = HostLlama(np.random.default_rng(1), n_layers=2, d=256, n_heads=4, n_kv=2, hd=128, ffn=512, vocab=1024)
+    run_case(dev, orc, host, B=3, ctx_lens=[0, 70, 131], max_seq=160, steps=1, interleave=False)
+    run_case(dev, orc, host, B=12, ctx_lens=list(range(5, 125, 10)), max_seq=160, steps=1, interleave=True)   # > 8 rows: separate operators
 
 
 def test_single_sequence_many_heads(dev, orc):

@@ -17,7 +17,7 @@ def _run(mode, n, port, worker="tp_worker.py"):
            "--master-port", str(port), os.path.join(HERE, worker), mode]
     env = dict(os.environ)
     env.setdefault("OMP_NUM_THREADS", "2")
-    if mode == "gpu":
+    if mode.startswith("gpu"):
         env["NCCL_NVLS_ENABLE"] = "0"
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
 
@@ -35,6 +35,18 @@ def test_tp2_decode_on_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     r = _run("gpu", 2, 29632)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.gpu
+def test_tp2_decode_with_peer_memory_allreduce_on_two_gpus():
+    """The same decode step with the row-parallel sums going through the one-shot peer-memory all-reduce
+    (plain peer stores + bounded flag waits), eagerly and replayed from a graph."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = _run("gpu_peer", 2, 29635)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
 
 

@@ -109,6 +109,8 @@ def main():
         ids = [tb.Comm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         comm = tb.Comm(dev, ids[0], rank, world)
+        if mode == "gpu_peer":      # the row-parallel sums through the one-shot peer-memory all-reduce instead of NCCL
+            comm.enable_peer(B * host.d)
         model = host.to_device(dev, max_seq, B, comm)
         kl = host.n_kv // world
         sl = slice(rank * kl * host.hd, (rank + 1) * kl * host.hd)
@@ -120,6 +122,21 @@ def main():
         logits = dev.alloc(B * host.vocab, tb.F32)
         model.decode(dev.upload(tokens, tb.I32), dev.upload(np.array(ctx, np.int32), tb.I32), B, max(ctx) + 1, logits)
         dev.sync()
+        if mode == "gpu_peer":      # and once more from a recorded graph: the sequence number lives on the device
+            first = logits.to_vec().copy()
+            for li in range(host.n_layers):      # (the step appended K/V rows: put the caches back)
+                kbuf, vbuf, _ = model.kv_buffers(li)
+                for buf, src in ((kbuf, caches[li][0]), (vbuf, caches[li][1])):
+                    a = np.ascontiguousarray(src[:, :, sl])
+                    dev._check(dev._L.tq_upload(dev._ctx, buf.ptr, a.ctypes.data, a.nbytes))
+            tok_d, pos_d = dev.upload(tokens, tb.I32), dev.upload(np.array(ctx, np.int32), tb.I32)
+            dev.begin_capture()
+            model.decode(tok_d, pos_d, B, max(ctx) + 1, logits)
+            g = dev.end_capture()
+            for _ in range(3):
+                g.launch()
+            dev.sync()
+            assert np.array_equal(logits.to_vec(), first), "graph replay of the peer all-reduce differs"
         got = logits.to_vec().reshape(world, B, host.vocab // world).transpose(1, 0, 2).reshape(B, host.vocab)
         tol = 2e-2
     ok = True
