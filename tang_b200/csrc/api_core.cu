@@ -128,6 +128,8 @@ int tq_ctx_destroy(tq_ctx* ctx) {
   if (ctx->splitk) cudaFree(ctx->splitk);
   if (ctx->dev_err) cudaFree(ctx->dev_err);
   if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
+  if (ctx->hostx_ring) cudaFree(ctx->hostx_ring);
+  if (ctx->hostx_tags) cudaFree(ctx->hostx_tags);
   if (ctx->host_err) cudaFreeHost(ctx->host_err);
   if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
@@ -143,6 +145,8 @@ int tq_sync(tq_ctx* ctx) {
   // the status word rides behind the work on the same stream: one wait, no second round trip
   TQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_err, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->inflight_unknown = false;   // the stream has drained: nothing is in flight
+  ctx->n_inflight = 0;
   const int code = *ctx->host_err;
   if (code != 0) {
     cudaMemset(ctx->dev_err, 0, (1 + kTileCounters) * sizeof(int));   // a kernel that gave up may have left tile counters half counted

@@ -12,6 +12,8 @@
 
 constexpr int kTileCounters = 1024;
 constexpr int kGemvSets = 6, kGemvMaxGrid = 512;
+constexpr int kHostXSlots = 64;
+constexpr size_t kHostXSlotBytes = 64 * 1024;
 
 struct tq_ctx {
   int device = 0;
@@ -42,6 +44,13 @@ struct tq_ctx {
   bool inflight_unknown = true;
   int n_inflight = 0;
   struct Range { uintptr_t lo, hi; bool written; } inflight[96];
+  // Host-vector matvecs (tq_q_matvec_host*) with pinned vectors: a one-CTA kernel copies x from the pinned host
+  // vector into the next slot of this ring and tags it; the GEMV looks at the tag.  kHostXSlots exceeds the
+  // longest run of kernels that wait for nothing (the in-flight list holds 32), so a slot is never rewritten
+  // while a kernel that reads it can still be running.
+  uint8_t* hostx_ring = nullptr;     // [kHostXSlots][kHostXSlotBytes]
+  unsigned* hostx_tags = nullptr;    // [kHostXSlots]
+  unsigned hostx_seq = 0;
   unsigned long long ws_generation = 0;        // bumped whenever a workspace is freed and reallocated: graphs recorded
                                                // before that hold the old addresses and refuse to launch
   unsigned long long launches = 0;             // kernels launched through this context
@@ -135,6 +144,19 @@ inline cudaError_t launch_k(tq_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3
   ctx->inflight_unknown = true;
   ctx->n_inflight = 0;
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
+// The same launch for a kernel that neither reads nor writes anything a kernel in flight touches and that waits for
+// nothing before its last instruction (the host-vector staging kernel): what the context knows about the kernels
+// in flight stays valid.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k_independent(tq_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+  const bool unknown = ctx->inflight_unknown;
+  const int n = ctx->n_inflight;
+  cudaError_t e = launch_k(ctx, kern, grid, block, smem, args...);
+  ctx->inflight_unknown = unknown;
+  ctx->n_inflight = n;
+  return e;
 }
 
 inline size_t dtype_size(int dt) {

@@ -62,6 +62,11 @@ struct QGemvParams {
   // Fused epilogue: rows 0..7 of every 16-row block are gate rows and rows 8..15 the matching up rows; what is stored
   // is silu(gate) * up (crates/tang-compute/src/device.rs:727-736), n_rows / 2 values per activation row.
   int swiglu;
+  // x written by a small staging kernel launched just before this one (host vectors): the word *x_tag becomes x_seq
+  // once x is complete.  That kernel waits for nothing, so this one may look at the word instead of waiting for it
+  // to finish; null otherwise.
+  const unsigned* x_tag;
+  unsigned x_seq;
   unsigned long long* ws;   // [gridDim.x][2][128] (value bits | 1 << 32): partial sums of row blocks cut by a range
                             // boundary; the tag in the upper half says the value is there; all zero between launches
   int* err;
@@ -198,10 +203,28 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemv_sk_kernel(const QGem
           bulk_g2s(smem + x_off + (size_t)m * x_stride, p.x + (size_t)m * p.ldx, (uint32_t)p.kx * 2u, x_bar, pol_x);
       };
       // The weights never depend on the previous kernel of the stream; the activations usually do.
-      if (p.x_early && !p.norm_w) load_x();
       int issued = 0;
+      if (p.x_tag) {
+        // activations staged by the kernel launched just before this one: ring first, then a bounded look at its tag
+        while (w.left > 0 && issued < S) issue(issued++);
+        uint32_t polls = 0;
+        for (;;) {
+          unsigned v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.x_tag) : "memory");
+          if (v == p.x_seq) break;
+          if (++polls > kMaxPolls) {
+            *failed = 1;
+            atomicCAS(p.err, 0, (int)DERR_FULL_WAIT);
+            break;
+          }
+          __nanosleep(32);
+        }
+        load_x();
+      } else if (p.x_early && !p.norm_w) {
+        load_x();
+      }
       while (w.left > 0 && issued < S) issue(issued++);
-      if (!p.x_early && !p.norm_w) {
+      if (!p.x_early && !p.norm_w && !p.x_tag) {   // (a second arrival on x_bar in one phase would overrun its count)
         pdl_wait();
         load_x();
       }

@@ -2,6 +2,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -227,7 +228,8 @@ static cudaError_t launch_sk_kind(tq_ctx* ctx, const QGemvParams& p, unsigned gr
 
 static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
                             void* y, int y_dtype, size_t ldy, const float* residual, int* status,
-                            const QlinearNorm* norm = nullptr, bool swiglu = false) {
+                            const QlinearNorm* norm = nullptr, bool swiglu = false, const unsigned* x_tag = nullptr,
+                            unsigned x_seq = 0) {
   if (mx > 8) return false;
   if (norm && (w->cols != (size_t)w->n_kc * kTileK)) return false;   // the fused norm wants whole 128-k chunks
   const bool m1 = mx == 1;
@@ -256,26 +258,30 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   }
   // Shared memory per CTA.  Kernels that wait for nothing run side by side: four small CTAs per SM (a two-stage
   // ring each) keep the most copies in flight and the most warps busy (measured per 14336 x 4096 launch: 5.8 us,
-  // against 6.3 us for three CTAs of eight warps and 6.9 us for two).  A kernel that waits for its activations
-  // takes more than half of an SM's shared memory: its ring fills while the small kernels before it run (they
-  // still fit beside it), and no SM can be handed two of its CTAs (a decode step measured 2.48 ms with CTAs
-  // that fit twice, 2.00 ms so).
+  // against 6.3 us for three CTAs of eight warps and 6.9 us for two).
   const size_t quarter = 56 * 1024, third = 74 * 1024, half = 113 * 1024, most = 150 * 1024, whole = 226 * 1024;
-  const bool small = mode == 2 && sk_fixed_bytes(w->kind, 4, kx, mx, m1) + 2 * stage <= quarter;
+  // (with nothing in flight the kernel has the GPU to itself, like one that waits: the larger shape below)
+  const bool small = mode == 2 && ctx->n_inflight > 0 && sk_fixed_bytes(w->kind, 4, kx, mx, m1) + 2 * stage <= quarter;
   const size_t fixed = sk_fixed_bytes(w->kind, small ? 4 : 8, kx, mx, m1);
   size_t budget = whole;
   if (small) budget = quarter;
-  else if (mode == 2 && fixed + 3 * stage <= third) budget = third;
-  else if (mode != 0 && fixed + 3 * stage <= half) budget = half;
-  else if (fixed + 3 * stage <= most) budget = most;
-  if (!small && fixed + 3 * stage > budget) return false;
+  else if (mode == 2 && ctx->n_inflight > 0 && fixed + 3 * stage <= third) budget = third;
+  else if (fixed + 3 * stage <= half) {
+    // A kernel that waits (for its activations or before its stores): two CTAs per SM, and a grid that fills both
+    // slots of every SM so that none is handed two while another gets none (a grid of one CTA per SM with room for
+    // two measured 2.48 ms per decode step; one large CTA per SM 1.89 ms; this 1.79 ms).
+    budget = half;
+    if (units >= 2LL * ctx->sm_count * 8) grid = 2LL * ctx->sm_count;
+  } else if (fixed + 3 * stage <= most) budget = most;
+  if (fixed + 2 * stage > budget) return false;
   int stages = (int)((budget - fixed) / stage);
   if (stages > kSkMaxStages) stages = kSkMaxStages;
   const size_t smem = fixed + (size_t)stages * stage;
   // Running entirely unordered relies on the rotating workspace sets: a CTA only leaves once the kernel before
   // its own has completed, so kernel n and kernel n + kGemvSets can both have resident CTAs only if kGemvSets - 1
-  // whole grids fit beside one more CTA.  Full-size grids and a CTA count per SM below the number of sets rule it out.
-  if (mode == 2 && !(grid == ctx->sm_count && (int)(233472 / (smem + 1024)) + 1 <= kGemvSets)) mode = 1;
+  // whole grids fit on the GPU beside one more CTA.  Grids of at least one CTA per SM rule that out.
+  const long long resident = (long long)(233472 / (smem + 1024)) * ctx->sm_count;   // CTAs of this shape the GPU can hold
+  if (mode == 2 && !(grid >= ctx->sm_count && (long long)(kGemvSets - 1) * grid >= resident)) mode = 1;
   QGemvParams p;
   p.tiles = w->tiles;
   p.row_scales = w->row_scales;
@@ -301,6 +307,8 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   p.ld_h = kx;
   p.norm_eps = norm ? norm->eps : 0.f;
   p.swiglu = swiglu ? 1 : 0;
+  p.x_tag = x_tag;
+  p.x_seq = x_seq;
   p.x_early = mode;
   const unsigned set = ctx->gemv_seq++ % kGemvSets;
   p.ws = ctx->gemv_ws + (size_t)set * kGemvMaxGrid * 2 * 128;
@@ -739,6 +747,114 @@ int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x_dtype,
 
 }  // extern "C"
 
+// Stages the activations of a host-vector matvec: x (bf16 or f32, in PINNED host memory, read through its device
+// alias) -> bf16 rows of kx elements in a ring slot, zero beyond `cols`; f32 values as three bf16 terms (rows 3r, 3r+1,
+// 3r+2, as prep_x_kernel).  It waits for nothing until its last instruction, so it runs beside whatever is in flight;
+// the GEMV that consumes the slot looks at the tag word instead of waiting for this kernel to finish.
+__global__ void __launch_bounds__(256) stage_host_x_kernel(const void* x, int dtype, size_t m, size_t cols, size_t kx,
+                                                           __nv_bfloat16* slot, unsigned* tag, unsigned seq) {
+  pdl_launch_dependents();
+  // Every load below crosses the bus: 16 bytes per load, all of a thread's loads issued before any is used.
+  if (dtype == TQ_BF16 && cols == kx && ((uintptr_t)x & 15) == 0) {
+    const size_t n16 = m * kx / 8;
+    const uint4* src = static_cast<const uint4*>(x);
+    uint4* dst = reinterpret_cast<uint4*>(slot);
+    for (size_t i0 = threadIdx.x; i0 < n16; i0 += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * blockDim.x < n16) v[u] = src[i0 + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * blockDim.x < n16) dst[i0 + u * blockDim.x] = v[u];
+    }
+  } else if (dtype == TQ_F32 && cols == kx && ((uintptr_t)x & 15) == 0) {
+    const size_t n4 = m * kx / 4;
+    const float4* src = static_cast<const float4*>(x);
+    for (size_t i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * blockDim.x < n4) v[u] = src[i0 + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const size_t i = i0 + u * blockDim.x;
+        if (i >= n4) continue;
+        const size_t row = (4 * i) / kx, col = (4 * i) % kx;
+        const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat16 hi = __float2bfloat16_rn(f[e]);
+          const float r1 = f[e] - __bfloat162float(hi);
+          const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+          slot[(3 * row + 0) * kx + col + e] = hi;
+          slot[(3 * row + 1) * kx + col + e] = mid;
+          slot[(3 * row + 2) * kx + col + e] = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+        }
+      }
+    }
+  } else
+  for (size_t idx = threadIdx.x; idx < m * kx; idx += blockDim.x) {
+    const size_t row = idx / kx, col = idx % kx;
+    if (dtype == TQ_BF16) {
+      slot[row * kx + col] = col < cols ? static_cast<const __nv_bfloat16*>(x)[row * cols + col] : __float2bfloat16_rn(0.f);
+    } else {
+      const float v = col < cols ? static_cast<const float*>(x)[row * cols + col] : 0.f;
+      const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+      const float r1 = v - __bfloat162float(hi);
+      const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+      slot[(3 * row + 0) * kx + col] = hi;
+      slot[(3 * row + 1) * kx + col] = mid;
+      slot[(3 * row + 2) * kx + col] = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(tag), "r"(seq) : "memory");
+  pdl_wait();   // kernels of a stream still complete in launch order
+}
+
+static void* pinned_alias(const void* host) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer) return attr.devicePointer;
+  cudaGetLastError();   // an unregistered pointer is not an error here
+  return nullptr;
+}
+
+// Host vectors in pinned memory, bf16 or f32, up to eight staged rows: no copy is queued on the stream at all.  A
+// one-CTA kernel pulls x over the bus into a ring slot, the persistent GEMV stores y straight into the pinned result,
+// and consecutive calls overlap on the GPU like any other run of independent GEMVs.  Returns false when the call
+// does not qualify (the caller then takes the copying path).
+static bool matvec_host_pinned(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m, int* status) {
+  if (dtype == TQ_F64 || ctx->capturing || !ctx->owns_stream || !ctx->pdl) return false;
+  const int combine = dtype == TQ_F32 ? 3 : 1;
+  const size_t mx = m * combine, kx = (size_t)w->n_kc * kTileK;
+  if (mx > 8 || mx * kx * 2 > kHostXSlotBytes) return false;
+  void* xa = pinned_alias(x_host);
+  void* ya = xa ? pinned_alias(y_host) : nullptr;
+  if (!xa || !ya) return false;
+  if (!ctx->hostx_ring) {
+    if (cudaMalloc(&ctx->hostx_ring, (size_t)kHostXSlots * kHostXSlotBytes) != cudaSuccess ||
+        cudaMalloc(&ctx->hostx_tags, kHostXSlots * sizeof(unsigned)) != cudaSuccess ||
+        cudaMemsetAsync(ctx->hostx_tags, 0, kHostXSlots * sizeof(unsigned), ctx->stream) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+  }
+  const unsigned seq = ++ctx->hostx_seq;                 // never 0: a zeroed tag matches nothing
+  const unsigned slot = seq % kHostXSlots;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ctx->hostx_ring + (size_t)slot * kHostXSlotBytes);
+  if (launch_k_independent(ctx, stage_host_x_kernel, dim3(1), dim3(256), 0, (const void*)xa, dtype, m, w->cols, kx, xs, ctx->hostx_tags + slot,
+                           seq) != cudaSuccess) {
+    *status = fail(ctx, TQ_ECUDA, "tq_q_matvec_host: staging kernel launch failed");
+    return true;
+  }
+  if (!launch_qgemv_sk(ctx, w, xs, kx, (int)mx, combine, ya, dtype == TQ_BF16 ? TQ_BF16 : TQ_F32, w->rows, nullptr, status, nullptr, false,
+                       ctx->hostx_tags + slot, seq))
+    return false;   // (the staged slot is simply not used)
+  return true;
+}
+
 // The host-vector call; `wait` = return only when y_host holds the result.
 static int matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m, bool wait) {
   if (int st = bind(ctx)) return st;
@@ -746,6 +862,10 @@ static int matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host, voi
   TQ_REQUIRE(ctx, dtype == TQ_F64 || dtype == TQ_F32 || dtype == TQ_BF16, "tq_q_matvec_host: dtype must be f64, f32 or bf16");
   if (m == 0) return TQ_OK;
   TQ_REQUIRE(ctx, x_host && y_host, "tq_q_matvec_host: null vector");
+  {
+    int st = TQ_OK;
+    if (matvec_host_pinned(ctx, w, x_host, y_host, dtype, m, &st)) return st != TQ_OK ? st : (wait ? tq_sync(ctx) : TQ_OK);
+  }
   const size_t nx = m * w->cols, ny = m * w->rows;
   const size_t es = dtype == TQ_F64 ? 8 : dtype == TQ_F32 ? 4 : 2;
   const size_t dev_es = dtype == TQ_BF16 ? 2 : 4;
