@@ -399,6 +399,29 @@ TQ_API int tq_mla_absorb_q(tq_ctx* ctx, const tq_qweight* w_qk_stacked, const vo
 TQ_API int tq_mla_unabsorb(tq_ctx* ctx, const tq_qweight* w_uv_stacked, const void* o_lat_bf16_dev, size_t batch,
                            size_t n_heads, size_t v_dim, void* out_dev, int out_dtype);
 
+/* One MLA attention layer of a decode step, composed from the calls above (no reference counterpart):
+ *   c_q = q_a h                      [q_lora]            (h bf16 [batch, d_model])
+ *   c_q = rms_norm(c_q) * gain       when the layer has a gain (eps = norm_eps)
+ *   q[h] = q_b[h] c_q                [nope_dim | 64] per head, the 64 rope dimensions rotated (interleaved pairs,
+ *                                    device.rs:582-610) by the table row of the query's position lens[b] - 1
+ *   o_lat = tq_mla_decode(absorb(q)) over the latent cache (which already holds the current token's row)
+ *   out = W_O concat_h(W_uv[h] o_lat[h])  f32 [batch, d_model], summed over the ranks when heads are sharded.
+ * All five weights are int8 with one f32 scale per row (any kind tq_qlinear takes works).  n_heads is THIS rank's
+ * head count: q_b, W_qk and W_uv hold its heads' rows, W_O [d_model, n_heads * v_dim] its heads' columns; the
+ * cache is replicated.  rope tables: tq_rope_tables(head_dim = 64, max_pos, ...).  The layer owns a workspace
+ * for max_batch <= 64 rows, so tq_mla_layer_decode allocates nothing and can be captured in a graph. */
+typedef struct tq_mla tq_mla;
+typedef struct tq_mla_config {
+  uint32_t d_model, n_heads, q_lora, kv_lora, nope_dim, rope_dim, v_dim, max_batch, max_pos;
+  float norm_eps;
+} tq_mla_config;
+TQ_API int tq_mla_create(tq_ctx* ctx, const tq_mla_config* cfg, const tq_qweight* q_a, const void* q_a_norm_gain_bf16_dev_or_null,
+                         const tq_qweight* q_b, const tq_qweight* w_qk_stacked, const tq_qweight* w_uv_stacked,
+                         const tq_qweight* w_o, const float* rope_cos_dev, const float* rope_sin_dev, tq_mla** out);
+TQ_API int tq_mla_destroy(tq_mla* layer);
+TQ_API int tq_mla_layer_decode(tq_mla* layer, const void* h_bf16_dev, const void* cache_bf16_dev, const int* lens_dev, size_t batch,
+                               size_t seq_stride, size_t max_len, tq_comm* comm_or_null, float* out_dev);
+
 /* ---- CUDA graphs ------------------------------------------------------------------------------
  * CudaComputeDevice::begin_capture / end_capture (crates/tang-compute/src/cuda.rs:344-356): every
  * asynchronous call made on the context between begin and end is recorded instead of run, and

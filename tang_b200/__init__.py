@@ -7,8 +7,8 @@ from ._lib import (BF16, F16, F32, F64, I8, I32, I8_ROW, Q4_F16, Q4_F32, Q8_F32,
 from .device import Buffer, Graph, QBuffer, QuantComputeDevice, QuantizedQ4, QuantizedQ8, SamplerConfig
 from .checkpoint import SafetensorsError, TensorView, quantize_linear, read_safetensors, write_safetensors
 from .llama import Comm, LlamaConfig, LlamaLayerWeights, LlamaModel
-from .mla import mla_decode
+from .mla import MlaConfig, MlaLayer, mla_decode
 from .moe import MoeConfig, MoeLayer, moe_router
 
-__all__ = ["read_safetensors", "write_safetensors", "quantize_linear", "TensorView", "SafetensorsError", "SamplerConfig", "mla_decode", "MoeLayer", "MoeConfig", "moe_router", "LlamaModel", "LlamaConfig", "LlamaLayerWeights", "Comm", "Graph", "QuantComputeDevice", "QuantizedQ4", "QuantizedQ8", "Buffer", "QBuffer", "TangqError", "load",
+__all__ = ["read_safetensors", "write_safetensors", "quantize_linear", "TensorView", "SafetensorsError", "SamplerConfig", "mla_decode", "MlaLayer", "MlaConfig", "MoeLayer", "MoeConfig", "moe_router", "LlamaModel", "LlamaConfig", "LlamaLayerWeights", "Comm", "Graph", "QuantComputeDevice", "QuantizedQ4", "QuantizedQ8", "Buffer", "QBuffer", "TangqError", "load",
            "F32", "BF16", "F16", "I8", "U8", "I32", "F64", "Q4_F32", "Q4_F16", "Q8_F32", "I8_ROW"]

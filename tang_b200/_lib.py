@@ -95,6 +95,9 @@ PROTOTYPES = {
     "tq_mla_decode": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, C.c_float, _p]),
     "tq_mla_absorb_q": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _p]),
     "tq_mla_unabsorb": (_i, [_p, _p, _p, _sz, _sz, _sz, _p, _i]),
+    "tq_mla_create": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _pp]),
+    "tq_mla_destroy": (_i, [_p]),
+    "tq_mla_layer_decode": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _p, _p]),
     "tq_graph_begin": (_i, [_p]),
     "tq_graph_end": (_i, [_p, _pp]),
     "tq_graph_launch": (_i, [_p, _p]),

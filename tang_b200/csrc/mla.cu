@@ -284,11 +284,144 @@ __global__ void mla_place_rope_kernel(const __nv_bfloat16* q_rope, __nv_bfloat16
   if (i < n_bh * kR) q_full[(i / kR) * kRow + kC + i % kR] = q_rope[i];
 }
 
+// q [batch][n_heads][nope + 64] bf16 straight from the q_b projection: rotates each head's 64 rope dimensions
+// (interleaved pairs, as ComputeDevice::rope_forward, crates/tang-compute/src/device.rs:582-610) by the table row of
+// the query's position lens[b] - 1 and writes them behind the head's latent query in q_full.
+__global__ void mla_rope_place_kernel(const __nv_bfloat16* q, int q_head_ld, int nope, const int* lens, const float* cos_t,
+                                      const float* sin_t, int max_pos, __nv_bfloat16* q_full, int n_heads, size_t n_bh) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr int half = kR / 2;
+  if (i >= n_bh * half) return;
+  const size_t bh = i / half;
+  const int pr = (int)(i % half);
+  int pos = lens[bh / n_heads] - 1;
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const __nv_bfloat16* src = q + bh * q_head_ld + nope + 2 * pr;
+  const float x0 = __bfloat162float(src[0]), x1 = __bfloat162float(src[1]);
+  const float c = cos_t[(size_t)pos * half + pr], sn = sin_t[(size_t)pos * half + pr];
+  __nv_bfloat16* dst = q_full + bh * kRow + kC + 2 * pr;
+  dst[0] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)));
+  dst[1] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c)));
+}
+
 }  // namespace tq
+
+struct tq_mla {
+  tq_ctx* ctx = nullptr;
+  tq_mla_config cfg{};
+  const tq_qweight *q_a = nullptr, *q_b = nullptr, *w_qk = nullptr, *w_uv = nullptr, *w_o = nullptr;
+  const void* q_norm_gain = nullptr;       // bf16 [q_lora] or null
+  const float *cos_t = nullptr, *sin_t = nullptr;
+  // workspace for max_batch rows
+  float* qc = nullptr;                     // [B][q_lora] f32: q_a's output
+  __nv_bfloat16* qc_n = nullptr;           // [B][q_lora]: normalised
+  __nv_bfloat16* q = nullptr;              // [B][n_heads][nope + rope]
+  __nv_bfloat16* q_full = nullptr;         // [B][n_heads][576]
+  __nv_bfloat16* o_lat = nullptr;          // [B][n_heads][512]
+  __nv_bfloat16* o = nullptr;              // [B][n_heads][v_dim]
+};
 
 using namespace tq;
 
 extern "C" {
+
+int tq_mla_create(tq_ctx* ctx, const tq_mla_config* cfg, const tq_qweight* q_a, const void* q_a_norm_gain_bf16_dev_or_null,
+                  const tq_qweight* q_b, const tq_qweight* w_qk_stacked, const tq_qweight* w_uv_stacked, const tq_qweight* w_o,
+                  const float* rope_cos_dev, const float* rope_sin_dev, tq_mla** out) {
+  if (int st = bind(ctx)) return st;
+  TQ_REQUIRE(ctx, cfg && out && q_a && q_b && w_qk_stacked && w_uv_stacked && w_o && rope_cos_dev && rope_sin_dev,
+             "tq_mla_create: null argument");
+  *out = nullptr;
+  const size_t H = cfg->n_heads, qh = (size_t)cfg->nope_dim + cfg->rope_dim;
+  TQ_REQUIRE(ctx, cfg->kv_lora == (uint32_t)kC && cfg->rope_dim == (uint32_t)kR, "tq_mla_create: kv_lora must be %d and rope_dim %d", kC, kR);
+  TQ_REQUIRE(ctx, H > 0 && H % 16 == 0, "tq_mla_create: heads (per rank) must be a multiple of 16");
+  TQ_REQUIRE(ctx, cfg->max_batch >= 1 && cfg->max_batch <= 64 && cfg->max_pos >= 1, "tq_mla_create: max_batch must be 1..64, max_pos >= 1");
+  TQ_REQUIRE(ctx, cfg->nope_dim % 8 == 0, "tq_mla_create: nope_dim must be a multiple of 8");
+  TQ_REQUIRE(ctx, q_a->rows == cfg->q_lora && q_a->cols == cfg->d_model, "tq_mla_create: q_a must be [%u, %u]", cfg->q_lora, cfg->d_model);
+  TQ_REQUIRE(ctx, q_b->rows == H * qh && q_b->cols == cfg->q_lora, "tq_mla_create: q_b must be [%zu * %zu, %u]", H, qh, cfg->q_lora);
+  TQ_REQUIRE(ctx, w_qk_stacked->rows == H * kC && w_qk_stacked->cols == cfg->nope_dim, "tq_mla_create: stacked W_qk must be [%zu * %d, %u]", H, kC,
+             cfg->nope_dim);
+  TQ_REQUIRE(ctx, w_uv_stacked->rows == H * cfg->v_dim && w_uv_stacked->cols == (size_t)kC, "tq_mla_create: stacked W_uv must be [%zu * %u, %d]", H,
+             cfg->v_dim, kC);
+  TQ_REQUIRE(ctx, w_o->rows == cfg->d_model && w_o->cols == H * cfg->v_dim, "tq_mla_create: W_O must be [%u, %zu * %u]", cfg->d_model, H, cfg->v_dim);
+  tq_mla* m = new (std::nothrow) tq_mla();
+  if (!m) return fail(ctx, TQ_ENOMEM, "out of host memory");
+  m->ctx = ctx;
+  m->cfg = *cfg;
+  m->q_a = q_a;
+  m->q_b = q_b;
+  m->w_qk = w_qk_stacked;
+  m->w_uv = w_uv_stacked;
+  m->w_o = w_o;
+  m->q_norm_gain = q_a_norm_gain_bf16_dev_or_null;
+  m->cos_t = rope_cos_dev;
+  m->sin_t = rope_sin_dev;
+  const size_t B = cfg->max_batch;
+  cudaError_t e = cudaMalloc(&m->qc, B * cfg->q_lora * sizeof(float));
+  if (e == cudaSuccess) e = cudaMalloc(&m->qc_n, B * cfg->q_lora * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&m->q, B * H * qh * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&m->q_full, B * H * kRow * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&m->o_lat, B * H * kC * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&m->o, B * H * cfg->v_dim * 2);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    tq_mla_destroy(m);
+    return fail(ctx, TQ_ENOMEM, "tq_mla_create: workspace allocation failed");
+  }
+  *out = m;
+  return TQ_OK;
+}
+
+int tq_mla_destroy(tq_mla* m) {
+  if (!m) return TQ_OK;
+  if (m->ctx) cudaSetDevice(m->ctx->device);
+  for (void* p : {(void*)m->qc, (void*)m->qc_n, (void*)m->q, (void*)m->q_full, (void*)m->o_lat, (void*)m->o})
+    if (p) cudaFree(p);
+  delete m;
+  return TQ_OK;
+}
+
+int tq_mla_layer_decode(tq_mla* m, const void* h_bf16_dev, const void* cache_bf16_dev, const int* lens_dev, size_t batch,
+                        size_t seq_stride, size_t max_len, tq_comm* comm_or_null, float* out_dev) {
+  if (!m || !m->ctx) return TQ_EINVAL;
+  tq_ctx* ctx = m->ctx;
+  if (int st = bind(ctx)) return st;
+  if (batch == 0) return TQ_OK;
+  const tq_mla_config& c = m->cfg;
+  TQ_REQUIRE(ctx, h_bf16_dev && cache_bf16_dev && lens_dev && out_dev, "tq_mla_layer_decode: null pointer");
+  TQ_REQUIRE(ctx, batch <= c.max_batch, "tq_mla_layer_decode: batch %zu exceeds the layer's max_batch %u", batch, c.max_batch);
+  const size_t H = c.n_heads, qh = (size_t)c.nope_dim + c.rope_dim;
+  // hidden -> compressed query (f32) -> RMSNorm (when the layer has a gain) -> per-head [nope | rope] queries
+  if (m->q_norm_gain) {
+    if (int st = tq_qlinear(ctx, m->q_a, h_bf16_dev, TQ_BF16, c.d_model, batch, m->qc, TQ_F32, c.q_lora, nullptr)) return st;
+    QlinearNorm norm;
+    norm.h = m->qc;
+    norm.gain_bf16 = m->q_norm_gain;
+    norm.eps = c.norm_eps;
+    norm.xn_tmp = m->qc_n;
+    if (int st = qlinear_fused(ctx, m->q_b, nullptr, &norm, batch, m->q, TQ_BF16, H * qh, false, nullptr)) return st;
+  } else {
+    if (int st = tq_qlinear(ctx, m->q_a, h_bf16_dev, TQ_BF16, c.d_model, batch, m->qc_n, TQ_BF16, c.q_lora, nullptr)) return st;
+    if (int st = tq_qlinear(ctx, m->q_b, m->qc_n, TQ_BF16, c.q_lora, batch, m->q, TQ_BF16, H * qh, nullptr)) return st;
+  }
+  // absorb W_UK: the nope part of each head is read in place (row stride H * qh, head stride qh)
+  if (int st = launch_qgemm_grouped(ctx, m->w_qk, (int)H, m->q, H * qh, (int)batch, nullptr, nullptr, 0, (long long)qh, (long long)kRow,
+                                    m->q_full, TQ_BF16, H * kRow))
+    return st;
+  const size_t n = batch * H * (kR / 2);
+  mla_rope_place_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(m->q, (int)qh, (int)c.nope_dim, lens_dev, m->cos_t, m->sin_t,
+                                                                              (int)c.max_pos, m->q_full, (int)H, batch * H);
+  ctx->launches++;
+  TQ_CUDA(ctx, cudaGetLastError());
+  if (int st = tq_mla_decode(ctx, m->q_full, cache_bf16_dev, lens_dev, batch, H, kC, kR, seq_stride, max_len,
+                             1.0f / sqrtf((float)qh), m->o_lat))
+    return st;
+  if (int st = tq_mla_unabsorb(ctx, m->w_uv, m->o_lat, batch, H, c.v_dim, m->o, TQ_BF16)) return st;
+  // row-parallel output projection over this rank's heads, then the sum over the ranks
+  if (int st = tq_qlinear(ctx, m->w_o, m->o, TQ_BF16, H * c.v_dim, batch, out_dev, TQ_F32, c.d_model, nullptr)) return st;
+  if (comm_or_null && tq_comm_world(comm_or_null) > 1) return tq_all_reduce_f32(ctx, comm_or_null, out_dev, batch * c.d_model);
+  return TQ_OK;
+}
 
 int tq_mla_absorb_q(tq_ctx* ctx, const tq_qweight* w_qk_stacked, const void* q_nope_bf16_dev, const void* q_rope_bf16_dev,
                     size_t batch, size_t n_heads, size_t nope_dim, void* q_full_bf16_dev) {

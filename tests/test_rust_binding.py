@@ -39,7 +39,7 @@ def test_every_exported_symbol_is_declared_with_its_arity():
         assert len(params) == len(_lib.PROTOTYPES[name][1]), name
     # by-value structs of the ABI are #[repr(C)] with every field of the header
     names = {n for n, _ in structs}
-    assert names == {"tq_sampler_config", "tq_llama_config", "tq_moe_config"}
+    assert names == {"tq_sampler_config", "tq_llama_config", "tq_moe_config", "tq_mla_config"}
     cfg = dict(structs)["tq_llama_config"]
     assert [f for f, _ in cfg] == ["n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab", "max_seq",
                                    "max_batch", "eps", "rope_base"]
