@@ -311,6 +311,14 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
     # ---- Llama-3-8B-shaped decode step, tensor parallel over the ranks of this job
     decode = None
+    comm = None
+    if world > 1 and not (args.no_decode and args.no_extras):
+        import torch.distributed as dist
+
+        ids = [tb.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = tb.Comm(dev, ids[0], rank, world)
+        comm.enable_peer(64 * 7168)      # the row-parallel sums of a decode step (<= 64 rows of d_model f32) go over peer memory
     if not args.no_decode:
         graph.free()
         graph = None
@@ -318,25 +326,19 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             L_.tq_qweight_free(dev._ctx, h)
         del packed, scales, y
         torch.cuda.empty_cache()
-        comm = None
-        if world > 1:
-            import torch.distributed as dist
-
-            ids = [tb.Comm.unique_id() if rank == 0 else None]
-            dist.broadcast_object_list(ids, src=0)
-            comm = tb.Comm(dev, ids[0], rank, world)
-            comm.enable_peer(64 * 4096)      # the row-parallel sums of a decode step (<= 64 x 4096 f32) go over peer memory
         decode = run_decode(dev, tb, torch, stream, comm, rank, world, args, barrier)
-        if comm:
-            comm.destroy()
 
     extras = None
-    if world == 1 and not args.no_extras:
+    if not args.no_extras:
         if graph is not None:
             graph.free()
             graph = None
         torch.cuda.empty_cache()
-        extras = run_extras(dev, tb, torch, stream, measured_peaks()[0])
+        peak_gbs = measured_peaks()[0]
+        extras = run_extras(dev, tb, torch, stream, peak_gbs) if world == 1 else {}
+        extras.update(run_sharded_extras(dev, tb, torch, stream, peak_gbs, comm, rank, world, barrier))
+    if comm:
+        comm.destroy()
 
     if rank == 0:
         bytes_launch = algorithmic_bytes(m)
@@ -693,66 +695,6 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
     del ws
     torch.cuda.empty_cache()
 
-    # ---- MoE layer, d 2048, 64 routed + 2 shared experts of width 1408, top-6
-    d, ffn, E, k, nsh = 2048, 1408, 64, 6, 2
-    wg = bf16((E, d), 0.02)
-    layer = tb.MoeLayer(dev, tb.MoeConfig(d, ffn, E, k, nsh, 0, 0, 1), tb.Buffer(dev, wg.data_ptr(), wg.numel(), tb.BF16, owns=False),
-                        q4(E * 2 * ffn, d), q4(E * d, ffn), [q4(2 * ffn, d) for _ in range(nsh)], [q4(d, ffn) for _ in range(nsh)])
-    per_expert = 3 * (ffn * d // 2 + ffn * d // 32 * 2)
-    moe = []
-    for T in (1, 64, 256, 4096):
-        h = bf16((T, d))
-        hb = tb.Buffer(dev, h.data_ptr(), h.numel(), tb.BF16, owns=False)
-        o, idx, _w = layer.forward(hb, T, want_routing=True)
-        dev.sync()
-        distinct = int(len(set(idx.to_vec().tolist())))
-        ob = dev.alloc(T * d, tb.F32)
-        dev.begin_capture()
-        layer.forward(hb, T, out=ob)
-        g = dev.end_capture()
-        ms = _time_ms(torch, stream, dev, g.launch, 10 if T <= 256 else 3)
-        g.free()
-        byt = (distinct + nsh) * per_expert
-        moe.append({"tokens": T, "us": ms * 1e3, "distinct_routed_experts": distinct, "weight_bytes_touched": byt,
-                    "gbs": byt / ms / 1e6, "tflops": 2.0 * T * (k + nsh) * 3 * ffn * d / ms / 1e9})
-    out["moe_dsv2_lite_layer"] = moe
-    layer.destroy()
-    torch.cuda.empty_cache()
-
-    # ---- MLA decode attention, 128 heads, latent 512 + rope 64, int8 per-row W_UK / W_UV
-    H, NOPE, VD, CL, RP = 128, 128, 128, 512, 64
-    wq, wu = i8(H * CL, NOPE), i8(H * VD, CL)
-    mla = []
-    for ctx, B in ((4096, 1), (16384, 16), (32768, 64)):
-        cache = torch.empty((B, ctx, CL + RP), dtype=torch.bfloat16, device="cuda")
-        with torch.cuda.stream(stream):
-            for b in range(B):
-                cache[b].copy_(torch.randn((ctx, CL + RP), device="cuda", generator=gen))
-        stream.synchronize()
-        qn, qr = bf16((B, H, NOPE)), bf16((B, H, RP))
-        lens = dev.upload(np.full(B, ctx, np.int32), tb.I32)
-        q_full, o_lat, o = dev.alloc(B * H * (CL + RP), tb.BF16), dev.alloc(B * H * CL, tb.BF16), dev.alloc(B * H * VD, tb.F32)
-
-        def fn():   # absorb W_UK into q, attend over the latent cache, un-absorb with W_UV
-            dev._check(L_.tq_mla_absorb_q(dev._ctx, C.c_void_p(wq.handle), C.c_void_p(qn.data_ptr()), C.c_void_p(qr.data_ptr()),
-                                          B, H, NOPE, C.c_void_p(q_full.ptr)))
-            dev._check(L_.tq_mla_decode(dev._ctx, C.c_void_p(q_full.ptr), C.c_void_p(cache.data_ptr()), C.c_void_p(lens.ptr), B, H,
-                                        CL, RP, ctx * (CL + RP), ctx, 1.0 / (NOPE + RP) ** 0.5, C.c_void_p(o_lat.ptr)))
-            dev._check(L_.tq_mla_unabsorb(dev._ctx, C.c_void_p(wu.handle), C.c_void_p(o_lat.ptr), B, H, VD, C.c_void_p(o.ptr), tb.F32))
-        fn()
-        dev.sync()
-        dev.begin_capture()
-        fn()
-        g = dev.end_capture()
-        ms = _time_ms(torch, stream, dev, g.launch, 5)
-        g.free()
-        byt = B * ctx * (CL + RP) * 2
-        mla.append({"ctx": ctx, "batch": B, "us": ms * 1e3, "cache_bytes": byt, "gbs": byt / ms / 1e6,
-                    "tflops": B * ctx * H * 2176.0 / ms / 1e9, "frac_of_hbm_peak": byt / ms / 1e6 / peak_gbs})
-        del cache
-        torch.cuda.empty_cache()
-    out["mla_dsv3_decode"] = mla
-
     # ---- prefill attention: one sequence, Llama-3-8B heads (32 query / 8 KV heads of 128), causal chunk of q_len positions
     pre = []
     for q_len in (512, 2048):
@@ -769,6 +711,133 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
         flops = 4.0 * nh * hd * q_len * (q_len + 1) / 2          # QK^T and PV over the causal half
         pre.append({"q_len": q_len, "us": ms * 1e3, "tflops": flops / ms / 1e9})
     out["gqa_prefill_llama_heads"] = pre
+    return out
+
+
+def run_sharded_extras(dev, tb, torch, stream, peak_gbs, comm, rank, world, barrier):
+    """The MoE layer with its experts over the ranks and the MLA layer with its heads over the ranks; at N = 1 the
+    same calls without a communicator.  Times are the max over the ranks."""
+    import ctypes as C
+
+    L_ = dev._L
+    gen = torch.Generator(device="cuda").manual_seed(77)      # same seed on every rank: replicated tensors are equal
+    out = {}
+
+    def q4(rows, cols):
+        with torch.cuda.stream(stream):
+            pay = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device="cuda", generator=gen)
+            sc = (torch.rand((rows, cols // 32), device="cuda", generator=gen) * 0.018 + 0.002).half()
+        stream.synchronize()
+        w = dev.qweight_from_device(tb.Q4_F16, pay.data_ptr(), sc.data_ptr(), rows, cols)
+        dev.sync()
+        return w
+
+    def i8(rows, cols):
+        with torch.cuda.stream(stream):
+            pay = torch.randint(-127, 128, (rows, cols), dtype=torch.int8, device="cuda", generator=gen)
+            sc = torch.rand(rows, device="cuda", generator=gen) * 0.009 + 0.001
+        stream.synchronize()
+        w = dev.qweight_from_device(tb.I8_ROW, pay.data_ptr(), sc.data_ptr(), rows, cols)
+        dev.sync()
+        return w
+
+    def bf16(shape, std=1.0):
+        with torch.cuda.stream(stream):
+            t = (torch.randn(shape, device="cuda", generator=gen) * std).bfloat16()
+        stream.synchronize()
+        return t
+
+    def timed(fn, reps):
+        fn()
+        dev.sync()
+        dev.begin_capture()
+        fn()
+        g = dev.end_capture()
+        barrier()
+        ms = _time_ms(torch, stream, dev, g.launch, reps)
+        g.free()
+        if world > 1:
+            import torch.distributed as dist
+
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        return ms
+
+    # ---- MoE layer, d 2048, 64 routed + 2 shared experts of width 1408, top-6; experts over the ranks
+    d, ffn, E, k, nsh = 2048, 1408, 64, 6, 2
+    n_local = E // world
+    wg = bf16((E, d), 0.02)
+    layer = tb.MoeLayer(dev, tb.MoeConfig(d, ffn, E, k, nsh, 0, rank, world), tb.Buffer(dev, wg.data_ptr(), wg.numel(), tb.BF16, owns=False),
+                        q4(n_local * 2 * ffn, d), q4(n_local * d, ffn), [q4(2 * ffn, d) for _ in range(nsh)], [q4(d, ffn) for _ in range(nsh)])
+    per_expert = 3 * (ffn * d // 2 + ffn * d // 32 * 2)
+    moe = []
+    for T in (1, 64, 256, 4096):
+        h = bf16((T, d))                                      # the same tokens on every rank
+        hb = tb.Buffer(dev, h.data_ptr(), h.numel(), tb.BF16, owns=False)
+        o, idx, _w = layer.forward(hb, T, comm=comm, want_routing=True)
+        dev.sync()
+        distinct = int(len(set(idx.to_vec().tolist())))
+        ob = dev.alloc(T * d, tb.F32)
+        reps = 10 if T <= 256 else 3
+        ms = timed(lambda: layer.forward(hb, T, out=ob, comm=comm), reps)
+        byt = (distinct + nsh) * per_expert
+        row = {"tokens": T, "us": ms * 1e3, "distinct_routed_experts": distinct, "weight_bytes_touched": byt,
+               "gbs": byt / ms / 1e6, "tflops": 2.0 * T * (k + nsh) * 3 * ffn * d / ms / 1e9,
+               "form": "one GPU" if world == 1 else "tokens replicated, experts over the ranks, all-reduce of the outputs"}
+        if world > 1 and T % world == 0:
+            # tokens sharded over the ranks: all-to-all dispatch to the experts' owners and all-to-all combine back
+            tl = T // world
+            hl = tb.Buffer(dev, h[rank * tl:(rank + 1) * tl].data_ptr(), tl * d, tb.BF16, owns=False)
+            ol = dev.alloc(tl * d, tb.F32)
+            ms2 = timed(lambda: layer.forward_dispatch(hl, tl, comm=comm, out=ol), reps)
+            row["dispatch"] = {"us": ms2 * 1e3, "tokens_per_rank": tl, "tflops": 2.0 * T * (k + nsh) * 3 * ffn * d / ms2 / 1e9,
+                               "form": "tokens over the ranks, all-to-all dispatch and combine"}
+        moe.append(row)
+    out["moe_dsv2_lite_layer"] = moe
+    layer.destroy()
+    torch.cuda.empty_cache()
+
+    # ---- MLA decode, 128 heads over the ranks, latent 512 + rope 64, int8 per-row weights.  The attention core
+    # (absorb W_UK, attend over the latent cache, un-absorb W_UV) and the whole layer with q_a [1536, d], q_b and the
+    # row-parallel W_O at d_model 7168 (an assumption: the configuration names no hidden size).
+    H, NOPE, VD, CL, RP, QL, DM = 128 // world, 128, 128, 512, 64, 1536, 7168
+    wq, wu = i8(H * CL, NOPE), i8(H * VD, CL)
+    max_pos = 32768 + 1
+    gain = bf16((QL,), 0.03)
+    mlayer = tb.MlaLayer(dev, tb.MlaConfig(DM, H, QL, CL, NOPE, RP, VD, 64, max_pos, 1e-6), i8(QL, DM),
+                         tb.Buffer(dev, gain.data_ptr(), QL, tb.BF16, owns=False), i8(H * (NOPE + RP), QL), wq, wu, i8(DM, H * VD))
+    mla = []
+    for ctx, B in ((4096, 1), (16384, 16), (32768, 64)):
+        cache = torch.empty((B, ctx, CL + RP), dtype=torch.bfloat16, device="cuda")
+        with torch.cuda.stream(stream):
+            for b in range(B):
+                cache[b].copy_(torch.randn((ctx, CL + RP), device="cuda", generator=gen))
+        stream.synchronize()
+        qn, qr = bf16((B, H, NOPE)), bf16((B, H, RP))
+        hid = bf16((B, DM))
+        lens = dev.upload(np.full(B, ctx, np.int32), tb.I32)
+        q_full, o_lat, o = dev.alloc(B * H * (CL + RP), tb.BF16), dev.alloc(B * H * CL, tb.BF16), dev.alloc(B * H * VD, tb.F32)
+        lo = dev.alloc(B * DM, tb.F32)
+        cb = tb.Buffer(dev, cache.data_ptr(), cache.numel(), tb.BF16, owns=False)
+        hb = tb.Buffer(dev, hid.data_ptr(), hid.numel(), tb.BF16, owns=False)
+
+        def core():   # absorb W_UK into q, attend over the latent cache, un-absorb with W_UV
+            dev._check(L_.tq_mla_absorb_q(dev._ctx, C.c_void_p(wq.handle), C.c_void_p(qn.data_ptr()), C.c_void_p(qr.data_ptr()),
+                                          B, H, NOPE, C.c_void_p(q_full.ptr)))
+            dev._check(L_.tq_mla_decode(dev._ctx, C.c_void_p(q_full.ptr), C.c_void_p(cache.data_ptr()), C.c_void_p(lens.ptr), B, H,
+                                        CL, RP, ctx * (CL + RP), ctx, 1.0 / (NOPE + RP) ** 0.5, C.c_void_p(o_lat.ptr)))
+            dev._check(L_.tq_mla_unabsorb(dev._ctx, C.c_void_p(wu.handle), C.c_void_p(o_lat.ptr), B, H, VD, C.c_void_p(o.ptr), tb.F32))
+        ms = timed(core, 5)
+        ms_layer = timed(lambda: mlayer.decode(hb, cb, lens, B, ctx * (CL + RP), ctx, comm=comm, out=lo), 5)
+        byt = B * ctx * (CL + RP) * 2                       # the cache is replicated: every rank streams all of it
+        mla.append({"ctx": ctx, "batch": B, "heads_per_gpu": H, "us": ms * 1e3, "layer_us": ms_layer * 1e3, "cache_bytes": byt,
+                    "gbs_per_gpu": byt / ms / 1e6, "tflops": B * ctx * H * world * 2176.0 / ms / 1e9,
+                    "frac_of_hbm_peak": byt / ms / 1e6 / peak_gbs})
+        del cache
+        torch.cuda.empty_cache()
+    out["mla_dsv3_decode"] = mla
+    mlayer.destroy()
     return out
 
 

@@ -60,6 +60,24 @@ int ensure_splitk(tq_ctx* ctx, size_t bytes) {
   return TQ_OK;
 }
 
+int ensure_gemm_ws2(tq_ctx* ctx, size_t bytes) {
+  if (ctx->gemm_ws2_bytes >= bytes) return TQ_OK;
+  if (ctx->capturing)
+    return fail(ctx, TQ_EINVAL, "a workspace has to grow (%zu bytes) during graph capture: run the same calls once before tq_graph_begin", bytes);
+  if (ctx->gemm_ws2) {
+    TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    TQ_CUDA(ctx, cudaFree(ctx->gemm_ws2));
+    ctx->gemm_ws2 = nullptr;
+    ctx->gemm_ws2_bytes = 0;
+    ctx->ws_generation++;
+  }
+  size_t want = bytes < (8u << 20) ? (8u << 20) : bytes;
+  TQ_CUDA(ctx, cudaMalloc(&ctx->gemm_ws2, want));
+  ctx->gemm_ws2_bytes = want;
+  TQ_CUDA(ctx, cudaMemsetAsync(ctx->gemm_ws2, 0, want, ctx->stream));   // tags: nothing parked
+  return TQ_OK;
+}
+
 __global__ void convert_kernel(const void* src, int sdt, void* dst, int ddt, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -128,6 +146,7 @@ int tq_ctx_destroy(tq_ctx* ctx) {
   if (ctx->splitk) cudaFree(ctx->splitk);
   if (ctx->dev_err) cudaFree(ctx->dev_err);
   if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
+  if (ctx->gemm_ws2) cudaFree(ctx->gemm_ws2);
   if (ctx->hostx_ring) cudaFree(ctx->hostx_ring);
   if (ctx->hostx_tags) cudaFree(ctx->hostx_tags);
   if (ctx->host_err) cudaFreeHost(ctx->host_err);
@@ -150,7 +169,8 @@ int tq_sync(tq_ctx* ctx) {
   const int code = *ctx->host_err;
   if (code != 0) {
     cudaMemset(ctx->dev_err, 0, (1 + kTileCounters) * sizeof(int));   // a kernel that gave up may have left tile counters half counted
-    cudaMemset(ctx->gemv_ws, 0, (size_t)kGemvSets * kGemvMaxGrid * 2 * 128 * sizeof(unsigned long long));   // ... or parked partial sums
+    cudaMemset(ctx->gemv_ws, 0, (size_t)kGemvSets * kGemvMaxGrid * 2 * 128 * sizeof(unsigned long long));
+    if (ctx->gemm_ws2) cudaMemset(ctx->gemm_ws2, 0, ctx->gemm_ws2_bytes);   // ... or parked partial sums
     if (code == 6)   // DERR_POSITION
       return fail(ctx, TQ_EINVAL, "a sequence position outside the KV cache reached a kernel (the access was skipped): positions must stay below max_seq");
     return fail(ctx, TQ_ETIMEOUT, "a kernel gave up a bounded wait (device code %d)", code);

@@ -22,6 +22,8 @@ struct tq_ctx {
   int* dev_err = nullptr;        // device status word written by kernels that give up a bounded wait,
                                  // followed by kTileCounters zeroed tile counters (split-K meets of the tcgen05
                                  // GEMM and the MoE router) and kTileCounters more for the persistent GEMV
+  unsigned long long* gemm_ws2 = nullptr;  // the several-row persistent kernel's per-(slab, row block) parked sums (zero between launches)
+  size_t gemm_ws2_bytes = 0;
   unsigned long long* gemv_ws = nullptr;   // [kGemvSets][kGemvMaxGrid][2][128] tagged f32 words: the persistent GEMV's
                                  // partial row blocks, all zero whenever no GEMV is running;
                                  // consecutive launches rotate through the sets (at most three kernels ever have
@@ -121,6 +123,7 @@ int qlinear_fused(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, const Ql
 int launch_swiglu_interleaved(tq_ctx* ctx, const float* gu, size_t rows, size_t n, void* out, int out_dtype);
 
 int ensure_xprep(tq_ctx* ctx, size_t bytes);
+int ensure_gemm_ws2(tq_ctx* ctx, size_t bytes);
 int ensure_scratch(tq_ctx* ctx, size_t bytes);
 int ensure_splitk(tq_ctx* ctx, size_t bytes);
 

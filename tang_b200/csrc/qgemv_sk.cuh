@@ -67,6 +67,10 @@ struct QGemvParams {
   // to finish; null otherwise.
   const unsigned* x_tag;
   unsigned x_seq;
+  // the several-row kernel (qgemm_sk.cuh): K is cut into n_slabs slabs of skc chunks, cps CTAs per slab; ws2 holds the
+  // slabs' parked sums, [n_slabs][n_row_blocks][column tiles * 128] tagged words, all zero between launches
+  int skc, n_slabs, cps;
+  unsigned long long* ws2;
   unsigned long long* ws;   // [gridDim.x][2][128] (value bits | 1 << 32): partial sums of row blocks cut by a range
                             // boundary; the tag in the upper half says the value is there; all zero between launches
   int* err;

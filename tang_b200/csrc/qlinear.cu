@@ -11,6 +11,7 @@
 #include "internal.h"
 #include "qgemm_mma.cuh"
 #include "qgemv_sk.cuh"
+#include "qgemm_sk.cuh"
 
 namespace tq {
 
@@ -226,10 +227,137 @@ static cudaError_t launch_sk_kind(tq_ctx* ctx, const QGemvParams& p, unsigned gr
   return m1 ? launch_sk_kernel<KIND, true, 8, 2, 3>(ctx, p, grid, smem) : launch_sk_kernel<KIND, false, 8, 2, 3>(ctx, p, grid, smem);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent GEMM for 2..8 staged activation rows (qgemm_sk.cuh): K in slabs, so that a CTA holds
+// only a slab of the activation rows beside its weight ring.  Returns false when the shape does
+// not fit; the caller then uses another kernel.
+// ---------------------------------------------------------------------------------------------
+template <int KIND, int TPW, int NT>
+static cudaError_t launch_skw_kernel(tq_ctx* ctx, const QGemvParams& p, unsigned grid, size_t smem) {
+  auto kern = qgemm_sk_kernel<KIND, 8, TPW, NT, 2>;
+  static size_t attr_bytes[64] = {};   // per device
+  const int dev = ctx->device & 63;
+  if (smem > 48 * 1024 && attr_bytes[dev] < smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_bytes[dev] = smem;
+  }
+  return launch_k(ctx, kern, dim3(grid), dim3(32 * 10), smem, p);
+}
+
+template <int KIND>
+static cudaError_t launch_skw_kind(tq_ctx* ctx, const QGemvParams& p, unsigned grid, size_t smem, int tpw, int nt) {
+  if (nt == 1) return tpw == 2 ? launch_skw_kernel<KIND, 2, 1>(ctx, p, grid, smem) : launch_skw_kernel<KIND, 1, 1>(ctx, p, grid, smem);
+  return tpw == 2 ? launch_skw_kernel<KIND, 2, 2>(ctx, p, grid, smem) : launch_skw_kernel<KIND, 1, 2>(ctx, p, grid, smem);
+}
+
+static bool launch_qgemm_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
+                            void* y, int y_dtype, size_t ldy, const float* residual, int* status, const QlinearNorm* norm,
+                            bool swiglu, const unsigned* x_tag, unsigned x_seq) {
+  // (measured per 14336 x 4096 launch in a dependent chain: 12-15 us for 4-8 rows, but 26 us for 16 rows with their
+  // eight-tile stages, against about 20 us for the general kernel: more than eight rows stay there)
+  if (mx < 2 || mx > 8) return false;
+  if (w->cols != (size_t)w->n_kc * kTileK && norm) return false;
+  const int nt = (mx + 7) / 8;
+  const int kc_total = w->n_kc;
+  // slab width: the largest divisor of the chunk count whose slab of activation rows stays near 36 KB
+  int skc_max = 36864 / (mx * 256);
+  if (skc_max > 32) skc_max = 32;
+  int skc = 0;
+  for (int d = skc_max < kc_total ? skc_max : kc_total; d >= 1; --d)
+    if (kc_total % d == 0) {
+      skc = d;
+      break;
+    }
+  if (skc < 4 && skc != kc_total) return false;
+  const int n_slabs = kc_total / skc;
+  const long long units = (long long)w->n_rb * skc;
+  long long cps = 2LL * ctx->sm_count / n_slabs;
+  if (cps < 1) cps = 1;
+  if (cps > units) cps = units;
+  const long long grid = cps * n_slabs;
+  if (grid > kGemvMaxGrid || grid * 2 * nt > (long long)kGemvSets * kGemvMaxGrid * 2) return false;
+  const int tpw = skc >= 16 ? 2 : 1;
+  const size_t stage = (size_t)8 * tpw * qk_tile_bytes(w->kind);
+  const size_t fixed = skw_fixed_bytes(w->kind, 8, skc, mx, nt);
+  const size_t budget = 113 * 1024;
+  if (fixed + 3 * stage > budget) return false;
+  int stages = (int)((budget - fixed) / stage);
+  if (stages > kSkMaxStages) stages = kSkMaxStages;
+  const size_t smem = fixed + (size_t)stages * stage;
+  if (n_slabs > 1) {
+    *status = ensure_gemm_ws2(ctx, (size_t)n_slabs * w->n_rb * nt * 128 * sizeof(unsigned long long));
+    if (*status != TQ_OK) return true;
+  }
+  const int kx = kc_total * kTileK;
+  const int m_out = mx / combine;
+  // the kernel may read its activations at once when nothing that may still be running writes them
+  struct R { uintptr_t lo, hi; };
+  const R rx = norm ? R{(uintptr_t)norm->h, (uintptr_t)norm->h + ((size_t)(mx - 1) * kx + kx) * 4}
+                    : R{(uintptr_t)xs, (uintptr_t)xs + ((size_t)(mx - 1) * ldxs + kx) * 2};
+  const R ry = {(uintptr_t)y, (uintptr_t)y + ((size_t)(m_out - 1) * ldy + w->rows) * (y_dtype == TQ_BF16 ? 2 : 4)};
+  const R rr = {(uintptr_t)residual, residual ? (uintptr_t)residual + ((size_t)(m_out - 1) * ldy + w->rows) * 4 : (uintptr_t)residual};
+  auto hit = [](const R& a, const tq_ctx::Range& b) { return a.lo < b.hi && b.lo < a.hi; };
+  int mode = (ctx->owns_stream && ctx->pdl && !ctx->inflight_unknown && ctx->n_inflight + 3 <= 96 && !norm) ? 1 : 0;
+  for (int i = 0; mode && i < ctx->n_inflight; ++i)
+    if (ctx->inflight[i].written && hit(rx, ctx->inflight[i])) mode = 0;
+  QGemvParams p;
+  p.tiles = w->tiles;
+  p.row_scales = w->row_scales;
+  p.x = xs;
+  p.y = y;
+  p.residual = residual;
+  p.ldx = (long long)ldxs;
+  p.ldy = (long long)ldy;
+  p.n_units = units;
+  p.n_rows = (int)w->rows;
+  p.n_row_blocks = w->n_rb;
+  p.kc_total = kc_total;
+  p.kx = kx;
+  p.mx = mx;
+  p.m_out = m_out;
+  p.combine = combine;
+  p.y_bf16 = y_dtype == TQ_BF16;
+  p.stages = stages;
+  p.nh = norm ? norm->h : nullptr;
+  p.ndelta = norm ? norm->delta : nullptr;
+  p.norm_w = norm ? static_cast<const __nv_bfloat16*>(norm->gain_bf16) : nullptr;
+  p.nh_out = norm ? norm->h_out : nullptr;
+  p.ld_h = kx;
+  p.norm_eps = norm ? norm->eps : 0.f;
+  p.swiglu = swiglu ? 1 : 0;
+  p.x_tag = x_tag;
+  p.x_seq = x_seq;
+  p.x_early = mode;
+  p.skc = skc;
+  p.n_slabs = n_slabs;
+  p.cps = (int)cps;
+  p.ws = ctx->gemv_ws;
+  p.ws2 = ctx->gemm_ws2;
+  p.err = ctx->dev_err;
+  cudaError_t e;
+  switch (w->kind) {
+    case TQ_Q4_F32: e = launch_skw_kind<Q4_F32>(ctx, p, (unsigned)grid, smem, tpw, nt); break;
+    case TQ_Q4_F16: e = launch_skw_kind<Q4_F16>(ctx, p, (unsigned)grid, smem, tpw, nt); break;
+    case TQ_Q8_F32: e = launch_skw_kind<Q8_F32>(ctx, p, (unsigned)grid, smem, tpw, nt); break;
+    default: e = launch_skw_kind<I8_ROW>(ctx, p, (unsigned)grid, smem, tpw, nt); break;
+  }
+  *status = e == cudaSuccess ? TQ_OK : fail(ctx, TQ_ECUDA, "persistent GEMM launch failed: %s", cudaGetErrorString(e));
+  if (e == cudaSuccess && !norm) {   // (launch_k has just marked the stream's state unknown)
+    if (mode == 0) ctx->n_inflight = 0;
+    ctx->inflight_unknown = false;
+    ctx->inflight[ctx->n_inflight++] = {rx.lo, rx.hi, false};
+    ctx->inflight[ctx->n_inflight++] = {ry.lo, ry.hi, true};
+    if (residual) ctx->inflight[ctx->n_inflight++] = {rr.lo, rr.hi, false};
+  }
+  return true;
+}
+
 static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
                             void* y, int y_dtype, size_t ldy, const float* residual, int* status,
                             const QlinearNorm* norm = nullptr, bool swiglu = false, const unsigned* x_tag = nullptr,
                             unsigned x_seq = 0) {
+  if (mx >= 2 && launch_qgemm_sk(ctx, w, xs, ldxs, mx, combine, y, y_dtype, ldy, residual, status, norm, swiglu, x_tag, x_seq)) return true;
   if (mx > 8) return false;
   if (norm && (w->cols != (size_t)w->n_kc * kTileK)) return false;   // the fused norm wants whole 128-k chunks
   const bool m1 = mx == 1;

@@ -108,7 +108,10 @@ def test_qlinear_f32_activations_are_exact_inputs(dev, orc, kind):
         x = rng.standard_normal((m, cols)).astype(np.float32)
         want = orc.qmatmul(kind, sc, pay, rows, cols, x.astype(np.float64))
         y = dev.qlinear(dev.upload(x), w, m).to_vec().reshape(m, rows)
-        assert rel_err(y, want) < 2e-5, (kind, m)
+        # (the persistent kernels multiply 128 + n and take 136 * sum(x) out again through the accumulator: sums about
+        # a hundred times the result pass through f32, which leaves a few 1e-7 of the output's rms -- 1e-4 against the
+        # 1 % floor -- where the bias-subtracting kernel leaves 2e-5)
+        assert rel_err(y, want) < 1e-4, (kind, m)
 
 
 def test_residual_and_strides(dev, orc):
@@ -348,3 +351,33 @@ def test_host_matvec_async_queue(dev, orc):
         dev._check(dev._L.tq_q_matvec_host(dev._ctx, C.c_void_p(w.handle), C.c_void_p(xh.data_ptr()), C.c_void_p(want.data_ptr()), dt, 1))
         assert torch.equal(yh.view(torch.int16) if dt == tb.BF16 else yh, want.view(torch.int16) if dt == tb.BF16 else want)
         assert float(want.float().abs().max()) > 0
+
+
+@pytest.mark.parametrize("kind,rows,cols", [(1, 4112, 14336), (3, 1040, 4096), (0, 528, 2816), (2, 272, 4096), (1, 2048, 1408)])
+def test_several_rows_k_slabs(dev, orc, kind, rows, cols):
+    """2..16 activation rows take the persistent kernel that cuts K into slabs: row blocks cut by CTA ranges inside
+    a slab, sums across 2..14 slabs, a ragged last row block, both output types, the residual, and the same bits
+    from a second run (every sum has a fixed order)."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(rows + cols + kind)
+    sc, pay = make_weight(rng, kind, rows, cols)
+    w = _upload(dev, kind, sc, pay, rows, cols)
+    sample = rng.choice(rows, 160, replace=False)
+    sample[:3] = [0, rows - 1, rows - 17]
+    sub_sc, sub_pay = sc[sample], pay[sample]
+    for m in (2, 7, 8, 9, 16):
+        xbits, xf = bf16_round(rng.standard_normal((m, cols)).astype(np.float32))
+        want = orc.qmatmul(kind, sub_sc, sub_pay, len(sample), cols, xf.astype(np.float64))
+        xb = dev.upload(xbits, tb.BF16)
+        y32 = dev.qlinear(xb, w, m, tb.F32).to_vec().reshape(m, rows)
+        again = dev.qlinear(xb, w, m, tb.F32).to_vec().reshape(m, rows)
+        y16 = dev.qlinear(xb, w, m, tb.BF16).to_vec().reshape(m, rows)
+        dev.sync()
+        assert rel_err(y32[:, sample], want) < TOL_F32, (kind, rows, cols, m)
+        assert np.array_equal(y32, again)
+        assert np.array_equal(y16, bf16_round(y32)[0])
+        res = rng.standard_normal((m, rows)).astype(np.float32)
+        yr = dev.qlinear(xb, w, m, tb.F32, residual=dev.upload(res)).to_vec().reshape(m, rows)
+        dev.sync()
+        assert np.array_equal(yr, y32 + res)
