@@ -394,8 +394,8 @@ __global__ void moe_localize_kernel(const int* idx, int n, int lo, int n_local, 
 }
 
 __global__ void moe_combine_local_kernel(const float* yo, const int* slot, const int* idx_local, const float* w,
-                                         const float* shared, int shared_lo, int shared_hi, int top_k, int d, int n_local,
-                                         float* out) {
+                                         const float* shared, int n_shared, size_t shared_stride, int shared_lo, int shared_hi,
+                                         int top_k, int d, int n_local, float* out) {
   // the token's few (row, weight) pairs first, then wide independent loads over the model dimension
   __shared__ int rows[kMaxTopK];
   __shared__ float wts[kMaxTopK];
@@ -419,7 +419,16 @@ __global__ void moe_combine_local_kernel(const float* yo, const int* slot, const
       acc.w += wts[s] * v.w;
     }
     if (add_shared) {
-      const float4 v = *reinterpret_cast<const float4*>(shared + (size_t)(t - shared_lo) * d + c);
+      // the shared experts' outputs, one buffer each (so that each down projection may run on the tensor-core
+      // path, which takes no residual input), summed first in expert order
+      float4 v = *reinterpret_cast<const float4*>(shared + (size_t)(t - shared_lo) * d + c);
+      for (int e = 1; e < n_shared; ++e) {
+        const float4 u = *reinterpret_cast<const float4*>(shared + e * shared_stride + (size_t)(t - shared_lo) * d + c);
+        v.x = u.x + v.x;
+        v.y = u.y + v.y;
+        v.z = u.z + v.z;
+        v.w = u.w + v.w;
+      }
       acc.x += v.x;
       acc.y += v.y;
       acc.z += v.z;
@@ -452,7 +461,7 @@ int tq_moe_ffn(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_de
   };
   const size_t o_idx = take(n * 4), o_idl = take(n * 4), o_w = take(n * 4), o_slot = take(n * 4), o_cnt = take((nl + 1) * 4),
                o_off = take((nl + 1) * 4), o_cur = take((nl + 1) * 4), o_act_list = take((nl + 1) * 4), o_lg = take(T * c.n_experts * 8), o_xs = take(n * d * 2), o_gu = take(n * 2 * f * 4),
-               o_act = take(n * f * 2), o_yo = take(n * d * 4), o_sh = take(Ts * d * 4), o_shgu = take(Ts * 2 * f * 4),
+               o_act = take(n * f * 2), o_yo = take(n * d * 4), o_sh = take((size_t)(c.n_shared ? c.n_shared : 1) * Ts * d * 4), o_shgu = take(Ts * 2 * f * 4),
                o_shact = take(Ts * f * 2);
   if (int st = ensure_scratch(ctx, off)) return st;
   uint8_t* s = static_cast<uint8_t*>(ctx->scratch);
@@ -512,10 +521,10 @@ int tq_moe_ffn(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_de
   for (size_t i = 0; i < m->sh_gate_up.size() && Ts > 0; ++i) {
     TQ_STEP(tq_qlinear(ctx, m->sh_gate_up[i], h + sh_lo * d, TQ_BF16, d, Ts, shgu, TQ_F32, 2 * f, nullptr));
     TQ_STEP(tq_swiglu(ctx, shgu, shgu + f, TQ_F32, 2 * f, Ts, f, shact, TQ_BF16));
-    TQ_STEP(tq_qlinear(ctx, m->sh_down[i], shact, TQ_BF16, f, Ts, sh, TQ_F32, d, i ? sh : nullptr));
+    TQ_STEP(tq_qlinear(ctx, m->sh_down[i], shact, TQ_BF16, f, Ts, sh + i * Ts * d, TQ_F32, d, nullptr));
   }
-  moe_combine_local_kernel<<<dim3((unsigned)T, (unsigned)((d + 1023) / 1024)), 256, 0, ctx->stream>>>(yo, slot, idl, w, (c.n_shared && Ts) ? sh : nullptr, (int)sh_lo,
-                                                                 (int)sh_hi, (int)k, (int)d, nl, out_dev);
+  moe_combine_local_kernel<<<dim3((unsigned)T, (unsigned)((d + 1023) / 1024)), 256, 0, ctx->stream>>>(yo, slot, idl, w, (c.n_shared && Ts) ? sh : nullptr, (int)c.n_shared,
+                                                                 Ts * d, (int)sh_lo, (int)sh_hi, (int)k, (int)d, nl, out_dev);
   TQ_LAUNCHED();
   if (comm) TQ_STEP(tq_all_reduce_f32(ctx, comm, out_dev, T * d));
   if (idx_out_dev) TQ_CUDA(ctx, cudaMemcpyAsync(idx_out_dev, idx, n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
@@ -552,7 +561,7 @@ int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, floa
                o_smeta = take(R * 4), o_rmeta = take(R * 4), o_sx = take(R * d * 2), o_rx = take(R * d * 2), o_bucket = take(R * 4),
                o_slot = take(R * 4), o_cnt = take((nl + 2) * 4), o_off = take((nl + 2) * 4), o_cur = take((nl + 2) * 4),
                o_active = take((nl + 2) * 4), o_xs = take(R * d * 2), o_gu = take(R * 2 * f * 4), o_act = take(R * f * 2),
-               o_yo = take(R * d * 4), o_back = take(R * d * 4), o_ret = take(R * d * 4), o_sh = take(T * d * 4),
+               o_yo = take(R * d * 4), o_back = take(R * d * 4), o_ret = take(R * d * 4), o_sh = take((size_t)(c.n_shared ? c.n_shared : 1) * T * d * 4),
                o_shgu = take(T * 2 * f * 4), o_shact = take(T * f * 2);
   if (int st = ensure_scratch(ctx, off)) return st;
   uint8_t* s = static_cast<uint8_t*>(ctx->scratch);
@@ -621,11 +630,11 @@ int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, floa
   for (size_t i = 0; i < m->sh_gate_up.size(); ++i) {
     TQ_STEP(tq_qlinear(ctx, m->sh_gate_up[i], h, TQ_BF16, d, T, shgu, TQ_F32, 2 * f, nullptr));
     TQ_STEP(tq_swiglu(ctx, shgu, shgu + f, TQ_F32, 2 * f, T, f, shact, TQ_BF16));
-    TQ_STEP(tq_qlinear(ctx, m->sh_down[i], shact, TQ_BF16, f, T, sh, TQ_F32, d, i ? sh : nullptr));
+    TQ_STEP(tq_qlinear(ctx, m->sh_down[i], shact, TQ_BF16, f, T, sh + i * T * d, TQ_F32, d, nullptr));
   }
   TQ_CUDA(ctx, cudaMemsetAsync(zero, 0, n * 4, ctx->stream));
   moe_combine_local_kernel<<<dim3((unsigned)T, (unsigned)((d + 1023) / 1024)), 256, 0, ctx->stream>>>(
-      ret, place, zero, w, c.n_shared ? sh : nullptr, 0, (int)T, (int)k, (int)d, 1, out_dev);
+      ret, place, zero, w, c.n_shared ? sh : nullptr, (int)c.n_shared, T * d, 0, (int)T, (int)k, (int)d, 1, out_dev);
   TQ_LAUNCHED();
   if (idx_out_dev) TQ_CUDA(ctx, cudaMemcpyAsync(idx_out_dev, idx, n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
   if (weight_out_dev) TQ_CUDA(ctx, cudaMemcpyAsync(weight_out_dev, w, n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
