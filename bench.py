@@ -271,9 +271,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     xh.copy_(torch.randn((L, m, K_IN), generator=torch.Generator().manual_seed(7 + rank)).bfloat16())
     yh = torch.empty((L, m, N_OUT), dtype=torch.bfloat16).pin_memory()
 
+    x_ptrs = [C.c_void_p(xh[i].data_ptr()) for i in range(L)]      # (a caller has its pointers at hand)
+    y_ptrs = [C.c_void_p(yh[i].data_ptr()) for i in range(L)]
+
     def e2e_pass(call):
         for i in range(L):
-            dev._check(call(dev._ctx, handles[i], C.c_void_p(xh[i].data_ptr()), C.c_void_p(yh[i].data_ptr()), tb.BF16, m))
+            dev._check(call(dev._ctx, handles[i], x_ptrs[i], y_ptrs[i], tb.BF16, m))
 
     # Timed on the host clock, from the first call to the return of the last wait (the clock an end-to-end caller
     # sees); the CUDA-event time of the same region is kept beside it.
@@ -295,15 +298,38 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         barrier()
         e2e_times.append((t1 - t0) * 1e3)
         e2e_event_times.append(ev0.elapsed_time(ev1))
-    e2e_sync_ms, e2e_ms = e2e_times
+    e2e_sync_ms, e2e_async_ms = e2e_times
+    # The same step recorded once (tq_graph_begin .. tq_graph_end around the L calls) and replayed: every replay reads
+    # the pinned input vectors again and writes the pinned results; per step the host launches one graph and waits once.
+    yh_calls = yh.clone()                    # what the call-by-call loop above produced
+    dev.begin_capture()
+    e2e_pass(L_.tq_q_matvec_host_async)
+    e2e_graph = dev.end_capture()
+    yh.zero_()
+    e2e_graph.launch()
+    dev.sync()
+    e2e_graph_ok = bool(torch.equal(yh.view(torch.int16), yh_calls.view(torch.int16)))
+    barrier()
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_graph.launch()
+            dev.sync()
+        t1 = time.perf_counter()
+        ev1.record(stream)
+    barrier()
+    e2e_ms = (t1 - t0) * 1e3
+    e2e_event_times.append(ev0.elapsed_time(ev1))
+    e2e_graph.free()
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
 
-    t = torch.tensor([ms, e2e_ms, e2e_sync_ms], dtype=torch.float64, device="cuda")
+    t = torch.tensor([ms, e2e_ms, e2e_sync_ms, e2e_async_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         import torch.distributed as dist
 
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, e2e_sync_ms = float(t[0]), float(t[1]), float(t[2])
+    ms, e2e_ms, e2e_sync_ms, e2e_async_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
 
     host_w = None   # layer 0 on the host, for the CPU baseline leg
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -372,9 +398,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                          "avg_launch_us": ms_per_step * 1e3 / L},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": L * m * K_IN * 2,
                     "d2h_bytes_per_step": L * m * N_OUT * 2, "steps": e2e_steps,
-                    "call": "tq_q_matvec_host_async per matrix + one tq_sync per step (host vectors, one per matrix, weights resident)",
+                    "call": "tq_graph_launch of a recorded step (L x tq_q_matvec_host_async: pinned host vectors, one per matrix, read "
+                            "again by every replay; results written to pinned host vectors) + one tq_sync per step",
                     "clock": "host wall clock around the calls and their final wait",
-                    "value_cuda_events": world * L * bytes_launch / (e2e_event_times[1] / e2e_steps * 1e-3) / 1e12,
+                    "graph_result_equals_call_by_call": e2e_graph_ok,
+                    "value_cuda_events": world * L * bytes_launch / (e2e_event_times[2] / e2e_steps * 1e-3) / 1e12,
+                    "value_async_calls": world * L * bytes_launch / (e2e_async_ms / e2e_steps * 1e-3) / 1e12,
+                    "call_async_calls": "tq_q_matvec_host_async per matrix + one tq_sync per step, no graph",
                     "value_wait_per_call": world * L * bytes_launch / (e2e_sync_ms / e2e_steps * 1e-3) / 1e12,
                     "call_wait_per_call": "tq_q_matvec_host (q4_matvec: returns when the result is on the host)"},
             "cpu_baseline": cpu, "gpu_launches": int(gpu_launches), "clocks": clocks,

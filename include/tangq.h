@@ -136,7 +136,12 @@ TQ_API int tq_q_matvec_host(tq_ctx* ctx, const tq_qweight* w, const void* x_host
  * order, and ONE tq_sync after the last call makes every y_host valid (and reports a device-side failure).  Both
  * vectors must stay alive and untouched until that tq_sync; pageable vectors make the copies themselves block, so
  * pinned ones (cudaHostAlloc / cudaHostRegister) are what this form is for -- a pinned y_host is written by the
- * kernel directly.  The reference has no asynchronous form: this replaces a loop of quantize.rs:256 calls. */
+ * kernel directly, and pinned bf16 / f32 x_host of up to eight rows are read by a small staging kernel through their
+ * device alias instead of being copied.  The reference has no asynchronous form: this replaces a loop of
+ * quantize.rs:256 calls.
+ * With pinned vectors the call may be recorded between tq_graph_begin and tq_graph_end (after one eager call has set
+ * the staging ring up): every tq_graph_launch then reads the vectors' current contents and writes the results again,
+ * so a step of many matvecs costs the host one launch and one tq_sync. */
 TQ_API int tq_q_matvec_host_async(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m);
 
 /* Row-wise concatenation of weights already on the device (same kind and column count; every part

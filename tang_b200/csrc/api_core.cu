@@ -148,7 +148,7 @@ int tq_ctx_destroy(tq_ctx* ctx) {
   if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
   if (ctx->gemm_ws2) cudaFree(ctx->gemm_ws2);
   if (ctx->hostx_ring) cudaFree(ctx->hostx_ring);
-  if (ctx->hostx_tags) cudaFree(ctx->hostx_tags);
+  if (ctx->hostx_tags) cudaFree(ctx->hostx_tags);   // (the epoch word sits behind the tags)
   if (ctx->host_err) cudaFreeHost(ctx->host_err);
   if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;

@@ -20,6 +20,7 @@ int tq_graph_begin(tq_ctx* ctx) {
   TQ_REQUIRE(ctx, !ctx->capturing, "tq_graph_begin: a capture is already open");
   TQ_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
   ctx->capturing = true;
+  ctx->hostx_epoch_pending = true;
   ctx->launches_at_capture = ctx->launches;
   ctx->inflight_unknown = true;   // a graph starts after everything before it: its first kernel assumes nothing
   ctx->n_inflight = 0;

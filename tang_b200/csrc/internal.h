@@ -53,6 +53,8 @@ struct tq_ctx {
   uint8_t* hostx_ring = nullptr;     // [kHostXSlots][kHostXSlotBytes]
   unsigned* hostx_tags = nullptr;    // [kHostXSlots]
   unsigned hostx_seq = 0;
+  unsigned* hostx_epoch = nullptr;   // device word: replays of captured graphs that stage host vectors (bumped by the graph's first such call)
+  bool hostx_epoch_pending = false;  // a capture is open and has not bumped the word yet
   unsigned long long ws_generation = 0;        // bumped whenever a workspace is freed and reallocated: graphs recorded
                                                // before that hold the old addresses and refuse to launch
   unsigned long long launches = 0;             // kernels launched through this context

@@ -191,10 +191,11 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemm_sk_kernel(const QGem
         // activations staged by the kernel launched just before this one: ring first, then a bounded look at its tag
         while (w.left > 0 && issued < S) issue(issued++);
         uint32_t polls = 0;
+        const unsigned want = sk_x_tag_value(p.x_seq, p.x_epoch);
         for (;;) {
           unsigned v;
           asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.x_tag) : "memory");
-          if (v == p.x_seq) break;
+          if (v == want) break;
           if (++polls > kMaxPolls) {
             *failed = 1;
             atomicCAS(p.err, 0, (int)DERR_FULL_WAIT);

@@ -67,6 +67,9 @@ struct QGemvParams {
   // to finish; null otherwise.
   const unsigned* x_tag;
   unsigned x_seq;
+  // Inside a captured graph x_seq is frozen, so the tag also carries the replay count, which a one-thread kernel at
+  // the head of the graph advances in *x_epoch (null outside a capture): see sk_x_tag_value.
+  const unsigned* x_epoch;
   // the several-row kernel (qgemm_sk.cuh): K is cut into n_slabs slabs of skc chunks, cps CTAs per slab; ws2 holds the
   // slabs' parked sums, [n_slabs][n_row_blocks][column tiles * 128] tagged words, all zero between launches
   int skc, n_slabs, cps;
@@ -75,6 +78,13 @@ struct QGemvParams {
                             // boundary; the tag in the upper half says the value is there; all zero between launches
   int* err;
 };
+
+// The tag value that says "slot complete": the call's sequence number with the top bit set, or inside a captured
+// graph (epoch != null) the replay count over the low 16 bits of the frozen sequence number (top bit clear, never 0:
+// the first replay has count 1).
+__host__ __device__ inline unsigned sk_x_tag_value(unsigned seq, const unsigned* epoch) {
+  return epoch ? (((*epoch) & 0x7FFFu) << 16) | (seq & 0xFFFFu) : (seq | 0x80000000u);
+}
 
 constexpr int kSkMaxStages = 12;
 constexpr int kSkHeaderBytes = 320;
@@ -212,10 +222,11 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemv_sk_kernel(const QGem
         // activations staged by the kernel launched just before this one: ring first, then a bounded look at its tag
         while (w.left > 0 && issued < S) issue(issued++);
         uint32_t polls = 0;
+        const unsigned want = sk_x_tag_value(p.x_seq, p.x_epoch);
         for (;;) {
           unsigned v;
           asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.x_tag) : "memory");
-          if (v == p.x_seq) break;
+          if (v == want) break;
           if (++polls > kMaxPolls) {
             *failed = 1;
             atomicCAS(p.err, 0, (int)DERR_FULL_WAIT);

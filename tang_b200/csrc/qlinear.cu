@@ -253,7 +253,7 @@ static cudaError_t launch_skw_kind(tq_ctx* ctx, const QGemvParams& p, unsigned g
 
 static bool launch_qgemm_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
                             void* y, int y_dtype, size_t ldy, const float* residual, int* status, const QlinearNorm* norm,
-                            bool swiglu, const unsigned* x_tag, unsigned x_seq) {
+                            bool swiglu, const unsigned* x_tag, unsigned x_seq, const unsigned* x_epoch) {
   // (measured per 14336 x 4096 launch in a dependent chain: 12-15 us for 4-8 rows, but 26 us for 16 rows with their
   // eight-tile stages, against about 20 us for the general kernel: more than eight rows stay there)
   if (mx < 2 || mx > 8) return false;
@@ -328,6 +328,7 @@ static bool launch_qgemm_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   p.swiglu = swiglu ? 1 : 0;
   p.x_tag = x_tag;
   p.x_seq = x_seq;
+  p.x_epoch = x_epoch;
   p.x_early = mode;
   p.skc = skc;
   p.n_slabs = n_slabs;
@@ -356,8 +357,8 @@ static bool launch_qgemm_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
 static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
                             void* y, int y_dtype, size_t ldy, const float* residual, int* status,
                             const QlinearNorm* norm = nullptr, bool swiglu = false, const unsigned* x_tag = nullptr,
-                            unsigned x_seq = 0) {
-  if (mx >= 2 && launch_qgemm_sk(ctx, w, xs, ldxs, mx, combine, y, y_dtype, ldy, residual, status, norm, swiglu, x_tag, x_seq)) return true;
+                            unsigned x_seq = 0, const unsigned* x_epoch = nullptr) {
+  if (mx >= 2 && launch_qgemm_sk(ctx, w, xs, ldxs, mx, combine, y, y_dtype, ldy, residual, status, norm, swiglu, x_tag, x_seq, x_epoch)) return true;
   if (mx > 8) return false;
   if (norm && (w->cols != (size_t)w->n_kc * kTileK)) return false;   // the fused norm wants whole 128-k chunks
   const bool m1 = mx == 1;
@@ -437,6 +438,7 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   p.swiglu = swiglu ? 1 : 0;
   p.x_tag = x_tag;
   p.x_seq = x_seq;
+  p.x_epoch = x_epoch;
   p.x_early = mode;
   const unsigned set = ctx->gemv_seq++ % kGemvSets;
   p.ws = ctx->gemv_ws + (size_t)set * kGemvMaxGrid * 2 * 128;
@@ -880,7 +882,7 @@ int tq_qlinear(tq_ctx* ctx, const tq_qweight* w, const void* x_dev, int x_dtype,
 // 3r+2, as prep_x_kernel).  It waits for nothing until its last instruction, so it runs beside whatever is in flight;
 // the GEMV that consumes the slot looks at the tag word instead of waiting for this kernel to finish.
 __global__ void __launch_bounds__(256) stage_host_x_kernel(const void* x, int dtype, size_t m, size_t cols, size_t kx,
-                                                           __nv_bfloat16* slot, unsigned* tag, unsigned seq) {
+                                                           __nv_bfloat16* slot, unsigned* tag, unsigned seq, const unsigned* epoch) {
   pdl_launch_dependents();
   // Every load below crosses the bus: 16 bytes per load, all of a thread's loads issued before any is used.
   if (dtype == TQ_BF16 && cols == kx && ((uintptr_t)x & 15) == 0) {
@@ -938,7 +940,7 @@ __global__ void __launch_bounds__(256) stage_host_x_kernel(const void* x, int dt
   }
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(tag), "r"(seq) : "memory");
+  if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(tag), "r"(sk_x_tag_value(seq, epoch)) : "memory");
   pdl_wait();   // kernels of a stream still complete in launch order
 }
 
@@ -953,8 +955,12 @@ static void* pinned_alias(const void* host) {
 // one-CTA kernel pulls x over the bus into a ring slot, the persistent GEMV stores y straight into the pinned result,
 // and consecutive calls overlap on the GPU like any other run of independent GEMVs.  Returns false when the call
 // does not qualify (the caller then takes the copying path).
+// First staging call of a captured graph: one thread advances the replay count.  It lets nothing start early, so every
+// kernel recorded after it starts after it has finished.
+__global__ void hostx_epoch_kernel(unsigned* epoch) { *epoch = *epoch + 1; }
+
 static bool matvec_host_pinned(tq_ctx* ctx, const tq_qweight* w, const void* x_host, void* y_host, int dtype, size_t m, int* status) {
-  if (dtype == TQ_F64 || ctx->capturing || !ctx->owns_stream || !ctx->pdl) return false;
+  if (dtype == TQ_F64 || !ctx->owns_stream || !ctx->pdl) return false;
   const int combine = dtype == TQ_F32 ? 3 : 1;
   const size_t mx = m * combine, kx = (size_t)w->n_kc * kTileK;
   if (mx > 8 || mx * kx * 2 > kHostXSlotBytes) return false;
@@ -962,23 +968,37 @@ static bool matvec_host_pinned(tq_ctx* ctx, const tq_qweight* w, const void* x_h
   void* ya = xa ? pinned_alias(y_host) : nullptr;
   if (!xa || !ya) return false;
   if (!ctx->hostx_ring) {
+    if (ctx->capturing) return false;   // (no allocation inside a capture: one eager call first sets the ring up)
     if (cudaMalloc(&ctx->hostx_ring, (size_t)kHostXSlots * kHostXSlotBytes) != cudaSuccess ||
-        cudaMalloc(&ctx->hostx_tags, kHostXSlots * sizeof(unsigned)) != cudaSuccess ||
-        cudaMemsetAsync(ctx->hostx_tags, 0, kHostXSlots * sizeof(unsigned), ctx->stream) != cudaSuccess) {
+        cudaMalloc(&ctx->hostx_tags, (kHostXSlots + 1) * sizeof(unsigned)) != cudaSuccess ||
+        cudaMemsetAsync(ctx->hostx_tags, 0, (kHostXSlots + 1) * sizeof(unsigned), ctx->stream) != cudaSuccess) {
       cudaGetLastError();
       return false;
+    }
+    ctx->hostx_epoch = ctx->hostx_tags + kHostXSlots;
+  }
+  const unsigned* epoch = nullptr;
+  if (ctx->capturing) {
+    // A replay runs the same launches with the same sequence numbers: the tags carry the replay count as well.
+    epoch = ctx->hostx_epoch;
+    if (ctx->hostx_epoch_pending) {
+      if (launch_k(ctx, hostx_epoch_kernel, dim3(1), dim3(1), 0, ctx->hostx_epoch) != cudaSuccess) {
+        *status = fail(ctx, TQ_ECUDA, "tq_q_matvec_host: launch failed");
+        return true;
+      }
+      ctx->hostx_epoch_pending = false;
     }
   }
   const unsigned seq = ++ctx->hostx_seq;                 // never 0: a zeroed tag matches nothing
   const unsigned slot = seq % kHostXSlots;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ctx->hostx_ring + (size_t)slot * kHostXSlotBytes);
   if (launch_k_independent(ctx, stage_host_x_kernel, dim3(1), dim3(256), 0, (const void*)xa, dtype, m, w->cols, kx, xs, ctx->hostx_tags + slot,
-                           seq) != cudaSuccess) {
+                           seq, epoch) != cudaSuccess) {
     *status = fail(ctx, TQ_ECUDA, "tq_q_matvec_host: staging kernel launch failed");
     return true;
   }
   if (!launch_qgemv_sk(ctx, w, xs, kx, (int)mx, combine, ya, dtype == TQ_BF16 ? TQ_BF16 : TQ_F32, w->rows, nullptr, status, nullptr, false,
-                       ctx->hostx_tags + slot, seq))
+                       ctx->hostx_tags + slot, seq, epoch))
     return false;   // (the staged slot is simply not used)
   return true;
 }

@@ -381,3 +381,39 @@ def test_several_rows_k_slabs(dev, orc, kind, rows, cols):
         yr = dev.qlinear(xb, w, m, tb.F32, residual=dev.upload(res)).to_vec().reshape(m, rows)
         dev.sync()
         assert np.array_equal(yr, y32 + res)
+
+
+def test_host_matvecs_in_a_replayed_graph(dev, orc):
+    """Host-vector calls captured in a graph: every replay reads the pinned vectors again (the host rewrites them between
+    replays) and lands the results in the pinned result vectors; eager calls in between do not disturb the graph's tags."""
+    import ctypes as C
+
+    import torch
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(33)
+    cols = 1024
+    jobs = []
+    for rows, dt, tdt in ((256, tb.BF16, torch.bfloat16), (512, tb.F32, torch.float32), (384, tb.BF16, torch.bfloat16)):
+        sc, pay = make_weight(rng, 1, rows, cols)
+        xh = torch.zeros(cols, dtype=tdt).pin_memory()
+        yh = torch.zeros(rows, dtype=tdt).pin_memory()
+        jobs.append((_upload(dev, 1, sc, pay, rows, cols), dt, xh, yh))
+    dev.q_matvec_host_async(jobs[0][0], jobs[0][2].data_ptr(), jobs[0][3].data_ptr(), jobs[0][1], 1)   # sets the staging ring up
+    dev.sync()
+    dev.begin_capture()
+    for w, dt, xh, yh in jobs:
+        dev.q_matvec_host_async(w, xh.data_ptr(), yh.data_ptr(), dt, 1)
+    g = dev.end_capture()
+    for rep in range(4):
+        for w, dt, xh, yh in jobs:
+            xh.copy_(torch.from_numpy(rng.standard_normal(cols).astype(np.float32)).to(xh.dtype))
+            yh.zero_()
+        g.launch()
+        dev.sync()
+        for w, dt, xh, yh in jobs:
+            want = torch.zeros_like(yh).pin_memory()
+            dev._check(dev._L.tq_q_matvec_host(dev._ctx, C.c_void_p(w.handle), C.c_void_p(xh.data_ptr()), C.c_void_p(want.data_ptr()), dt, 1))
+            assert torch.equal(yh.view(torch.int16) if dt == tb.BF16 else yh, want.view(torch.int16) if dt == tb.BF16 else want), rep
+            assert float(want.float().abs().max()) > 0
+    g.free()
