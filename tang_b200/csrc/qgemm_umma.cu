@@ -124,8 +124,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
   } else if (warp == 1 || warp == 3) {
     // ------------------------------------------------------------------ MMA issuers
     // Two of them: issuing one step's MMAs from a single thread (~55 cycles each, plus the waits and the
-    // commit) is what bounds the step time, so warp 1 takes the even steps into accumulator 0 and warp 3
-    // the odd steps into accumulator 1; the epilogue adds the two (a fixed order: reproducible).  With an
+    // commit) is what bounds the step time, so warp 1 takes the even steps into the even accumulators and warp 3
+    // the odd steps into the odd ones; the epilogue adds them all (a fixed order: reproducible).  With an
     // even ring depth each issuer only ever returns to slots it consumed itself.
     // The whole warp runs the loop (warp-uniform control flow keeps the descriptors in uniform
     // registers); one elected lane issues.  The barriers of the NEXT step are looked at before this
@@ -136,7 +136,11 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     const uint32_t stage_u = (uint32_t)(stage_bytes >> 4), b_off_u = (uint32_t)((TERMS * kUmmaRows * 128) >> 4);
     bool ok = true;
     const int odd = warp == 3;
-    const uint32_t acc = tmem_d + (uint32_t)(odd * p.acc_stride);
+    // Each issuer rotates over n_acc / 2 accumulators: the tensor core truncates every f32 addition, an error that
+    // grows with the number of additions one accumulator sees, so as many short sums as tensor memory holds
+    // (512 columns) are kept and the epilogue adds them, in accumulator order.
+    const int rot_mask = (p.n_acc >> 1) - 1;
+    int j = 0;                                  // this issuer's step count
     int s = odd;
     uint32_t ph = 0;
     uint32_t tok_x = mbar_test(&x_full[s], 0), tok_a = mbar_test(&a_full[s], 0);
@@ -152,11 +156,14 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         s -= S;
         ph ^= 1u;
       }
+      const uint32_t acc = tmem_d + (uint32_t)((odd + 2 * (j & rot_mask)) * p.acc_stride);
+      const uint32_t fresh = j <= rot_mask ? 0u : 1u;   // the accumulator's first step overwrites it
+      ++j;
       if (leader) {
 #pragma unroll
         for (int k16 = 0; k16 < kUmmaK / 16; ++k16) {
           const uint64_t bd = ad + b_off_u + 2 * k16;
-          umma_f16(acc, ad + 2 * k16, bd, idesc, (kb > 1) | (k16 != 0));
+          umma_f16(acc, ad + 2 * k16, bd, idesc, fresh | (k16 != 0));
           if (TERMS == 2) umma_f16(acc, ad + (kUmmaRows * 128 >> 4) + 2 * k16, bd, idesc, 1u);
         }
       }
@@ -286,9 +293,12 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       for (int c0 = 16 * ((warp - kUmmaFirstDqWarp) >> 2); c0 < p.ntok; c0 += 16 * (kUmmaDqWarps / 4)) {
         float v[16], v1[16];
         tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)c0, v);
-        tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)(p.acc_stride + c0), v1);
+        const int used = min(p.n_acc, n_kb);              // step kb < n_acc is the first to touch accumulator kb
+        for (int a = 1; a < used; ++a) {
+          tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)(a * p.acc_stride + c0), v1);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] += v1[i];
+          for (int i = 0; i < 16; ++i) v[i] += v1[i];
+        }
         if constexpr (KIND == I8_ROW) {
           if (p.splits == 1) {   // (with K split, the scale multiplies the sum of the partials instead)
             const float rs = row_scales[n];
@@ -418,7 +428,8 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   splits = (w->n_kc + kc_per_split - 1) / kc_per_split;
   int acc_stride = 32;
   while (acc_stride < ntok) acc_stride <<= 1;
-  const int tmem_cols = 2 * acc_stride;
+  const int n_acc = 512 / acc_stride > 16 ? 16 : 512 / acc_stride;   // 16 accumulators up to 32 tokens, 8 at 64, 4 at 128, 2 at 256
+  const int tmem_cols = n_acc * acc_stride;
   // Four A/B stages are what the dequant groups need; everything else goes to the packed-tile ring, because
   // the bytes in flight from HBM (ring slots not being read) are what hides its latency.  A ring slot holds
   // KT = 4 k-tiles of the eight row blocks (eight 4.6 KB copies) when three such slots fit, else KT = 2.
@@ -456,6 +467,7 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.ntok = ntok;
   p.tmem_cols = tmem_cols;
   p.acc_stride = acc_stride;
+  p.n_acc = n_acc;
   p.y_bf16 = y_dtype == TQ_BF16;
   p.err = ctx->dev_err;
   p.splits = splits;

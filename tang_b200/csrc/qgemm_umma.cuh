@@ -48,8 +48,9 @@ struct UmmaParams {
   int n_rows;             // output features (multiple of 128)
   int kc_total;           // K / 128
   int ntok;               // tokens per CTA tile = UMMA N (multiple of 16, <= 256)
-  int tmem_cols;          // allocation: two accumulators, power of two
-  int acc_stride;         // columns between the accumulators of the even and the odd steps
+  int tmem_cols;          // allocation: n_acc accumulators, power of two
+  int acc_stride;         // columns between accumulators
+  int n_acc;              // accumulators (2, 4, 8 or 16): step kb adds into number (kb & 1) + 2 * ((kb >> 1) % (n_acc / 2))
   int stages;             // A/B ring depth
   int raw_stages;         // packed-tile ring depth (slots of kt tiles of 128 k): what keeps the HBM stream in flight
   int kt;                 // k-tiles per ring slot (2 or 4)

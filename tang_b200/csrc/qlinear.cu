@@ -247,8 +247,8 @@ static cudaError_t launch_skw_kernel(tq_ctx* ctx, const QGemvParams& p, unsigned
 
 template <int KIND>
 static cudaError_t launch_skw_kind(tq_ctx* ctx, const QGemvParams& p, unsigned grid, size_t smem, int tpw, int nt) {
-  if (nt == 1) return tpw == 2 ? launch_skw_kernel<KIND, 2, 1>(ctx, p, grid, smem) : launch_skw_kernel<KIND, 1, 1>(ctx, p, grid, smem);
-  return tpw == 2 ? launch_skw_kernel<KIND, 2, 2>(ctx, p, grid, smem) : launch_skw_kernel<KIND, 1, 2>(ctx, p, grid, smem);
+  (void)nt;   // one column tile of eight rows: the launcher takes up to eight rows
+  return tpw == 2 ? launch_skw_kernel<KIND, 2, 1>(ctx, p, grid, smem) : launch_skw_kernel<KIND, 1, 1>(ctx, p, grid, smem);
 }
 
 static bool launch_qgemm_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,

@@ -204,10 +204,11 @@ def test_config1_int4_full_size(dev, orc, m):
     # the oracle on every row for m <= 8, on a seeded sample of token rows beyond that
     sel = np.arange(m) if m <= 8 else np.sort(rng.choice(m, 8, replace=False))
     want = orc.qmatmul(1, sc, pay, rows, cols, xf[sel].astype(np.float64), threads=0)
-    # From 24 rows on the call runs on the tensor-memory GEMM: exact products (hi + lo terms), but 8192
-    # accumulation steps per output in the tensor core's f32 adder, whose error (2.6e-5 of the output rms)
-    # is measured against max(|ref|, 5 % rms) instead of the 1 % used for the register-accumulated path.
-    assert rel_err(y[sel], want, floor_frac=0.01 if m < 24 else 0.05) < TOL_F32
+    # From 24 rows on the call runs on the tensor-memory GEMM: exact products (hi + lo terms) added by the tensor
+    # core's truncating f32 adder.  The steps rotate over as many accumulators as tensor memory holds (16 up to 32
+    # tokens, 8 at 64, 4 at 128, 2 at 256), which keeps the error at 1e-4 .. 3e-4 against the same 1 % floor as the
+    # register-accumulated path (it was 2.6e-5 of the output rms, i.e. up to 2.6e-3 at this floor, with two).
+    assert rel_err(y[sel], want) < TOL_F32
     # linearity (size-independent property): W(a+b) = Wa + Wb for bf16-exact a, b, a+b
     a = np.round(rng.standard_normal((m, cols)) * 4) / 4
     b = np.round(rng.standard_normal((m, cols)) * 4) / 4
@@ -242,7 +243,9 @@ def test_tensor_memory_gemm(dev, orc, kind, rows, cols, m):
     want = orc.qmatmul(kind, sc, pay, rows, cols, xf[sel].astype(np.float64), threads=0)
     y = dev.qlinear(xb, w, m, tb.F32).to_vec().reshape(m, rows)
     dev.sync()
-    assert rel_err(y[sel], want, floor_frac=0.05) < TOL_F32
+    # f16 scales split exactly into the hi + lo pair; an f32 scale keeps 16 of its 24 bits there (2^-17 per product,
+    # 1e-5 of the output rms after the sum), which is measured against the 5 % floor
+    assert rel_err(y[sel], want, floor_frac=0.05 if kind == 0 else 0.01) < TOL_F32
     yb = dev.qlinear(xb, w, m, tb.BF16).to_vec().reshape(m, rows)
     dev.sync()
     yb = (yb.astype(np.uint32) << 16).view(np.float32)
@@ -417,3 +420,22 @@ def test_host_matvecs_in_a_replayed_graph(dev, orc):
             assert torch.equal(yh.view(torch.int16) if dt == tb.BF16 else yh, want.view(torch.int16) if dt == tb.BF16 else want), rep
             assert float(want.float().abs().max()) > 0
     g.free()
+
+
+@pytest.mark.parametrize("m", [64, 256])
+def test_tensor_memory_gemm_long_k(dev, orc, m):
+    """K = 14336 (the down projection): 224 steps of 64 k.  With 64-token tiles eight accumulators share them; a
+    256-token tile leaves room for two, whose 112 steps each bring the error to about 1e-3 at the 1 % floor (measured
+    9e-4 at 512 rows, 1.1e-3 at 2048), so that case is held to 2e-3 here and named in the design notes."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(1400 + m)
+    rows, cols = 1024, 14336
+    sc, pay = make_weight(rng, 1, rows, cols)
+    w = _upload(dev, 1, sc, pay, rows, cols)
+    xbits, xf = bf16_round(rng.standard_normal((m, cols)).astype(np.float32))
+    sel = np.sort(rng.choice(m, 8, replace=False))
+    want = orc.qmatmul(1, sc, pay, rows, cols, xf[sel].astype(np.float64), threads=0)
+    y = dev.qlinear(dev.upload(xbits, tb.BF16), w, m, tb.F32).to_vec().reshape(m, rows)
+    dev.sync()
+    assert rel_err(y[sel], want) < (TOL_F32 if m <= 128 else 2e-3)
