@@ -822,7 +822,20 @@ def run_sharded_extras(dev, tb, torch, stream, peak_gbs, comm, rank, world, barr
             ol = dev.alloc(tl * d, tb.F32)
             ms2 = timed(lambda: layer.forward_dispatch(hl, tl, comm=comm, out=ol), reps)
             row["dispatch"] = {"us": ms2 * 1e3, "tokens_per_rank": tl, "tflops": 2.0 * T * (k + nsh) * 3 * ffn * d / ms2 / 1e9,
-                               "form": "tokens over the ranks, all-to-all dispatch and combine"}
+                               "form": "tokens over the ranks, all-to-all dispatch and combine, peer blocks padded to the worst case "
+                                       "(fixed size: replayed from a graph)"}
+            if tl * k >= 256:
+                # outside a graph the call exchanges the row counts first and sends true sizes (one host round trip inside)
+                barrier()
+                ms3 = _time_ms(torch, stream, dev, lambda: layer.forward_dispatch(hl, tl, comm=comm, out=ol), reps)
+                if world > 1:
+                    import torch.distributed as dist
+
+                    t3 = torch.tensor([ms3], dtype=torch.float64, device="cuda")
+                    dist.all_reduce(t3, op=dist.ReduceOp.MAX)
+                    ms3 = float(t3[0])
+                row["dispatch_counts_first"] = {"us": ms3 * 1e3, "tflops": 2.0 * T * (k + nsh) * 3 * ffn * d / ms3 / 1e9,
+                                                "form": "the same call made eagerly: counts exchanged first, rows sent with their true sizes"}
         moe.append(row)
     out["moe_dsv2_lite_layer"] = moe
     layer.destroy()

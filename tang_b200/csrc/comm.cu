@@ -433,3 +433,25 @@ int tq_all_to_all(tq_ctx* ctx, tq_comm* comm, const void* send_dev, void* recv_d
 }
 
 }  // extern "C"
+
+namespace tq {
+// All-to-all with a different amount per peer (sizes known on the host): rank p's send_bytes[p'] bytes at
+// send_off[p'] go to rank p', which receives them at its recv_off[p].  One grouped NCCL call.
+int all_to_all_v(tq_ctx* ctx, tq_comm* comm, const void* send_dev, const size_t* send_off, const size_t* send_bytes, void* recv_dev,
+                 const size_t* recv_off, const size_t* recv_bytes) {
+  if (int st = bind(ctx)) return st;
+  ctx->inflight_unknown = true;
+  ctx->n_inflight = 0;
+  TQ_REQUIRE(ctx, comm && comm->world > 1 && comm->comm != nullptr, "all_to_all_v: needs a live communicator of several ranks");
+  TQ_NCCL(ctx, api().GroupStart());
+  for (int peer = 0; peer < comm->world; ++peer) {
+    if (send_bytes[peer])
+      TQ_NCCL(ctx, api().Send(static_cast<const char*>(send_dev) + send_off[peer], send_bytes[peer], ncclInt8, peer, comm->comm, ctx->stream));
+    if (recv_bytes[peer])
+      TQ_NCCL(ctx, api().Recv(static_cast<char*>(recv_dev) + recv_off[peer], recv_bytes[peer], ncclInt8, peer, comm->comm, ctx->stream));
+  }
+  TQ_NCCL(ctx, api().GroupEnd());
+  return TQ_OK;
+}
+}  // namespace tq
+

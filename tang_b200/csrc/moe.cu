@@ -29,6 +29,8 @@ int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const v
 constexpr int kMaxExperts = 256;
 constexpr int kMaxTopK = 16;
 
+int all_to_all_v(tq_ctx* ctx, tq_comm* comm, const void* send_dev, const size_t* send_off, const size_t* send_bytes, void* recv_dev,
+                 const size_t* recv_off, const size_t* recv_bytes);
 int launch_qgemm_umma_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, size_t m_total,
                               const int* counts, const int* offsets, const int* active, int max_active, int max_rows,
                               int expected_rows, void* y, int y_dtype, size_t ldy);
@@ -257,7 +259,8 @@ __global__ void moe_combine_kernel(const float* yo, const int* slot, const float
 // expert id, -1 marks padding.  Which pair gets which place within a block is not fixed (atomic counter),
 // but every row is processed on its own and its result comes back to the same place, so outputs do not
 // depend on it.
-__global__ void moe_dispatch_plan_kernel(const int* idx, int n, int n_local, int world, int cap, int* place, int* send_meta) {
+__global__ void moe_dispatch_plan_kernel(const int* idx, int n, int n_local, int world, int cap, int* place, int* send_meta,
+                                         int* send_cnt) {
   __shared__ int cnt[64];
   for (int i = threadIdx.x; i < world; i += blockDim.x) cnt[i] = 0;
   for (int i = threadIdx.x; i < world * cap; i += blockDim.x) send_meta[i] = -1;
@@ -268,6 +271,8 @@ __global__ void moe_dispatch_plan_kernel(const int* idx, int n, int n_local, int
     place[i] = owner * cap + pos;
     send_meta[owner * cap + pos] = idx[i] - owner * n_local;
   }
+  __syncthreads();
+  for (int i = threadIdx.x; i < world; i += blockDim.x) send_cnt[i] = cnt[i];   // rows for every owner
 }
 
 __global__ void moe_dispatch_rows_kernel(const __nv_bfloat16* h, const int* place, int top_k, int d, __nv_bfloat16* send_x) {
@@ -311,6 +316,7 @@ struct tq_moe {
   const tq_qweight* w_down = nullptr;       // stacked [n_local * d_model, ffn]
   std::vector<const tq_qweight*> sh_gate_up, sh_down;
   int expert_lo = 0, n_local = 0;           // experts held by this rank
+  int* host_counts = nullptr;               // pinned [2][64]: rows per peer, sent and received (counts-first dispatch)
 };
 
 using namespace tq;
@@ -557,6 +563,7 @@ int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, floa
     off += up(bytes);
     return o;
   };
+  const size_t o_scnt = take(64 * 4), o_rcnt = take(64 * 4);
   const size_t o_idx = take(n * 4), o_w = take(n * 4), o_place = take(n * 4), o_zero = take(n * 4), o_lg = take(T * c.n_experts * 8),
                o_smeta = take(R * 4), o_rmeta = take(R * 4), o_sx = take(R * d * 2), o_rx = take(R * d * 2), o_bucket = take(R * 4),
                o_slot = take(R * 4), o_cnt = take((nl + 2) * 4), o_off = take((nl + 2) * 4), o_cur = take((nl + 2) * 4),
@@ -586,21 +593,56 @@ int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, floa
 
   // route this rank's tokens, plan the places, fill the send buffers
   TQ_STEP(launch_router(ctx, h, m->wg, T, d, c.n_experts, k, c.renormalize, idx, w, reinterpret_cast<double*>(s + o_lg)));
-  moe_dispatch_plan_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)n, nl, W, (int)cap, place, smeta);
+  int *scnt = reinterpret_cast<int*>(s + o_scnt), *rcnt = reinterpret_cast<int*>(s + o_rcnt);
+  moe_dispatch_plan_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)n, nl, W, (int)cap, place, smeta, scnt);
   TQ_LAUNCHED();
   moe_dispatch_rows_kernel<<<(unsigned)n, 128, 0, ctx->stream>>>(h, place, (int)k, (int)d, sx);
   TQ_LAUNCHED();
-  // dispatch: rows and their expert ids to the owners
-  TQ_STEP(tq_all_to_all(ctx, comm, sx, rx, cap * d * 2));
-  TQ_STEP(tq_all_to_all(ctx, comm, smeta, rmeta, cap * 4));
+  // Counts first, for batches large enough to pay for a host round trip (and outside a graph capture, which cannot
+  // wait for the host): the ranks tell one another how many rows follow, the host reads the counts, and rows, ids
+  // and results travel with their true sizes into one contiguous block per owner.  Otherwise every peer block has
+  // the worst-case `cap` rows (padding marked -1) and the exchange has a fixed size.
+  const bool exact = comm && W > 1 && !ctx->capturing && n >= 256;
+  size_t Rr = R;                             // rows on the owner's side
+  size_t s_off[64], s_len[64], r_off[64], r_len[64];
+  if (exact) {
+    if (!m->host_counts) TQ_CUDA(ctx, cudaHostAlloc(&m->host_counts, 2 * 64 * sizeof(int), cudaHostAllocDefault));
+    TQ_STEP(tq_all_to_all(ctx, comm, scnt, rcnt, 4));
+    TQ_CUDA(ctx, cudaMemcpyAsync(m->host_counts, scnt, W * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    TQ_CUDA(ctx, cudaMemcpyAsync(m->host_counts + 64, rcnt, W * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    Rr = 0;
+    for (int p = 0; p < W; ++p) {
+      TQ_REQUIRE(ctx, m->host_counts[p] >= 0 && (size_t)m->host_counts[p] <= cap && m->host_counts[64 + p] >= 0 &&
+                          (size_t)m->host_counts[64 + p] <= cap, "tq_moe_ffn_dispatch: a peer announced an impossible row count");
+      s_off[p] = (size_t)p * cap;            // rows: the send side keeps the place layout the combine reads
+      s_len[p] = (size_t)m->host_counts[p];
+      r_off[p] = Rr;
+      r_len[p] = (size_t)m->host_counts[64 + p];
+      Rr += r_len[p];
+    }
+    auto scaled = [&](const size_t* v, size_t mul, size_t* out) {
+      for (int p = 0; p < W; ++p) out[p] = v[p] * mul;
+    };
+    size_t so[64], sl[64], ro[64], rl[64];
+    scaled(s_off, d * 2, so); scaled(s_len, d * 2, sl); scaled(r_off, d * 2, ro); scaled(r_len, d * 2, rl);
+    TQ_STEP(all_to_all_v(ctx, comm, sx, so, sl, rx, ro, rl));
+    scaled(s_off, 4, so); scaled(s_len, 4, sl); scaled(r_off, 4, ro); scaled(r_len, 4, rl);
+    TQ_STEP(all_to_all_v(ctx, comm, smeta, so, sl, rmeta, ro, rl));
+  } else {
+    // dispatch: rows and their expert ids to the owners
+    TQ_STEP(tq_all_to_all(ctx, comm, sx, rx, cap * d * 2));
+    TQ_STEP(tq_all_to_all(ctx, comm, smeta, rmeta, cap * 4));
+  }
   // the owner's side: bucket by local expert, run the experts on what arrived
-  moe_recv_bucket_kernel<<<(unsigned)((R + 255) / 256), 256, 0, ctx->stream>>>(rmeta, (int)R, nl, bucket);
+  if (Rr > 0) {
+  moe_recv_bucket_kernel<<<(unsigned)((Rr + 255) / 256), 256, 0, ctx->stream>>>(rmeta, (int)Rr, nl, bucket);
   TQ_LAUNCHED();
-  moe_count_kernel<<<1, 1024, 0, ctx->stream>>>(bucket, (int)R, nl + 1, cnt, offs, cur, active, nl);
+  moe_count_kernel<<<1, 1024, 0, ctx->stream>>>(bucket, (int)Rr, nl + 1, cnt, offs, cur, active, nl);
   TQ_LAUNCHED();
-  moe_slot_kernel<<<(unsigned)((R + 255) / 256), 256, 0, ctx->stream>>>(bucket, (int)R, cur, slot);
+  moe_slot_kernel<<<(unsigned)((Rr + 255) / 256), 256, 0, ctx->stream>>>(bucket, (int)Rr, cur, slot);
   TQ_LAUNCHED();
-  moe_gather_recv_kernel<<<(unsigned)R, 128, 0, ctx->stream>>>(rx, bucket, slot, nl, (int)d, xs);
+  moe_gather_recv_kernel<<<(unsigned)Rr, 128, 0, ctx->stream>>>(rx, bucket, slot, nl, (int)d, xs);
   TQ_LAUNCHED();
   size_t want = 2 * R / (size_t)(nl > 0 ? nl : 1) / (size_t)W + 1;   // expected rows per local expert, with slack
   int chunk = 8;
@@ -610,22 +652,34 @@ int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, floa
   const size_t expected = (size_t)W * n / (size_t)c.n_experts;      // rows per local expert when routing is even
   const bool tensor_path = expected >= 24 && umma_grouped_supported(m->w_gate_up, nl) && umma_grouped_supported(m->w_down, nl);
   if (tensor_path) {
-    TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_gate_up, nl, xs, d, R, cnt, offs, active, max_active, max_rows, (int)(expected * 3 / 2),
+    TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_gate_up, nl, xs, d, Rr, cnt, offs, active, max_active, max_rows, (int)(expected * 3 / 2),
                                       gu, TQ_F32, 2 * f));
   } else {
     TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, chunk, cnt, offs, max_rows, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
   }
-  TQ_STEP(tq_swiglu(ctx, gu, gu + f, TQ_F32, 2 * f, R, f, act, TQ_BF16));
+  TQ_STEP(tq_swiglu(ctx, gu, gu + f, TQ_F32, 2 * f, Rr, f, act, TQ_BF16));
   if (tensor_path) {
-    TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_down, nl, act, f, R, cnt, offs, active, max_active, max_rows, (int)(expected * 3 / 2), yo,
+    TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_down, nl, act, f, Rr, cnt, offs, active, max_active, max_rows, (int)(expected * 3 / 2), yo,
                                       TQ_F32, d));
   } else {
     TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, chunk, cnt, offs, max_rows, 0, 0, yo, TQ_F32, d, active, max_active));
   }
-  moe_scatter_back_kernel<<<(unsigned)R, 128, 0, ctx->stream>>>(yo, bucket, slot, nl, (int)d, back);
+  moe_scatter_back_kernel<<<(unsigned)Rr, 128, 0, ctx->stream>>>(yo, bucket, slot, nl, (int)d, back);
   TQ_LAUNCHED();
+  }
   // combine: results back to the places they came from
-  TQ_STEP(tq_all_to_all(ctx, comm, back, ret, cap * d * 4));
+  if (exact) {
+    size_t so[64], sl[64], ro[64], rl[64];
+    for (int p = 0; p < W; ++p) {
+      so[p] = r_off[p] * d * 4;              // what arrived from p goes back to p ...
+      sl[p] = r_len[p] * d * 4;
+      ro[p] = s_off[p] * d * 4;              // ... and what was sent to p comes back into p's block of places
+      rl[p] = s_len[p] * d * 4;
+    }
+    TQ_STEP(all_to_all_v(ctx, comm, back, so, sl, ret, ro, rl));
+  } else {
+    TQ_STEP(tq_all_to_all(ctx, comm, back, ret, cap * d * 4));
+  }
   // shared experts run where the token lives
   for (size_t i = 0; i < m->sh_gate_up.size(); ++i) {
     TQ_STEP(tq_qlinear(ctx, m->sh_gate_up[i], h, TQ_BF16, d, T, shgu, TQ_F32, 2 * f, nullptr));
@@ -644,6 +698,7 @@ int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, floa
 }
 
 int tq_moe_destroy(tq_moe* m) {
+  if (m && m->host_counts) cudaFreeHost(m->host_counts);
   delete m;
   return TQ_OK;
 }

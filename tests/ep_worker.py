@@ -1,6 +1,6 @@
 """Worker of the expert-parallel MoE tests with token dispatch: one process per rank, tokens sharded.
 
-    torchrun --nproc-per-node N tests/ep_worker.py gpu     # NCCL, tq_moe_ffn_dispatch on N GPUs
+    torchrun --nproc-per-node N tests/ep_worker.py gpu     # NCCL, tq_moe_ffn_dispatch on N GPUs (gpu_big: counts-first exchange)
     torchrun --nproc-per-node N tests/ep_worker.py cpu     # gloo, the same protocol in numpy + the oracle
 
 Protocol (both modes): every rank routes its own tokens; each (token, choice) row goes to the block of the
@@ -22,10 +22,12 @@ from moe_util import KIND, HostMoe  # noqa: E402
 from util import bf16_round, rel_err  # noqa: E402
 
 
-def make_case(world):
+def make_case(world, big=False):
     host = HostMoe(np.random.default_rng(21), d=256, ffn=256, n_experts=8, top_k=2, n_shared=1)
     rng = np.random.default_rng(22)
-    T_loc = [5, 3, 4, 6][:world]                 # ragged on purpose
+    # ragged on purpose; the large case has T * top_k >= 256 rows per rank, from where tq_moe_ffn_dispatch exchanges
+    # the row counts first and sends rows, ids and results with their true sizes
+    T_loc = ([150, 131, 140, 129] if big else [5, 3, 4, 6])[:world]
     hb, hf = bf16_round(rng.standard_normal((sum(T_loc), host.d)).astype(np.float32))
     return host, T_loc, hb, hf
 
@@ -91,7 +93,7 @@ def main():
 
     mode = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    host, T_loc, hb, hf = make_case(world)
+    host, T_loc, hb, hf = make_case(world, big=mode == "gpu_big")
     lo = sum(T_loc[:rank])
     h_bits, h_f32 = hb[lo:lo + T_loc[rank]], hf[lo:lo + T_loc[rank]]
     want, idx_o, _, _ = host.oracle(orc, h_f32)

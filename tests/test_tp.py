@@ -66,3 +66,15 @@ def test_ep2_token_dispatch_on_two_gpus():
         pytest.skip("needs two GPUs")
     r = _run("gpu", 2, 29634, "ep_worker.py")
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.gpu
+def test_ep2_counts_first_dispatch_on_two_gpus():
+    """A batch large enough for the counts-first exchange (row counts to the owners, then rows, ids and results with
+    their true sizes): same result as the unsharded oracle, and the padded rows of the ragged shard change nothing."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = _run("gpu_big", 2, 29636, "ep_worker.py")
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
