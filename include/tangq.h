@@ -381,7 +381,10 @@ TQ_API int tq_moe_ffn(tq_moe* moe, const void* h_bf16_dev, size_t n_tokens, floa
  * (all-to-all dispatch, padded to the worst case of n_tokens*top_k rows per peer so that the exchange has a
  * fixed size and can be captured in a graph), the owners run their experts on what arrived, and a second
  * all-to-all brings the f32 results back to be weighted and summed where the token lives; shared experts run
- * locally.  The communicator must have the layer's ep_size and ep_rank.  No reference counterpart. */
+ * locally.  The communicator must have the layer's ep_size and ep_rank.  No reference counterpart.
+ * From 256 (token, choice) rows per rank on, and when no graph capture is open (on ALL ranks alike), the ranks
+ * exchange their per-peer row counts first and the call waits once for the stream to read them; rows, expert ids
+ * and results then travel with their true sizes.  Results do not depend on which form ran. */
 TQ_API int tq_moe_ffn_dispatch(tq_moe* moe, const void* h_bf16_dev, size_t n_tokens, float* out_dev, tq_comm* comm_or_null,
                                int* idx_out_dev_or_null, float* weight_out_dev_or_null);
 
