@@ -130,6 +130,7 @@ int tq_ctx_create(int device, void* stream, tq_ctx** out) {
   const size_t ws_bytes = (size_t)kGemvSets * kGemvMaxGrid * 2 * 128 * sizeof(unsigned long long);
   if (cudaMalloc(&ctx->gemv_ws, ws_bytes) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaMemsetAsync(ctx->gemv_ws, 0, ws_bytes, ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
+  if (cudaMalloc(&ctx->skg_jobs, kSkgJobs * sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_err), sizeof(int), cudaHostAllocDefault) != cudaSuccess) return bail(TQ_ECUDA);
   *ctx->host_err = 0;
   if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
@@ -146,6 +147,7 @@ int tq_ctx_destroy(tq_ctx* ctx) {
   if (ctx->splitk) cudaFree(ctx->splitk);
   if (ctx->dev_err) cudaFree(ctx->dev_err);
   if (ctx->gemv_ws) cudaFree(ctx->gemv_ws);
+  if (ctx->skg_jobs) cudaFree(ctx->skg_jobs);
   if (ctx->gemm_ws2) cudaFree(ctx->gemm_ws2);
   if (ctx->hostx_ring) cudaFree(ctx->hostx_ring);
   if (ctx->hostx_tags) cudaFree(ctx->hostx_tags);   // (the epoch word sits behind the tags)

@@ -12,6 +12,7 @@
 
 constexpr int kTileCounters = 1024;
 constexpr int kGemvSets = 6, kGemvMaxGrid = 512;
+constexpr int kSkgJobs = 4096;
 constexpr int kHostXSlots = 64;
 constexpr size_t kHostXSlotBytes = 64 * 1024;
 
@@ -22,6 +23,7 @@ struct tq_ctx {
   int* dev_err = nullptr;        // device status word written by kernels that give up a bounded wait,
                                  // followed by kTileCounters zeroed tile counters (split-K meets of the tcgen05
                                  // GEMM and the MoE router) and kTileCounters more for the persistent GEMV
+  int* skg_jobs = nullptr;                 // [kSkgJobs] job list of a grouped persistent launch (rebuilt by every such launch)
   unsigned long long* gemm_ws2 = nullptr;  // the several-row persistent kernel's per-(slab, row block) parked sums (zero between launches)
   size_t gemm_ws2_bytes = 0;
   unsigned long long* gemv_ws = nullptr;   // [kGemvSets][kGemvMaxGrid][2][128] tagged f32 words: the persistent GEMV's

@@ -26,7 +26,7 @@ namespace tq {
 int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, int mx,
                          const int* counts, const int* offsets, int max_rows, long long x_stride, long long y_stride,
                          void* y, int y_dtype, size_t ldy, const int* active = nullptr,
-                         int max_active = 0);
+                         int max_active = 0, size_t total_rows = 0);
 
 constexpr int kC = 512, kR = 64, kRow = kC + kR;         // latent, rope, cache row width
 constexpr int kMlaTile = 64;

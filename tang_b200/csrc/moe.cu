@@ -24,7 +24,7 @@ namespace tq {
 int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, int mx,
                          const int* counts, const int* offsets, int max_rows, long long x_stride, long long y_stride,
                          void* y, int y_dtype, size_t ldy, const int* active = nullptr,
-                         int max_active = 0);
+                         int max_active = 0, size_t total_rows = 0);
 
 constexpr int kMaxExperts = 256;
 constexpr int kMaxTopK = 16;
@@ -515,14 +515,14 @@ int tq_moe_ffn(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, float* out_de
     TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_gate_up, nl, xs, d, n, cnt, offs, active, max_active, (int)T, (int)(expected * 3 / 2),
                                       gu, TQ_F32, 2 * f));
   } else {
-    TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, cap, cnt, offs, (int)T, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
+    TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, cap, cnt, offs, (int)T, 0, 0, gu, TQ_F32, 2 * f, active, max_active, n));
   }
   TQ_STEP(tq_swiglu(ctx, gu, gu + f, TQ_F32, 2 * f, n, f, act, TQ_BF16));
   if (tensor_path) {
     TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_down, nl, act, f, n, cnt, offs, active, max_active, (int)T, (int)(expected * 3 / 2), yo,
                                       TQ_F32, d));
   } else {
-    TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, cap, cnt, offs, (int)T, 0, 0, yo, TQ_F32, d, active, max_active));
+    TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, cap, cnt, offs, (int)T, 0, 0, yo, TQ_F32, d, active, max_active, n));
   }
   for (size_t i = 0; i < m->sh_gate_up.size() && Ts > 0; ++i) {
     TQ_STEP(tq_qlinear(ctx, m->sh_gate_up[i], h + sh_lo * d, TQ_BF16, d, Ts, shgu, TQ_F32, 2 * f, nullptr));
@@ -655,14 +655,14 @@ int tq_moe_ffn_dispatch(tq_moe* m, const void* h_bf16_dev, size_t n_tokens, floa
     TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_gate_up, nl, xs, d, Rr, cnt, offs, active, max_active, max_rows, (int)(expected * 3 / 2),
                                       gu, TQ_F32, 2 * f));
   } else {
-    TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, chunk, cnt, offs, max_rows, 0, 0, gu, TQ_F32, 2 * f, active, max_active));
+    TQ_STEP(launch_qgemm_grouped(ctx, m->w_gate_up, nl, xs, d, chunk, cnt, offs, max_rows, 0, 0, gu, TQ_F32, 2 * f, active, max_active, Rr));
   }
   TQ_STEP(tq_swiglu(ctx, gu, gu + f, TQ_F32, 2 * f, Rr, f, act, TQ_BF16));
   if (tensor_path) {
     TQ_STEP(launch_qgemm_umma_grouped(ctx, m->w_down, nl, act, f, Rr, cnt, offs, active, max_active, max_rows, (int)(expected * 3 / 2), yo,
                                       TQ_F32, d));
   } else {
-    TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, chunk, cnt, offs, max_rows, 0, 0, yo, TQ_F32, d, active, max_active));
+    TQ_STEP(launch_qgemm_grouped(ctx, m->w_down, nl, act, f, chunk, cnt, offs, max_rows, 0, 0, yo, TQ_F32, d, active, max_active, Rr));
   }
   moe_scatter_back_kernel<<<(unsigned)Rr, 128, 0, ctx->stream>>>(yo, bucket, slot, nl, (int)d, back);
   TQ_LAUNCHED();

@@ -12,6 +12,7 @@
 #include "qgemm_mma.cuh"
 #include "qgemv_sk.cuh"
 #include "qgemm_sk.cuh"
+#include "qgemm_skg.cuh"
 
 namespace tq {
 
@@ -520,13 +521,115 @@ static int launch_qgemm(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* x
 }
 
 // Grouped launch entry for the other translation units (MoE experts, per-head MLA projections).
+// ---------------------------------------------------------------------------------------------
+// Grouped persistent kernel (qgemm_skg.cuh) for expert batches / per-head matrices with 8..17 k chunks.
+// Returns false when the shape does not fit; the caller then uses the general kernel.
+// ---------------------------------------------------------------------------------------------
+template <int KIND, int TPW>
+static cudaError_t launch_skg_kernel(tq_ctx* ctx, const QGroupParams& p, dim3 grid, size_t smem) {
+  auto kern = qgemm_skg_kernel<KIND, 8, TPW>;
+  static size_t attr_bytes[64] = {};   // per device
+  const int dev = ctx->device & 63;
+  if (smem > 48 * 1024 && attr_bytes[dev] < smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_bytes[dev] = smem;
+  }
+  return launch_k(ctx, kern, grid, dim3(32 * 10), smem, p);
+}
+
+static bool launch_qgemm_skg(tq_ctx* ctx, const tq_qweight* w, int n_groups, const __nv_bfloat16* x, size_t ldx, int mx, const int* counts,
+                             const int* offsets, int max_rows, long long x_stride, long long y_stride, void* y, int y_dtype, size_t ldy,
+                             const int* active, int max_active, size_t total_rows, int* status) {
+  const int kc = w->n_kc, n_rb = w->n_rb / n_groups;
+  if (kc < 8 || kc > 17 || n_rb < 1 || n_groups > 65535) return false;
+  const int rows_bound = counts ? max_rows : mx;
+  if (rows_bound < 1) return false;
+  int gz = (rows_bound + 7) / 8;
+  int gy = (active && max_active < n_groups) ? max_active : n_groups;
+  // With the row counts on the device, a one-thread kernel first lists the (group, row chunk) jobs that exist, so
+  // that the grid need not cover every chunk of every group (CTAs without a job cost a scheduling slot each): there
+  // are at most (groups with rows) + (rows / 8) of them.
+  bool listed = false;
+  if (counts && total_rows > 0) {
+    const long long bound = (long long)gy + (long long)(total_rows / 8);
+    if (bound < (long long)gy * gz && bound <= kSkgJobs && bound <= 65535) {
+      if (launch_k(ctx, skg_jobs_kernel, dim3(1), dim3(32), 0, counts, (active && max_active < n_groups) ? active : (const int*)nullptr, gy,
+                   ctx->skg_jobs, (int)bound) != cudaSuccess) {
+        *status = fail(ctx, TQ_ECUDA, "grouped persistent GEMM: job list launch failed");
+        return true;
+      }
+      listed = true;
+      gy = (int)bound;
+      gz = 1;
+    }
+  }
+  // CTAs per job: about two per SM over the jobs that are expected to have rows (mx is the caller's row chunk, about
+  // twice the expected rows of a group, when the counts live on the device)
+  const int est_chunks = listed ? 1 : counts ? (mx > 16 ? (mx / 2 + 7) / 8 : 1) : gz;
+  long long est_jobs = (long long)gy * est_chunks;
+  if (listed) est_jobs = est_jobs * 3 / 4 + 1;          // (the bound is loose by the groups that have no partial chunk)
+  long long cps = 2LL * ctx->sm_count / est_jobs;
+  const long long units = (long long)n_rb * kc;
+  if (cps > 32) cps = 32;
+  if (cps > units / 16) cps = units / 16;
+  if (cps < 1) cps = 1;
+  while (cps > 1 && cps * gy * gz > (long long)kGemvSets * kGemvMaxGrid * 2) cps >>= 1;   // one 128-word slot per CTA
+  if (cps * gy * gz > (long long)kGemvSets * kGemvMaxGrid * 2 || gz > 65535 || gy > 65535) return false;
+  const int tpw = kc >= 16 ? 2 : 1;
+  const size_t stage = (size_t)8 * tpw * qk_tile_bytes(w->kind);
+  const size_t fixed = (size_t)kSkwHeaderBytes + skw_red_bytes(8, 1) + (size_t)8 * skw_x_stride(kc) + skw_csum_bytes(w->kind, kc, 1);
+  const size_t budget = 113 * 1024;
+  if (fixed + 3 * stage > budget) return false;
+  int stages = (int)((budget - fixed) / stage);
+  if (stages > kSkMaxStages) stages = kSkMaxStages;
+  QGroupParams p;
+  p.tiles = w->tiles;
+  p.row_scales = w->row_scales;
+  p.x = x;
+  p.y = y;
+  p.ldx = (long long)ldx;
+  p.ldy = (long long)ldy;
+  p.n_rows = (int)(w->rows / n_groups);
+  p.n_row_blocks = n_rb;
+  p.kc_total = kc;
+  p.mx = mx;
+  p.y_bf16 = y_dtype == TQ_BF16;
+  p.stages = stages;
+  p.counts = counts;
+  p.offsets = offsets;
+  p.active = (active && max_active < n_groups) ? active : nullptr;
+  p.jobs = listed ? ctx->skg_jobs : nullptr;
+  p.x_stride = x_stride;
+  p.y_stride = y_stride;
+  p.ws = ctx->gemv_ws;
+  p.err = ctx->dev_err;
+  const size_t smem = fixed + (size_t)stages * stage;
+  const dim3 grid((unsigned)cps, (unsigned)gy, (unsigned)gz);
+  cudaError_t e;
+  switch (w->kind) {
+    case TQ_Q4_F32: e = tpw == 2 ? launch_skg_kernel<Q4_F32, 2>(ctx, p, grid, smem) : launch_skg_kernel<Q4_F32, 1>(ctx, p, grid, smem); break;
+    case TQ_Q4_F16: e = tpw == 2 ? launch_skg_kernel<Q4_F16, 2>(ctx, p, grid, smem) : launch_skg_kernel<Q4_F16, 1>(ctx, p, grid, smem); break;
+    case TQ_Q8_F32: e = tpw == 2 ? launch_skg_kernel<Q8_F32, 2>(ctx, p, grid, smem) : launch_skg_kernel<Q8_F32, 1>(ctx, p, grid, smem); break;
+    default: e = tpw == 2 ? launch_skg_kernel<I8_ROW, 2>(ctx, p, grid, smem) : launch_skg_kernel<I8_ROW, 1>(ctx, p, grid, smem); break;
+  }
+  *status = e == cudaSuccess ? TQ_OK : fail(ctx, TQ_ECUDA, "grouped persistent GEMM launch failed: %s", cudaGetErrorString(e));
+  return true;
+}
+
 int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const void* x_bf16, size_t ldx, int mx,
                          const int* counts, const int* offsets, int max_rows, long long x_stride, long long y_stride,
-                         void* y, int y_dtype, size_t ldy, const int* active, int max_active) {
+                         void* y, int y_dtype, size_t ldy, const int* active, int max_active, size_t total_rows) {
   TQ_REQUIRE(ctx, w && n_groups > 0 && w->rows % n_groups == 0 && (w->rows / n_groups) % kTileRows == 0,
              "grouped qlinear: rows per group must be a multiple of 16");
   TQ_REQUIRE(ctx, w->cols == (size_t)w->n_kc * kTileK && ldx % 8 == 0 && ((uintptr_t)x_bf16 & 15) == 0 && (x_stride % 8) == 0,
              "grouped qlinear: K must be a multiple of 128 and activation rows 16-byte aligned");
+  {
+    int st = TQ_OK;
+    if (launch_qgemm_skg(ctx, w, n_groups, static_cast<const __nv_bfloat16*>(x_bf16), ldx, mx, counts, offsets, max_rows, x_stride, y_stride, y,
+                         y_dtype, ldy, active, max_active, total_rows, &st))
+      return st;
+  }
   QgGroup g;
   g.n_groups = n_groups;
   g.counts = counts;
