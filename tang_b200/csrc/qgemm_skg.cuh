@@ -39,20 +39,40 @@ struct QGroupParams {
 };
 
 // The jobs of a grouped launch whose row counts live on the device: one entry per (group with rows, chunk of eight
-// of its rows), groups in list order, then -1s up to `bound`.  One small CTA.
-__global__ void skg_jobs_kernel(const int* counts, const int* active, int n_listed, int* jobs, int bound) {
+// of its rows), groups in list order, then -1s up to `bound`.  One CTA of 256 threads, a group per thread (more
+// groups: several rounds), positions from a prefix sum over the CTA.
+__global__ void __launch_bounds__(256) skg_jobs_kernel(const int* counts, const int* active, int n_listed, int* jobs, int bound) {
   pdl_wait();
   pdl_launch_dependents();
-  if (threadIdx.x == 0) {
-    int j = 0;
-    for (int a = 0; a < n_listed && j < bound; ++a) {
-      const int e = active ? active[a] : a;
-      if (e < 0) continue;
-      const int chunks = (counts[e] + 7) / 8;
-      for (int c = 0; c < chunks && j < bound; ++c) jobs[j++] = e | (c << 16);
+  __shared__ int warp_sums[8];
+  __shared__ int base_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) base_s = 0;
+  __syncthreads();
+  for (int a0 = 0; a0 < n_listed; a0 += 256) {
+    const int a = a0 + threadIdx.x;
+    int e = -1, chunks = 0;
+    if (a < n_listed) {
+      e = active ? active[a] : a;
+      if (e >= 0) chunks = (counts[e] + 7) / 8;
     }
-    for (; j < bound; ++j) jobs[j] = -1;
+    int incl = chunks;                        // inclusive prefix sum over the warp, then over the warps
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    int before = base_s;
+    for (int q = 0; q < warp; ++q) before += warp_sums[q];
+    int pos = before + incl - chunks;
+    for (int c = 0; c < chunks && pos < bound; ++c, ++pos) jobs[pos] = e | (c << 16);
+    __syncthreads();
+    if (threadIdx.x == 255) base_s = before + incl;
+    __syncthreads();
   }
+  for (int i = base_s + threadIdx.x; i < bound; i += 256) jobs[i] = -1;
 }
 
 template <int KIND, int W, int TPW>

@@ -554,7 +554,7 @@ static bool launch_qgemm_skg(tq_ctx* ctx, const tq_qweight* w, int n_groups, con
   if (counts && total_rows > 0) {
     const long long bound = (long long)gy + (long long)(total_rows / 8);
     if (bound < (long long)gy * gz && bound <= kSkgJobs && bound <= 65535) {
-      if (launch_k(ctx, skg_jobs_kernel, dim3(1), dim3(32), 0, counts, (active && max_active < n_groups) ? active : (const int*)nullptr, gy,
+      if (launch_k(ctx, skg_jobs_kernel, dim3(1), dim3(256), 0, counts, (active && max_active < n_groups) ? active : (const int*)nullptr, gy,
                    ctx->skg_jobs, (int)bound) != cudaSuccess) {
         *status = fail(ctx, TQ_ECUDA, "grouped persistent GEMM: job list launch failed");
         return true;
@@ -568,8 +568,9 @@ static bool launch_qgemm_skg(tq_ctx* ctx, const tq_qweight* w, int n_groups, con
   // twice the expected rows of a group, when the counts live on the device)
   const int est_chunks = listed ? 1 : counts ? (mx > 16 ? (mx / 2 + 7) / 8 : 1) : gz;
   long long est_jobs = (long long)gy * est_chunks;
-  if (listed) est_jobs = est_jobs * 3 / 4 + 1;          // (the bound is loose by the groups that have no partial chunk)
-  long long cps = 2LL * ctx->sm_count / est_jobs;
+  if (listed) est_jobs = (long long)((active && max_active < n_groups) ? max_active : n_groups) + (long long)(total_rows / 32);   // (the bound is loose)
+  if (est_jobs < 1) est_jobs = 1;
+  long long cps = (2LL * ctx->sm_count + est_jobs / 2) / est_jobs;
   const long long units = (long long)n_rb * kc;
   if (cps > 32) cps = 32;
   if (cps > units / 16) cps = units / 16;
