@@ -570,7 +570,9 @@ static bool launch_qgemm_skg(tq_ctx* ctx, const tq_qweight* w, int n_groups, con
   long long est_jobs = (long long)gy * est_chunks;
   if (listed) est_jobs = (long long)((active && max_active < n_groups) ? max_active : n_groups) + (long long)(total_rows / 32);   // (the bound is loose)
   if (est_jobs < 1) est_jobs = 1;
-  long long cps = (2LL * ctx->sm_count + est_jobs / 2) / est_jobs;
+  // (rounded down: with every slot of the GPU spoken for, a job or two more than estimated would put whole CTAs --
+  // tens of microseconds each -- into a second wave)
+  long long cps = 2LL * ctx->sm_count / est_jobs;
   const long long units = (long long)n_rb * kc;
   if (cps > 32) cps = 32;
   if (cps > units / 16) cps = units / 16;
