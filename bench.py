@@ -37,8 +37,8 @@ N_OUT, K_IN, GROUP = 14336, 4096, 32
 METRIC, UNIT = "int4_gemv_hbm_tbps", "TB/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu
-# capture of this command with 8 layers and 1 step (33.08 MB read; the 28 KB of results stay in L2).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 33_084_160
+# capture of this command with 8 layers and 1 step (33.10 MB read; the 28 KB of results stay in L2).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 33_104_640
 
 
 def algorithmic_bytes(m: int) -> int:
@@ -394,7 +394,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "pct_of_8tbps_nominal": 100.0 * value / world / 8.0,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "kernel": "qgemv_sk_kernel<Q4_F16> (persistent GEMV, M <= 8)" if m <= 8 else "qgemm_mma_kernel / qgemm_umma_kernel", "algorithmic_bytes_per_launch": bytes_launch,
+                         "kernel": "qgemv_sk_kernel<Q4_F16> (persistent GEMV)" if m == 1 else "qgemm_sk_kernel (2..8 rows) / qgemm_mma_kernel / qgemm_umma_kernel", "algorithmic_bytes_per_launch": bytes_launch,
                          "avg_launch_us": ms_per_step * 1e3 / L},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": L * m * K_IN * 2,
                     "d2h_bytes_per_step": L * m * N_OUT * 2, "steps": e2e_steps,
