@@ -131,8 +131,9 @@ int tq_ctx_create(int device, void* stream, tq_ctx** out) {
   if (cudaMalloc(&ctx->gemv_ws, ws_bytes) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaMemsetAsync(ctx->gemv_ws, 0, ws_bytes, ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaMalloc(&ctx->skg_jobs, kSkgJobs * sizeof(int)) != cudaSuccess) return bail(TQ_ECUDA);
-  if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_err), sizeof(int), cudaHostAllocDefault) != cudaSuccess) return bail(TQ_ECUDA);
-  *ctx->host_err = 0;
+  if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->host_err), 2 * sizeof(int), cudaHostAllocMapped) != cudaSuccess) return bail(TQ_ECUDA);
+  ctx->host_err[0] = ctx->host_err[1] = 0;
+  if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->host_err_dev), ctx->host_err, 0) != cudaSuccess) return bail(TQ_ECUDA);
   if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return bail(TQ_ECUDA);
   *out = ctx;
   return TQ_OK;
@@ -161,11 +162,26 @@ const char* tq_last_error(const tq_ctx* ctx) { return ctx ? ctx->last_error.c_st
 
 void* tq_ctx_stream(tq_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
+// Last kernel before a wait: copies the status word into pinned host memory and, after a system-wide fence, the wait's
+// number behind it.  It waits for everything before it on the stream, so a host that sees the number has the results.
+__global__ void sync_signal_kernel(const int* dev_err, volatile int* host_words, unsigned seq) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // (launched with programmatic stream serialization)
+  host_words[0] = *dev_err;
+  __threadfence_system();
+  host_words[1] = (int)seq;
+}
+
 int tq_sync(tq_ctx* ctx) {
   if (int st = bind(ctx)) return st;
-  // the status word rides behind the work on the same stream: one wait, no second round trip
-  TQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_err, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
-  TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  // A short wait costs less as a look at pinned memory than as a driver call (the wake-up of cudaStreamSynchronize is
+  // ~10 us): the signal kernel rides behind the work on the same stream, the host polls its word for up to ~100 us and
+  // only then blocks in the driver.  Either way the status word arrives with the same round trip.
+  const unsigned seq = ++ctx->sync_seq;
+  volatile int* hw = ctx->host_err;
+  TQ_CUDA(ctx, launch_k(ctx, sync_signal_kernel, dim3(1), dim3(1), 0, (const int*)ctx->dev_err, (volatile int*)ctx->host_err_dev, seq));
+  bool seen = false;
+  for (int spin = 0; spin < 40000 && !seen; ++spin) seen = (unsigned)hw[1] == seq;
+  if (!seen) TQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   ctx->inflight_unknown = false;   // the stream has drained: nothing is in flight
   ctx->n_inflight = 0;
   const int code = *ctx->host_err;

@@ -31,7 +31,9 @@ struct tq_ctx {
                                  // consecutive launches rotate through the sets (at most three kernels ever have
                                  // resident CTAs at a time: a CTA slot only frees when an older kernel's CTA exits)
   unsigned gemv_seq = 0;
-  int* host_err = nullptr;       // pinned copy target of dev_err: tq_sync reads the status with one stream wait
+  int* host_err = nullptr;       // pinned [2]: the device's status word and the number of the last tq_sync whose signal kernel ran
+  int* host_err_dev = nullptr;   // ... as the device sees it
+  unsigned sync_seq = 0;
   void* xprep = nullptr;         // activation staging for tq_qlinear (bf16 copy / 3-way f32 split)
   size_t xprep_bytes = 0;
   void* scratch = nullptr;       // general workspace (attention partials, host-call staging, ...)
