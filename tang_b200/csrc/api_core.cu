@@ -176,6 +176,7 @@ int tq_sync(tq_ctx* ctx) {
   // A short wait costs less as a look at pinned memory than as a driver call (the wake-up of cudaStreamSynchronize is
   // ~10 us): the signal kernel rides behind the work on the same stream, the host polls its word for up to ~100 us and
   // only then blocks in the driver.  Either way the status word arrives with the same round trip.
+  TQ_REQUIRE(ctx, !ctx->capturing, "tq_sync: a graph capture is open (a capture cannot wait for the stream)");
   const unsigned seq = ++ctx->sync_seq;
   volatile int* hw = ctx->host_err;
   TQ_CUDA(ctx, launch_k(ctx, sync_signal_kernel, dim3(1), dim3(1), 0, (const int*)ctx->dev_err, (volatile int*)ctx->host_err_dev, seq));
