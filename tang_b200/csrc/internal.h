@@ -48,6 +48,11 @@ struct tq_ctx {
   // overlap none of the outputs reads them without waiting and lets its own successor be scheduled at once; if
   // its output and residual are clear of everything listed as well, it does not wait at all.
   bool inflight_unknown = true;
+  // Set around one tq_qlinear call by a caller that wants the row sums of squares of the f32 output (residual
+  // included), [m][row blocks of the weight]: the persistent GEMV kernels store them and set ss_written; every other
+  // path leaves both alone.
+  float* ss_req = nullptr;
+  bool ss_written = false;
   int n_inflight = 0;
   struct Range { uintptr_t lo, hi; bool written; } inflight[96];
   // Host-vector matvecs (tq_q_matvec_host*) with pinned vectors: a one-CTA kernel copies x from the pinned host
@@ -121,6 +126,10 @@ struct QlinearNorm {
   float* h_out = nullptr;
   float eps = 0.f;
   void* xn_tmp = nullptr;      // bf16 [m][cols]: the normalised rows, when the fused kernel does not apply
+  // n_sumsq partial sums of squares per row of h, [m][n_sumsq], left by the projection that wrote h (tq_ctx::ss_req);
+  // delta is then null.  Only a shortcut: the separate operators ignore it.
+  const float* sumsq = nullptr;
+  int n_sumsq = 0;
 };
 int qlinear_fused(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, const QlinearNorm* norm, size_t m, void* y, int y_dtype,
                   size_t ldy, bool swiglu, float* gu_tmp);

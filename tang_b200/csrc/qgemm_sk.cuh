@@ -37,7 +37,7 @@ __host__ __device__ inline size_t skw_fixed_bytes(int kind, int w, int skc, int 
   return (size_t)kSkwHeaderBytes + skw_red_bytes(w, nt) + (size_t)mx * skw_x_stride(skc) + skw_csum_bytes(kind, skc, nt);
 }
 
-template <int KIND, int W, int TPW, int NT, int MINB = 2>
+template <int KIND, int W, int TPW, int NT, int MINB = 2, bool SS = false>
 __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemm_sk_kernel(const QGemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr bool kIs8 = (KIND == Q8_F32 || KIND == I8_ROW);
@@ -116,6 +116,7 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemm_sk_kernel(const QGem
     for (int i = 0; i < NV; ++i) {
       const int idx = lane + 32 * i;
       const int r = rb * 16 + (idx & 15), m = idx >> 4;
+      float sq = 0.f;
       if (idx < n_out && r < p.n_rows) {
         const size_t o = (size_t)m * p.ldy + r;
         float v = vals[i];
@@ -124,7 +125,10 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemm_sk_kernel(const QGem
           reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(v);
         else
           reinterpret_cast<float*>(p.y)[o] = v;
+        sq = v * v;
       }
+      if constexpr (SS)
+        if (p.ss_out) sk_store_sumsq(p.ss_out, sq, lane, m, p.m_out, p.n_row_blocks, rb);
     }
   };
   // One parked partial: NT * 128 words of (value bits | tag << 32), each written with one 64-bit store.  Adds what
@@ -240,7 +244,10 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemm_sk_kernel(const QGem
       const float* hrow = p.nh + (size_t)(live ? m : 0) * p.ld_h;
       const float* drow = p.ndelta ? p.ndelta + (size_t)(live ? m : 0) * p.ld_h : nullptr;
       float sq = 0.f;
-      if (live)
+      float total = 0.f;
+      const bool have_ss = SS && p.ss_in != nullptr;
+      if (have_ss) total = sk_load_sumsq(p.ss_in + (size_t)(live ? m : 0) * p.ss_n, p.ss_n, lane);
+      if (live && !have_ss)
         for (int k = 4 * (sub * 32 + lane); k < p.kx; k += 128 * gsz) {
           float4 v = __ldcg(reinterpret_cast<const float4*>(hrow + k));
           if (drow) {
@@ -249,12 +256,14 @@ __global__ void __launch_bounds__(32 * (W + 2), MINB) qgemm_sk_kernel(const QGem
           }
           sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
-      sq = warp_sum(sq);
-      if (lane == 0) scratch[warp] = sq;
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * W) : "memory");
+      if (!have_ss) {
+        sq = warp_sum(sq);
+        if (lane == 0) scratch[warp] = sq;
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * W) : "memory");
+      }
       if (live) {
-        float total = 0.f;
-        for (int q = 0; q < gsz; ++q) total += scratch[m * gsz + q];
+        if (!have_ss)
+          for (int q = 0; q < gsz; ++q) total += scratch[m * gsz + q];
         const float inv = 1.0f / sqrtf(total / (float)p.kx + p.norm_eps);
         uint8_t* xrow_s = smem + x_off + (size_t)m * x_stride;
         const int k0 = slab * kxs;

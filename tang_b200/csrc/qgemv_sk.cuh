@@ -59,6 +59,13 @@ struct QGemvParams {
   float* nh_out;                // optional [mx][ld_h]
   long long ld_h;
   float norm_eps;
+  // The row sums of squares, handed from the projection that wrote the residual stream to the one that normalises it
+  // (the several-row kernel only): a kernel with ss_out stores, per 16-row block, the sum of the squares of what it
+  // wrote to y (y and the residual included), [m_out][n_row_blocks] floats; a fused prologue with ss_in adds the ss_n
+  // partial sums of each row of nh instead of reading the whole row first (ndelta is then null).
+  float* ss_out;
+  const float* ss_in;
+  int ss_n;
   // Fused epilogue: rows 0..7 of every 16-row block are gate rows and rows 8..15 the matching up rows; what is stored
   // is silu(gate) * up (crates/tang-compute/src/device.rs:727-736), n_rows / 2 values per activation row.
   int swiglu;
@@ -84,6 +91,23 @@ struct QGemvParams {
 // the first replay has count 1).
 __host__ __device__ inline unsigned sk_x_tag_value(unsigned seq, const unsigned* epoch) {
   return epoch ? (((*epoch) & 0x7FFFu) << 16) | (seq & 0xFFFFu) : (seq | 0x80000000u);
+}
+
+// The 16 lanes that hold one activation row's 16 outputs of a row block add their squares (a fixed tree) and the
+// first of them stores the sum to ss[m][rb].  Called by whole warps.
+__device__ __forceinline__ void sk_store_sumsq(float* ss, float sq, int lane, int m, int m_out, int n_rb, int rb) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if ((lane & 15) == 0 && m < m_out) ss[(size_t)m * n_rb + rb] = sq;
+}
+
+// The sum of a row's n partial sums of squares, the same in every lane and every warp that asks.
+__device__ __forceinline__ float sk_load_sumsq(const float* ss, int n, int lane) {
+  float a = 0.f;
+  for (int k = lane; k < n; k += 32) a += __ldcg(ss + k);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+  return a;
 }
 
 constexpr int kSkMaxStages = 12;

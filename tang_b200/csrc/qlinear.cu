@@ -233,9 +233,9 @@ static cudaError_t launch_sk_kind(tq_ctx* ctx, const QGemvParams& p, unsigned gr
 // only a slab of the activation rows beside its weight ring.  Returns false when the shape does
 // not fit; the caller then uses another kernel.
 // ---------------------------------------------------------------------------------------------
-template <int KIND, int TPW, int NT>
+template <int KIND, int TPW, bool SS>
 static cudaError_t launch_skw_kernel(tq_ctx* ctx, const QGemvParams& p, unsigned grid, size_t smem) {
-  auto kern = qgemm_sk_kernel<KIND, 8, TPW, NT, 2>;
+  auto kern = qgemm_sk_kernel<KIND, 8, TPW, 1, 2, SS>;
   static size_t attr_bytes[64] = {};   // per device
   const int dev = ctx->device & 63;
   if (smem > 48 * 1024 && attr_bytes[dev] < smem) {
@@ -249,7 +249,10 @@ static cudaError_t launch_skw_kernel(tq_ctx* ctx, const QGemvParams& p, unsigned
 template <int KIND>
 static cudaError_t launch_skw_kind(tq_ctx* ctx, const QGemvParams& p, unsigned grid, size_t smem, int tpw, int nt) {
   (void)nt;   // one column tile of eight rows: the launcher takes up to eight rows
-  return tpw == 2 ? launch_skw_kernel<KIND, 2, 1>(ctx, p, grid, smem) : launch_skw_kernel<KIND, 1, 1>(ctx, p, grid, smem);
+  // (the variant that hands sums of squares over is a kernel of its own: the plain one pays nothing for it)
+  if (p.ss_out || p.ss_in)
+    return tpw == 2 ? launch_skw_kernel<KIND, 2, true>(ctx, p, grid, smem) : launch_skw_kernel<KIND, 1, true>(ctx, p, grid, smem);
+  return tpw == 2 ? launch_skw_kernel<KIND, 2, false>(ctx, p, grid, smem) : launch_skw_kernel<KIND, 1, false>(ctx, p, grid, smem);
 }
 
 static bool launch_qgemm_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat16* xs, size_t ldxs, int mx, int combine,
@@ -326,6 +329,11 @@ static bool launch_qgemm_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   p.nh_out = norm ? norm->h_out : nullptr;
   p.ld_h = kx;
   p.norm_eps = norm ? norm->eps : 0.f;
+  p.ss_in = norm ? norm->sumsq : nullptr;
+  p.ss_n = norm ? norm->n_sumsq : 0;
+  // (asked for by the caller of the enclosing operator: the row sums of squares of what this launch stores)
+  p.ss_out = (ctx->ss_req && !swiglu && combine == 1 && y_dtype == TQ_F32) ? ctx->ss_req : nullptr;
+  if (p.ss_out) ctx->ss_written = true;
   p.swiglu = swiglu ? 1 : 0;
   p.x_tag = x_tag;
   p.x_seq = x_seq;
@@ -440,6 +448,9 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
   p.nh_out = norm ? norm->h_out : nullptr;
   p.ld_h = kx;
   p.norm_eps = norm ? norm->eps : 0.f;
+  p.ss_in = nullptr;   // (this kernel neither reads nor leaves sums of squares)
+  p.ss_n = 0;
+  p.ss_out = nullptr;
   p.swiglu = swiglu ? 1 : 0;
   p.x_tag = x_tag;
   p.x_seq = x_seq;

@@ -86,6 +86,20 @@ def test_gate_up_in_the_reference_order_takes_the_separate_swiglu(dev, orc):
     run_case(dev, orc, host, B=12, ctx_lens=list(range(5, 125, 10)), max_seq=160, steps=1, interleave=True)   # > 8 rows: separate operators
 
 
+def test_four_to_eight_rows_hand_the_sums_of_squares_over(dev, orc):
+    """From four rows on, the output and down projections add the residual themselves and leave each row's sum of
+    squares per 16-row block; the pre-norm fused into the next projection adds those instead of reading the row twice."""
+    host = HostLlama(np.random.default_rng(4), n_layers=2, d=256, n_heads=4, n_kv=2, hd=128, ffn=512, vocab=1024)
+    run_case(dev, orc, host, B=5, ctx_lens=[0, 17, 70, 131, 140], max_seq=160, steps=2)
+    run_case(dev, orc, host, B=8, ctx_lens=[3, 0, 64, 65, 127, 128, 129, 150], max_seq=160, steps=1)
+
+
+def test_llama3_8b_width_four_rows(dev, orc):
+    """Full Llama-3-8B layer widths at four rows (K in two slabs, 256 partial sums of squares per row)."""
+    host = HostLlama(np.random.default_rng(5), n_layers=2, d=4096, n_heads=32, n_kv=8, hd=128, ffn=14336, vocab=128256)
+    run_case(dev, orc, host, B=4, ctx_lens=[600, 0, 257, 31], max_seq=640)
+
+
 def test_single_sequence_many_heads(dev, orc):
     host = HostLlama(np.random.default_rng(2), n_layers=1, d=512, n_heads=8, n_kv=1, hd=128, ffn=1024, vocab=2048)
     run_case(dev, orc, host, B=1, ctx_lens=[300], max_seq=320)
