@@ -410,10 +410,11 @@ static bool launch_qgemv_sk(tq_ctx* ctx, const tq_qweight* w, const __nv_bfloat1
     // two measured 2.48 ms per decode step; one large CTA per SM 1.89 ms; this 1.79 ms).
     budget = half;
     if (units >= 2LL * ctx->sm_count * 8) grid = 2LL * ctx->sm_count;
-    // A short matrix with between one and two row blocks per SM (the 4096 x 4096 output projection): one whole row
-    // block per CTA.  No row block is cut, so nothing is parked and nobody waits at the end, which for so few bytes
-    // is worth more than the last 14 % of the slots.
-    if (w->n_kc <= 48 && w->n_rb >= ctx->sm_count && w->n_rb <= 2 * ctx->sm_count) grid = w->n_rb;
+    // A short matrix with 1.5 to 2 row blocks per SM (the 4096 x 4096 output projection): one whole row block per
+    // CTA.  No row block is cut, so nothing is parked and nobody waits at the end, which for so few bytes is worth
+    // more than the last 14 % of the slots (same-box decode step at one row: 1.82 -> 1.78 ms).  Fewer row blocks or
+    // shorter rows (the tensor-parallel shards) measured no better that way and keep the even split.
+    if (w->n_kc >= 24 && w->n_kc <= 48 && 2 * w->n_rb >= 3 * ctx->sm_count && w->n_rb <= 2 * ctx->sm_count) grid = w->n_rb;
   } else if (fixed + 3 * stage <= most) budget = most;
   if (fixed + 2 * stage > budget) return false;
   int stages = (int)((budget - fixed) / stage);
