@@ -652,6 +652,25 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
             us = _time_ms(torch, stream, dev, g.launch, 10, 3) * 1e3 / n8
             g.free()
             row[tag] = {"us_per_launch": us, "gbs": byt / us / 1e3, "frac_of_hbm_peak": byt / us / 1e3 / peak_gbs}
+        # the same weights against many rows (the tcgen05 GEMM from 32 rows on): bf16 activations, f32 results
+        for m in (64, 2048):
+            xm = bf16((m, 4096))
+            ym = torch.empty((n8, m, 4096), dtype=torch.float32, device="cuda")
+            stream.synchronize()
+
+            def many8():
+                for i, w in enumerate(w8):
+                    dev._check(L_.tq_qlinear(dev._ctx, C.c_void_p(w.handle), C.c_void_p(xm.data_ptr()), tb.BF16, 0, m,
+                                             C.c_void_p(ym[i].data_ptr()), tb.F32, 0, None))
+            many8()
+            dev.sync()
+            dev.begin_capture()
+            many8()
+            g = dev.end_capture()
+            us = _time_ms(torch, stream, dev, g.launch, 10, 3) * 1e3 / n8
+            g.free()
+            row["m%d_bf16_x" % m] = {"us_per_launch": us, "tflops": 2.0 * m * 4096 * 4096 / us / 1e6}
+            del xm, ym
         int8.append(row)
         for w in w8:
             w.free()

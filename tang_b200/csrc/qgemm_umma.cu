@@ -11,7 +11,8 @@ template <int KIND, int TERMS>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
-  constexpr int TB = (KIND == I8_ROW) ? 2048 : (KIND == Q4_F16) ? 1152 : 1280;
+  constexpr int TB = (KIND == I8_ROW) ? 2048 : (KIND == Q8_F32) ? 2304 : (KIND == Q4_F16) ? 1152 : 1280;
+  constexpr bool kIs8 = KIND == I8_ROW || KIND == Q8_F32;
   static_assert(KIND != I8_ROW || TERMS == 1, "int8 rows carry no scale into the operand: one exact term");
   constexpr int kMaxStages = 6;
   // ---- shared-memory carve-up (operand tiles need 1024-byte alignment for the 128-byte swizzle)
@@ -194,8 +195,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       const int rbi = combo >> 6, h = (combo >> 5) & 1, L = combo & 31;
       const int g = L >> 2, t = L & 3;
       const int row = rbi * 16 + g + 8 * h;
-      src_off[i] = rbi * KT * TB + (KIND == I8_ROW ? h * 1024 : h * 512) + 16 * L;
-      sc_off[i] = rbi * KT * TB + 1024 + (KIND == Q4_F16 ? h * 64 + g * 8 : h * 128 + g * 16);
+      src_off[i] = rbi * KT * TB + (kIs8 ? h * 1024 : h * 512) + 16 * L;
+      sc_off[i] = rbi * KT * TB + (kIs8 ? 2048 : 1024) + (KIND == Q4_F16 ? h * 64 + g * 8 : h * 128 + g * 16);
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) dst_off[i][jj] = row * 128 + (((4 * jj + t) ^ (row & 7)) << 4);
     }
@@ -244,10 +245,16 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
           }
           continue;
         }
-        const uint2 w2 = *reinterpret_cast<const uint2*>(raw + src_off[i] + 8 * c);   // blocks 2c, 2c+1
+        // blocks 2c, 2c+1: eight nibbles per word (Q4), or the [even k | odd k] byte planes of both blocks (Q8)
+        uint2 w2 = make_uint2(0u, 0u);
+        uint4 w8 = make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (KIND == Q8_F32) w8 = *reinterpret_cast<const uint4*>(raw + src_off[i] + 512 * c);
+        else w2 = *reinterpret_cast<const uint2*>(raw + src_off[i] + 8 * c);
         // The scale as s_hi + s_lo, two bf16 numbers (exact for an f16 scale: 11 = 8 + 3 significant bits).
         // With t = q*s_lo (7 bits, exact in bf16), hi = fma(q, s_hi, t) is the exact product rounded once;
         // lo = fma(q, s_hi, -hi) + t = q*scale - hi, both steps exact, so hi + lo reproduces the product.
+        // (f32 scales keep their first 16 significant bits this way, and with int8 values t itself is rounded to 8
+        // bits: hi + lo is then the product to about 2^-16.)
         float2 f;
         if (KIND == Q4_F16) f = __half22float2(*reinterpret_cast<const __half2*>(raw + sc_off[i] + 4 * c));
         else f = *reinterpret_cast<const float2*>(raw + sc_off[i] + 8 * c);
@@ -259,7 +266,9 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         for (int jj = 0; jj < 2; ++jj) {
           const uint32_t s_hi = prmt(sh, sh, jj ? 0x3232u : 0x1010u), s_lo = prmt(sl, sl, jj ? 0x3232u : 0x1010u);
           uint32_t q[4];
-          dequant_q4_word(jj ? w2.y : w2.x, q);                  // (k0,k1) (k2,k3) (k4,k5) (k6,k7), exact ints
+          // (k0,k1) (k2,k3) (k4,k5) (k6,k7), exact ints
+          if constexpr (KIND == Q8_F32) dequant_i8_words(jj ? w8.z : w8.x, jj ? w8.w : w8.y, q);
+          else dequant_q4_word(jj ? w2.y : w2.x, q);
           uint32_t hi[4], lo[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -381,7 +390,7 @@ static EncodeTiledFn encode_tiled() {
 }
 
 bool umma_supported(const tq_qweight* w, size_t m) {
-  return (w->kind == TQ_Q4_F16 || w->kind == TQ_Q4_F32 || w->kind == TQ_I8_ROW) && w->rows % kUmmaRows == 0 &&
+  return (w->kind == TQ_Q4_F16 || w->kind == TQ_Q4_F32 || w->kind == TQ_Q8_F32 || w->kind == TQ_I8_ROW) && w->rows % kUmmaRows == 0 &&
          w->cols % kTileK == 0 && m >= 1;
 }
 
@@ -393,7 +402,7 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   if (w->kind == TQ_I8_ROW) terms = 1;   // exact with one term: the row scale is applied to the accumulator
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return fail(ctx, TQ_EUNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
-  TQ_REQUIRE(ctx, umma_supported(w, m), "tcgen05 GEMM: needs a Q4 or int8-per-row weight with rows %% 128 == 0 and cols %% 128 == 0");
+  TQ_REQUIRE(ctx, umma_supported(w, m), "tcgen05 GEMM: needs rows %% 128 == 0 and cols %% 128 == 0");
   TQ_REQUIRE(ctx, ((uintptr_t)x_bf16 & 15) == 0 && (ldx * 2) % 16 == 0, "tcgen05 GEMM: activation rows must be 16-byte aligned");
   // Ring sizes.  Two rules come from the dequant groups running ahead of one another (a parity wait
   // is only sound when the waiter is at most one phase ahead of the barrier): at least kUmmaGroups
@@ -497,6 +506,7 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   cudaError_t e;
   if (w->kind == TQ_I8_ROW) e = go(qgemm_umma_kernel<I8_ROW, 1>);
   else if (w->kind == TQ_Q4_F16) e = terms == 2 ? go(qgemm_umma_kernel<Q4_F16, 2>) : go(qgemm_umma_kernel<Q4_F16, 1>);
+  else if (w->kind == TQ_Q8_F32) e = terms == 2 ? go(qgemm_umma_kernel<Q8_F32, 2>) : go(qgemm_umma_kernel<Q8_F32, 1>);
   else e = terms == 2 ? go(qgemm_umma_kernel<Q4_F32, 2>) : go(qgemm_umma_kernel<Q4_F32, 1>);
   TQ_CUDA(ctx, e);
   return TQ_OK;

@@ -227,6 +227,9 @@ def test_config1_int4_full_size(dev, orc, m):
     (0, 512, 4096, 130),      # long k: every ring wraps many times
     (3, 256, 512, 40),        # int8 with one scale per row: integers into the operand, scale on the accumulator
     (3, 4096, 4096, 64),      # the int8 benchmark shape at a decode batch (split K)
+    (2, 256, 512, 70),        # Q8 blocks (int8 values, an f32 scale per 32): scaled in the operand like Q4
+    (2, 4096, 4096, 64),
+    (2, 384, 1024, 300),
 ])
 def test_tensor_memory_gemm(dev, orc, kind, rows, cols, m):
     """Many activation rows take the tcgen05 kernel (weights dequantised into 128-byte-swizzled
@@ -243,9 +246,9 @@ def test_tensor_memory_gemm(dev, orc, kind, rows, cols, m):
     want = orc.qmatmul(kind, sc, pay, rows, cols, xf[sel].astype(np.float64), threads=0)
     y = dev.qlinear(xb, w, m, tb.F32).to_vec().reshape(m, rows)
     dev.sync()
-    # f16 scales split exactly into the hi + lo pair; an f32 scale keeps 16 of its 24 bits there (2^-17 per product,
-    # 1e-5 of the output rms after the sum), which is measured against the 5 % floor
-    assert rel_err(y[sel], want, floor_frac=0.05 if kind == 0 else 0.01) < TOL_F32
+    # f16 scales split exactly into the hi + lo pair; an f32 scale (Q4 or Q8 blocks) keeps 16 of its 24 bits there
+    # (2^-17 per product, 1e-5 of the output rms after the sum), which is measured against the 5 % floor
+    assert rel_err(y[sel], want, floor_frac=0.05 if kind in (0, 2) else 0.01) < TOL_F32
     yb = dev.qlinear(xb, w, m, tb.BF16).to_vec().reshape(m, rows)
     dev.sync()
     yb = (yb.astype(np.uint32) << 16).view(np.float32)
