@@ -7,7 +7,7 @@
 
 namespace tq {
 
-template <int KIND, int TERMS>
+template <int KIND, int TERMS, bool TS = false>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -27,7 +27,8 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t base_u32 = smem_u32(smem_raw);
   uint8_t* tiles_s = smem_raw + kUmmaHeader + ((1024 - ((base_u32 + kUmmaHeader) & 1023)) & 1023);  // 1024-aligned
-  const size_t stage_bytes = umma_stage_bytes(TERMS, p.ntok);
+  const size_t stage_bytes = umma_stage_bytes(TERMS, p.ntok, TS ? 1 : 0);
+  constexpr int kBOff = TS ? 0 : TERMS * kUmmaRows * 128;   // the activation box inside a stage
   uint8_t* raw_s = tiles_s + (size_t)p.stages * stage_bytes;   // [raw stages][8 tiles]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -114,7 +115,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       for (int kb = 0; kb < n_kb && !*failed; ++kb) {
         if (!mbar_wait_spin(&empty[s], ph ^ 1u)) { give_up(DERR_EMPTY_WAIT); break; }
         mbar_arrive_expect_tx(&x_full[s], (uint32_t)p.ntok * 128u);
-        tma_load_2d(tiles_s + (size_t)s * stage_bytes + (size_t)TERMS * kUmmaRows * 128, &x_map,
+        tma_load_2d(tiles_s + (size_t)s * stage_bytes + (size_t)kBOff, &x_map,
                     (kc_begin * 2 + kb) * kUmmaK, m0, &x_full[s]);
         if (++s == S) {
           s = 0;
@@ -134,7 +135,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     const bool leader = elect_one();
     const uint32_t idesc = umma_idesc_bf16(p.ntok);
     const uint64_t desc0 = umma_desc_sw128(tiles_s);
-    const uint32_t stage_u = (uint32_t)(stage_bytes >> 4), b_off_u = (uint32_t)((TERMS * kUmmaRows * 128) >> 4);
+    const uint32_t stage_u = (uint32_t)(stage_bytes >> 4), b_off_u = (uint32_t)(kBOff >> 4);
     bool ok = true;
     const int odd = warp == 3;
     // Each issuer rotates over n_acc / 2 accumulators: the tensor core truncates every f32 addition, an error that
@@ -164,8 +165,15 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
 #pragma unroll
         for (int k16 = 0; k16 < kUmmaK / 16; ++k16) {
           const uint64_t bd = ad + b_off_u + 2 * k16;
-          umma_f16(acc, ad + 2 * k16, bd, idesc, fresh | (k16 != 0));
-          if (TERMS == 2) umma_f16(acc, ad + (kUmmaRows * 128 >> 4) + 2 * k16, bd, idesc, 1u);
+          if constexpr (TS) {
+            // the stage's weights sit in tensor memory: 32 columns (64 k) of the hi term, then 32 of the lo term
+            const uint32_t a_t = tmem_d + (uint32_t)(p.a_col0 + s_cur * (32 * TERMS) + 8 * k16);
+            umma_f16_ts(acc, a_t, bd, idesc, fresh | (k16 != 0));
+            if (TERMS == 2) umma_f16_ts(acc, a_t + 32u, bd, idesc, 1u);
+          } else {
+            umma_f16(acc, ad + 2 * k16, bd, idesc, fresh | (k16 != 0));
+            if (TERMS == 2) umma_f16(acc, ad + (kUmmaRows * 128 >> 4) + 2 * k16, bd, idesc, 1u);
+          }
         }
       }
       if (leader) umma_commit(&empty[s_cur]);   // arrives when the MMAs above have finished reading the stage
@@ -231,6 +239,63 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       uint8_t* a_hi = tiles_s + (size_t)s_cur * stage_bytes;
       uint8_t* a_lo = a_hi + kUmmaRows * 128;
       const uint8_t* raw = raw_s + ((size_t)r_cur * 8 * KT + within_cur) * TB;
+      if constexpr (TS) {
+        // ---- weights to tensor memory: this thread owns output row 32 * (warp % 4) + lane, i.e. that lane, and
+        // converts the row's 64 k of the stage.  In a fragment tile the row's nibbles are 64 contiguous bytes (its
+        // four k quarters of 16 bytes, each holding one word per 32-block), its scales 8 or 16 contiguous bytes.
+        tc_fence_after();                          // the stage's columns were last read by MMAs whose commit was waited for
+        const int q4 = warp & 3;
+        const int rbi = 2 * q4 + (lane >> 4), h = (lane >> 3) & 1, g = lane & 7;
+        const uint8_t* wrow = raw + rbi * KT * TB + (kIs8 ? h * 1024 + 512 * c : h * 512 + 8 * c) + g * 64;
+        const uint32_t a_t = tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)(p.a_col0 + s_cur * (32 * TERMS));
+        uint32_t sh = 0, sl = 0;
+        if constexpr (KIND != I8_ROW) {
+          const uint8_t* srow = raw + rbi * KT * TB + (kIs8 ? 2048 : 1024);
+          float2 f;
+          if (KIND == Q4_F16) f = __half22float2(*reinterpret_cast<const __half2*>(srow + h * 64 + g * 8 + 4 * c));
+          else f = *reinterpret_cast<const float2*>(srow + h * 128 + g * 16 + 8 * c);
+          const __nv_bfloat162 shb = __floats2bfloat162_rn(f.x, f.y);
+          sh = *reinterpret_cast<const uint32_t*>(&shb);
+          const __nv_bfloat162 slb = __floats2bfloat162_rn(f.x - __uint_as_float(sh << 16), f.y - __uint_as_float(sh & 0xFFFF0000u));
+          sl = *reinterpret_cast<const uint32_t*>(&slb);
+        }
+        uint32_t wq[4][4];                         // [k quarter][word]: Q4 uses words 0, 1 (blocks 2c, 2c+1)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          if constexpr (kIs8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(wrow + 16 * t);
+            wq[t][0] = v.x; wq[t][1] = v.y; wq[t][2] = v.z; wq[t][3] = v.w;
+          } else {
+            const uint2 v = *reinterpret_cast<const uint2*>(wrow + 16 * t);
+            wq[t][0] = v.x; wq[t][1] = v.y; wq[t][2] = 0u; wq[t][3] = 0u;
+          }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          uint32_t hi[16], lo[16];
+          const uint32_t s_hi = prmt(sh, sh, jj ? 0x3232u : 0x1010u), s_lo = prmt(sl, sl, jj ? 0x3232u : 0x1010u);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            uint32_t q[4];                         // (k0,k1) (k2,k3) (k4,k5) (k6,k7) of k quarter t, exact ints
+            if constexpr (kIs8) dequant_i8_words(wq[t][2 * jj], wq[t][2 * jj + 1], q);
+            else dequant_q4_word(wq[t][jj], q);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if constexpr (KIND == I8_ROW) {
+                hi[4 * t + e] = q[e];
+              } else {
+                const uint32_t tt = bf16x2_mul(q[e], s_lo);
+                hi[4 * t + e] = bf16x2_fma(q[e], s_hi, tt);
+                if (TERMS == 2) lo[4 * t + e] = bf16x2_add(bf16x2_fma(q[e], s_hi, hi[4 * t + e] ^ 0x80008000u), tt);
+              }
+            }
+          }
+          tmem_st16(a_t + (uint32_t)(16 * jj), hi);
+          if (TERMS == 2) tmem_st16(a_t + (uint32_t)(32 + 16 * jj), lo);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      } else {
 #pragma unroll
       for (int i = 0; i < kCombos; ++i) {
         if constexpr (KIND == I8_ROW) {
@@ -281,6 +346,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
+      }
       __syncwarp();
       if (lane == 0) {                                                // one arrival per warp
         mbar_arrive(&a_full[s_cur]);
@@ -412,6 +478,17 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   const size_t budget = kSmemMax - kUmmaHeader - 1024;
   int ntok_max = (int)(((budget - 4 * raw_tile) / kUmmaGroups - (size_t)terms * kUmmaRows * 128) / 128) / 16 * 16;
   if (ntok_max > 256) ntok_max = 256;
+  // The dequantised weights in tensor memory instead of shared memory: writing them there and having the tensor core
+  // read them back is what fills the shared-memory pipe (32 KB written + 32 KB read per 64-k step with two terms).
+  // Four stages of weights take 32 columns per term each; the rest holds the accumulators, two at least (one per
+  // issuing warp): token tiles up to 128 with two terms, up to 192 with one.
+  // With one term the shared-memory operand allows wider token tiles: it stays where the narrower tiles would mean
+  // more of them, i.e. more conversions of the same weights (2048 rows: 9 tiles of 228 against 11 of 192 measured
+  // the same; 512 rows, three tiles either way: 95 -> 77 us).
+  const size_t m_basis = grp ? (size_t)grp->expected_rows : m;
+  const int ts_cap = terms == 2 ? 128 : 192;
+  const int ts = (terms == 2 || (m_basis + ts_cap - 1) / ts_cap <= (m_basis + ntok_max - 1) / ntok_max) ? 1 : 0;
+  if (ts && (ntok_max > ts_cap || terms == 2)) ntok_max = ts_cap;
   const size_t rows_g = grp ? w->rows / grp->n_groups : w->rows;       // output features per group
   if (grp) TQ_REQUIRE(ctx, grp->n_groups > 0 && w->rows % grp->n_groups == 0 && rows_g % kUmmaRows == 0 && grp->counts && grp->offsets,
                       "tcgen05 GEMM: every group needs a multiple of 128 output features");
@@ -437,15 +514,18 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   splits = (w->n_kc + kc_per_split - 1) / kc_per_split;
   int acc_stride = 32;
   while (acc_stride < ntok) acc_stride <<= 1;
-  const int n_acc = 512 / acc_stride > 16 ? 16 : 512 / acc_stride;   // 16 accumulators up to 32 tokens, 8 at 64, 4 at 128, 2 at 256
-  const int tmem_cols = n_acc * acc_stride;
+  if (ts && ntok > 128) acc_stride = 192;
+  const int acc_cols = ts ? 512 - 128 * terms : 512;
+  int n_acc = 2;                       // a power of two: 16 accumulators up to 32 tokens, 8 at 64, 4 at 128, 2 at 256 in
+  while (n_acc < 16 && 2 * n_acc * acc_stride <= acc_cols) n_acc <<= 1;   // all of tensor memory, fewer beside the weights
+  const int tmem_cols = ts ? 512 : n_acc * acc_stride;
   // Four A/B stages are what the dequant groups need; everything else goes to the packed-tile ring, because
   // the bytes in flight from HBM (ring slots not being read) are what hides its latency.  A ring slot holds
   // KT = 4 k-tiles of the eight row blocks (eight 4.6 KB copies) when three such slots fit, else KT = 2.
   int stages = kUmmaGroups;
-  if ((budget - 4 * raw_tile) / umma_stage_bytes(terms, ntok) < (size_t)stages)
+  if ((budget - 4 * raw_tile) / umma_stage_bytes(terms, ntok, ts) < (size_t)stages)
     return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: token tile of %d does not fit", ntok);
-  const size_t avail = budget - (size_t)stages * umma_stage_bytes(terms, ntok);
+  const size_t avail = budget - (size_t)stages * umma_stage_bytes(terms, ntok, ts);
   int kt = avail / (4 * raw_tile) >= 3 ? 4 : 2;
   int raw_stages = (int)(avail / ((size_t)kt * raw_tile));
   if (raw_stages > kUmmaMaxRawStages) raw_stages = kUmmaMaxRawStages;
@@ -477,6 +557,8 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.tmem_cols = tmem_cols;
   p.acc_stride = acc_stride;
   p.n_acc = n_acc;
+  p.ts = ts;
+  p.a_col0 = acc_cols;
   p.y_bf16 = y_dtype == TQ_BF16;
   p.err = ctx->dev_err;
   p.splits = splits;
@@ -491,7 +573,7 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.stages = stages;
   p.raw_stages = raw_stages;
   p.kt = kt;
-  const size_t smem = umma_smem_bytes(w->kind, terms, ntok, stages, raw_stages * kt);
+  const size_t smem = umma_smem_bytes(w->kind, terms, ntok, stages, raw_stages * kt, ts);
   if (smem > kSmemMax) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: %zu bytes of shared memory needed", smem);
   dim3 grid((unsigned)(rows_g / kUmmaRows), (unsigned)((m + ntok - 1) / ntok), (unsigned)splits);
   if (grp) {
@@ -504,7 +586,12 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
     return launch_k(ctx, kern, grid, dim3(kUmmaThreads), smem, map, p);
   };
   cudaError_t e;
-  if (w->kind == TQ_I8_ROW) e = go(qgemm_umma_kernel<I8_ROW, 1>);
+  if (ts) {
+    if (w->kind == TQ_I8_ROW) e = go(qgemm_umma_kernel<I8_ROW, 1, true>);
+    else if (w->kind == TQ_Q4_F16) e = terms == 2 ? go(qgemm_umma_kernel<Q4_F16, 2, true>) : go(qgemm_umma_kernel<Q4_F16, 1, true>);
+    else if (w->kind == TQ_Q8_F32) e = terms == 2 ? go(qgemm_umma_kernel<Q8_F32, 2, true>) : go(qgemm_umma_kernel<Q8_F32, 1, true>);
+    else e = terms == 2 ? go(qgemm_umma_kernel<Q4_F32, 2, true>) : go(qgemm_umma_kernel<Q4_F32, 1, true>);
+  } else if (w->kind == TQ_I8_ROW) e = go(qgemm_umma_kernel<I8_ROW, 1>);
   else if (w->kind == TQ_Q4_F16) e = terms == 2 ? go(qgemm_umma_kernel<Q4_F16, 2>) : go(qgemm_umma_kernel<Q4_F16, 1>);
   else if (w->kind == TQ_Q8_F32) e = terms == 2 ? go(qgemm_umma_kernel<Q8_F32, 2>) : go(qgemm_umma_kernel<Q8_F32, 1>);
   else e = terms == 2 ? go(qgemm_umma_kernel<Q4_F32, 2>) : go(qgemm_umma_kernel<Q4_F32, 1>);

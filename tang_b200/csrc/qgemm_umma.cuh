@@ -20,6 +20,12 @@
 //     bf16 x bf16 -> f32), each into an accumulator of its own, and commits each stage back to the
 //     producers;
 //   * the dequant warps finally read both accumulators with tcgen05.ld, add them and store y.
+// Tensor-memory operand (UmmaParams::ts, every launch whose token tile allows it): the A tiles do not go through
+// shared memory at all.  A dequant thread owns one output row = one tensor-memory lane (in a fragment tile the row's
+// nibbles are 64 contiguous bytes), converts the row's 64 k of the stage and writes them with tcgen05.st (32 columns
+// per term and stage); the MMA takes A from tensor memory and only the activation box from shared memory.  Writing
+// 32 KB of A tiles per step and reading them back was what bound the step time (14336 x 4096 at 64 rows, f32
+// results: the decode step at batch 64 went from 9.55 to 8.26 ms; 4096^2 Q8 blocks at 2048 rows 386 -> 130 us).
 // Every mbarrier wait is bounded; on failure the CTA records a code, skips ahead and still frees its
 // tensor memory.
 #pragma once
@@ -50,6 +56,10 @@ struct UmmaParams {
   int ntok;               // tokens per CTA tile = UMMA N (multiple of 16, <= 256)
   int tmem_cols;          // allocation: n_acc accumulators, power of two
   int acc_stride;         // columns between accumulators
+  int ts;                 // 1: the dequantised weights go to tensor memory (columns a_col0 ..: stages x terms x 32), not to
+                          //    shared memory, and the MMA reads them from there; a stage in shared memory is then the
+                          //    activation box alone
+  int a_col0;
   int n_acc;              // accumulators (2, 4, 8 or 16): step kb adds into number (kb & 1) + 2 * ((kb >> 1) % (n_acc / 2))
   int stages;             // A/B ring depth
   int raw_stages;         // packed-tile ring depth (slots of kt tiles of 128 k): what keeps the HBM stream in flight
@@ -77,13 +87,13 @@ struct UmmaGroups {
   int expected_rows = 0;   // typical counts[e]: sets the token tile
 };
 
-__host__ __device__ inline size_t umma_stage_bytes(int terms, int ntok) {
-  return (size_t)terms * kUmmaRows * 128 + (size_t)ntok * 128;   // A tiles + B tile, all 1024-aligned sizes
+__host__ __device__ inline size_t umma_stage_bytes(int terms, int ntok, int ts = 0) {
+  return (ts ? 0 : (size_t)terms * kUmmaRows * 128) + (size_t)ntok * 128;   // A tiles + B tile, all 1024-aligned sizes
 }
 constexpr int kUmmaMaxRawStages = 16;
 constexpr int kUmmaHeader = 1024;
-__host__ __device__ inline size_t umma_smem_bytes(int kind, int terms, int ntok, int stages, int raw_tiles) {
-  return kUmmaHeader + 1024 /*alignment slack*/ + (size_t)stages * umma_stage_bytes(terms, ntok) +
+__host__ __device__ inline size_t umma_smem_bytes(int kind, int terms, int ntok, int stages, int raw_tiles, int ts = 0) {
+  return kUmmaHeader + 1024 /*alignment slack*/ + (size_t)stages * umma_stage_bytes(terms, ntok, ts) +
          (size_t)raw_tiles * 8 * qk_tile_bytes(kind);
 }
 
@@ -126,6 +136,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Sixteen 32-bit columns of the calling warp's 32 lanes: thread i writes lane i (registers = consecutive columns).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem descriptor]: the A operand is read from tensor memory (lane = row, each 32-bit
+// column holds two consecutive k as bf16, eight columns per 16-k instruction).
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
