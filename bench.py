@@ -652,7 +652,7 @@ def run_extras(dev, tb, torch, stream, peak_gbs):
             us = _time_ms(torch, stream, dev, g.launch, 10, 3) * 1e3 / n8
             g.free()
             row[tag] = {"us_per_launch": us, "gbs": byt / us / 1e3, "frac_of_hbm_peak": byt / us / 1e3 / peak_gbs}
-        # the same weights against many rows (the tcgen05 GEMM from 32 rows on): bf16 activations, f32 results
+        # the same weights against many rows (the tcgen05 GEMM): bf16 activations, f32 results
         for m in (64, 2048):
             xm = bf16((m, 4096))
             ym = torch.empty((n8, m, 4096), dtype=torch.float32, device="cuda")

@@ -703,9 +703,12 @@ __global__ void swiglu_interleaved_kernel(const float* gu, size_t rows, size_t n
 }
 
 // Activation rows from which the tcgen05 kernel takes over from the mma.sync kernel.
-// Rows from which the tcgen05 kernel takes over.  With f32 outputs (two operand terms per weight) the mma.sync kernel
-// stays ahead a little longer: per Llama-3-8B layer at 24 rows 131 us against 145 us, at 32 rows 153 us against 149 us.
-static int umma_min_m(int y_dtype) { return y_dtype == TQ_F32 ? 32 : 24; }
+// Rows from which the tcgen05 kernel takes over from the mma.sync kernel (Llama-3-8B decode step, 32 layers, f32
+// outputs: 4.87 against 4.98 ms at 16 rows, 5.63 against 5.30 ms at 20, 6.10 against 5.50 ms at 24).
+static int umma_min_m(int y_dtype) {
+  (void)y_dtype;
+  return 17;
+}
 
 }  // namespace tq
 

@@ -288,7 +288,7 @@ def test_graph_recorded_before_a_workspace_grew_refuses_to_launch(dev, orc):
 
 @pytest.mark.parametrize("B", [16, 64])
 def test_llama3_8b_width_decode_batches(dev, orc, B):
-    """The benchmark's decode batches at full Llama-3-8B layer widths (two layers, context 2048): from 24 rows on
+    """The benchmark's decode batches at full Llama-3-8B layer widths (two layers, context 2048): from 17 rows on
     every linear layer of the step runs on the tcgen05 GEMM (split K for the narrow ones), which the small batches
     above never reach.  The oracle checks a seeded sample of the sequences."""
     import tang_b200 as tb

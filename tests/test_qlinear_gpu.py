@@ -204,7 +204,7 @@ def test_config1_int4_full_size(dev, orc, m):
     # the oracle on every row for m <= 8, on a seeded sample of token rows beyond that
     sel = np.arange(m) if m <= 8 else np.sort(rng.choice(m, 8, replace=False))
     want = orc.qmatmul(1, sc, pay, rows, cols, xf[sel].astype(np.float64), threads=0)
-    # From 24 rows on the call runs on the tensor-memory GEMM: exact products (hi + lo terms) added by the tensor
+    # From 17 rows on the call runs on the tensor-memory GEMM: exact products (hi + lo terms) added by the tensor
     # core's truncating f32 adder.  The steps rotate over as many accumulators as tensor memory holds (16 up to 32
     # tokens, 8 at 64, 4 at 128, 2 at 256), which keeps the error at 1e-4 .. 3e-4 against the same 1 % floor as the
     # register-accumulated path (it was 2.6e-5 of the output rms, i.e. up to 2.6e-3 at this floor, with two).
