@@ -462,10 +462,10 @@ int tq_llama_prefill(tq_llama* m, const int* token_ids_dev, const int* cache_sta
     TQ_STEP(tq_qlinear(ctx, L.wo, m->p_attn, TQ_BF16, q_dim, R, m->p_delta, TQ_F32, d, nullptr));
     TQ_STEP(tq_all_reduce_f32(ctx, m->comm, m->p_delta, R * d));
     TQ_STEP(tq_rms_norm(ctx, m->p_delta, TQ_F32, m->p_h, L.ffn_norm, TQ_BF16, R, d, c.eps, m->p_xn, TQ_BF16, m->p_h));
-    TQ_STEP(tq_qlinear(ctx, L.wgu, m->p_xn, TQ_BF16, d, R, m->p_gu, TQ_F32, 2 * (size_t)m->ffn_l, nullptr));
     if (L.wgu->gate_up_interleaved) {
-      TQ_STEP(launch_swiglu_interleaved(ctx, m->p_gu, R, m->ffn_l, m->p_act, TQ_BF16));
+      TQ_STEP(qlinear_fused(ctx, L.wgu, m->p_xn, nullptr, R, m->p_act, TQ_BF16, m->ffn_l, true, m->p_gu));
     } else {
+      TQ_STEP(tq_qlinear(ctx, L.wgu, m->p_xn, TQ_BF16, d, R, m->p_gu, TQ_F32, 2 * (size_t)m->ffn_l, nullptr));
       TQ_STEP(tq_swiglu(ctx, m->p_gu, m->p_gu + m->ffn_l, TQ_F32, 2 * (size_t)m->ffn_l, R, m->ffn_l, m->p_act, TQ_BF16));
     }
     TQ_STEP(tq_qlinear(ctx, L.wdown, m->p_act, TQ_BF16, m->ffn_l, R, m->p_delta, TQ_F32, d, nullptr));

@@ -402,6 +402,20 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
             const int m = m0 + c0 + i;
             if (m < m_end) __stcg(part + (size_t)m * p.n_rows + n, v[i]);
           }
+        } else if (p.swiglu) {
+          // lane l holds output row n: gate rows are the lanes with (l & 15) < 8, their up rows sit eight lanes on
+          const int o_col = (n >> 4) * 8 + (lane & 7);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float up = __shfl_down_sync(0xffffffffu, v[i], 8);
+            const int m = m0 + c0 + i;
+            if ((lane & 8) == 0 && m < m_end) {
+              const float g = v[i];
+              const float act = g * (1.0f / (1.0f + expf(-g))) * up;   // the formula of swiglu_kernel, term for term
+              if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + o_col] = __float2bfloat16_rn(act);
+              else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + o_col] = act;
+            }
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -442,6 +456,17 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         float sum = 0.f;
         for (int z = 0; z < p.splits; ++z) sum += __ldcg(src + z * plane);
         if constexpr (KIND == I8_ROW) sum *= row_scales[n];
+        if (p.swiglu) {
+          if (n & 8) continue;                                   // up rows are folded into their gate rows
+          float up = 0.f;
+          for (int z = 0; z < p.splits; ++z) up += __ldcg(src + 8 + z * plane);
+          if constexpr (KIND == I8_ROW) up *= row_scales[n + 8];
+          const float act = sum * (1.0f / (1.0f + expf(-sum))) * up;
+          const size_t o = (size_t)m * p.ldy + (n >> 4) * 8 + (n & 7);
+          if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(act);
+          else reinterpret_cast<float*>(p.y)[o] = act;
+          continue;
+        }
         if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(sum);
         else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + n] = sum;
       }
@@ -477,7 +502,7 @@ bool umma_supported(const tq_qweight* w, size_t m) {
 // With `grp`: `grp->n_groups` weight matrices stacked by rows (experts); group e multiplies rows
 // offsets[e] .. +counts[e] of x (device arrays) and m is the total row count of x / y.
 int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
-                      size_t ldy, int terms, const UmmaGroups* grp) {
+                      size_t ldy, int terms, const UmmaGroups* grp, bool swiglu) {
   if (w->kind == TQ_I8_ROW) terms = 1;   // exact with one term: the row scale is applied to the accumulator
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return fail(ctx, TQ_EUNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
@@ -573,6 +598,7 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.ts = ts;
   p.a_col0 = acc_cols;
   p.y_bf16 = y_dtype == TQ_BF16;
+  p.swiglu = swiglu ? 1 : 0;
   p.err = ctx->dev_err;
   p.splits = splits;
   p.kc_per_split = kc_per_split;
@@ -624,7 +650,7 @@ int launch_qgemm_umma_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, co
   g.max_active = max_active;
   g.max_rows = max_rows;
   g.expected_rows = expected_rows;
-  return launch_qgemm_umma(ctx, w, x_bf16, ldx, m_total, y, y_dtype, ldy, y_dtype == TQ_F32 ? 2 : 1, &g);
+  return launch_qgemm_umma(ctx, w, x_bf16, ldx, m_total, y, y_dtype, ldy, y_dtype == TQ_F32 ? 2 : 1, &g, false);
 }
 
 bool umma_grouped_supported(const tq_qweight* w, int n_groups) {

@@ -65,6 +65,8 @@ struct UmmaParams {
   int raw_stages;         // packed-tile ring depth (slots of kt tiles of 128 k): what keeps the HBM stream in flight
   int kt;                 // k-tiles per ring slot (2 or 4)
   int y_bf16;
+  int swiglu;             // the weight is a gate/up projection in the interleaved row order (rows 0..7 of every 16 gate, rows
+                          // 8..15 the matching up rows): y [M][n_rows / 2] = silu(gate) * up, formed from the f32 sums
   int splits;             // CTAs along K per output tile (gridDim.z)
   int kc_per_split;       // 128-k tiles per split
   float* partial;         // [splits][m_total][n_rows] f32, only when splits > 1

@@ -664,7 +664,7 @@ int launch_qgemm_grouped(tq_ctx* ctx, const tq_qweight* w, int n_groups, const v
 bool umma_supported(const tq_qweight* w, size_t m);
 struct UmmaGroups;
 int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size_t ldx, size_t m, void* y, int y_dtype,
-                      size_t ldy, int terms, const UmmaGroups* grp);
+                      size_t ldy, int terms, const UmmaGroups* grp, bool swiglu = false);
 
 // ---------------------------------------------------------------------------------------------
 // Gate/up weights in the row order the fused SwiGLU epilogue wants: out row block b = gate rows 8b..8b+7 then up
@@ -1219,6 +1219,9 @@ int qlinear_fused(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, const Ql
     xin = norm->xn_tmp;
   }
   if (!swiglu) return tq_qlinear(ctx, w, xin, TQ_BF16, cols, m, y, y_dtype, ldy, nullptr);
+  // many rows: the tcgen05 kernel applies silu(gate) * up to its f32 sums (two operand terms: exact products) itself
+  if (m >= (size_t)umma_min_m(TQ_F32) && umma_supported(w, m) && w->cols == (size_t)w->n_kc * kTileK && ((uintptr_t)xin & 15) == 0)
+    return launch_qgemm_umma(ctx, w, xin, cols, m, y, y_dtype, ldy, 2, nullptr, true);
   TQ_REQUIRE(ctx, gu_tmp != nullptr, "fused linear: no buffer for the gate/up projection");
   if (int st = tq_qlinear(ctx, w, xin, TQ_BF16, cols, m, gu_tmp, TQ_F32, w->rows, nullptr)) return st;
   const size_t n = w->rows / 2;
