@@ -7,13 +7,17 @@
 
 namespace tq {
 
-template <int KIND, int TERMS, bool TS = false>
+template <int KIND, int TERMS, bool TS = false, bool DUAL = false>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int TB = (KIND == I8_ROW) ? 2048 : (KIND == Q8_F32) ? 2304 : (KIND == Q4_F16) ? 1152 : 1280;
   constexpr bool kIs8 = KIND == I8_ROW || KIND == Q8_F32;
   static_assert(KIND != I8_ROW || TERMS == 1, "int8 rows carry no scale into the operand: one exact term");
+  // DUAL: the CTA covers two token tiles of p.ntok rows with one conversion of the weights: issuer warp 1 multiplies
+  // every stage with the first tile's activations, warp 3 with the second tile's, each into one accumulator
+  static_assert(!DUAL || (TS && TERMS == 1), "two token tiles per CTA: single-term weights in tensor memory");
+  constexpr int kTokTiles = DUAL ? 2 : 1;
   constexpr int kMaxStages = 6;
   // ---- shared-memory carve-up (operand tiles need 1024-byte alignment for the 128-byte swizzle)
   uint8_t* smem = smem_raw;
@@ -27,14 +31,14 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t base_u32 = smem_u32(smem_raw);
   uint8_t* tiles_s = smem_raw + kUmmaHeader + ((1024 - ((base_u32 + kUmmaHeader) & 1023)) & 1023);  // 1024-aligned
-  const size_t stage_bytes = umma_stage_bytes(TERMS, p.ntok, TS ? 1 : 0);
+  const size_t stage_bytes = umma_stage_bytes(TERMS, p.ntok, TS ? 1 : 0) * kTokTiles;
   constexpr int kBOff = TS ? 0 : TERMS * kUmmaRows * 128;   // the activation box inside a stage
   uint8_t* raw_s = tiles_s + (size_t)p.stages * stage_bytes;   // [raw stages][8 tiles]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.stages, RS = p.raw_stages, KT = p.kt;
   const int rb0 = blockIdx.x * (kUmmaRows / kTileRows);        // first 16-row block
-  int m0 = blockIdx.y * p.ntok;                                // first token of this CTA
+  int m0 = blockIdx.y * p.ntok * kTokTiles;                    // first token of this CTA
   int m_end = p.m_total;                                       // rows at or beyond this are not this CTA's to store
   const uint8_t* tile_base = p.tiles;
   const float* row_scales = p.row_scales;   // TQ_I8_ROW: per output row, applied to the accumulator
@@ -62,7 +66,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     for (int s = 0; s < S; ++s) {
       mbar_init(&x_full[s], 1);
       mbar_init(&a_full[s], kUmmaGroupWarps);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], DUAL ? 2 : 1);   // one commit per issuer that reads the stage
     }
     for (int r = 0; r < RS; ++r) {
       mbar_init(&raw_full[r], 1);
@@ -114,9 +118,12 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       uint32_t ph = 0;
       for (int kb = 0; kb < n_kb && !*failed; ++kb) {
         if (!mbar_wait_spin(&empty[s], ph ^ 1u)) { give_up(DERR_EMPTY_WAIT); break; }
-        mbar_arrive_expect_tx(&x_full[s], (uint32_t)p.ntok * 128u);
+        mbar_arrive_expect_tx(&x_full[s], (uint32_t)(p.ntok * kTokTiles) * 128u);
         tma_load_2d(tiles_s + (size_t)s * stage_bytes + (size_t)kBOff, &x_map,
                     (kc_begin * 2 + kb) * kUmmaK, m0, &x_full[s]);
+        if constexpr (DUAL)     // (rows beyond the matrix read as zeros, a box entirely beyond it too)
+          tma_load_2d(tiles_s + (size_t)s * stage_bytes + (size_t)p.ntok * 128, &x_map, (kc_begin * 2 + kb) * kUmmaK,
+                      m0 + p.ntok, &x_full[s]);
         if (++s == S) {
           s = 0;
           ph ^= 1u;
@@ -143,28 +150,30 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
     // (512 columns) are kept and the epilogue adds them, in accumulator order.
     const int rot_mask = (p.n_acc >> 1) - 1;
     int j = 0;                                  // this issuer's step count
-    int s = odd;
+    constexpr int kStep = DUAL ? 1 : 2;         // (two token tiles: every issuer takes every step)
+    int s = DUAL ? 0 : odd;
     uint32_t ph = 0;
     uint32_t tok_x = mbar_test(&x_full[s], 0), tok_a = mbar_test(&a_full[s], 0);
+    const uint32_t tile_off_u = DUAL ? (uint32_t)odd * (uint32_t)((p.ntok * 128) >> 4) : 0u;
 #pragma unroll 1
-    for (int kb = odd; kb < n_kb; kb += 2) {
+    for (int kb = DUAL ? 0 : odd; kb < n_kb; kb += kStep) {
       ok = !*failed && mbar_wait_token(&x_full[s], ph, tok_x) && mbar_wait_token(&a_full[s], ph, tok_a);
       if (!ok) { give_up(DERR_FULL_WAIT); break; }
       tc_fence_after();
       const uint64_t ad = desc0 + (uint64_t)((uint32_t)s * stage_u);
       const int s_cur = s;
-      s += 2;
+      s += kStep;
       if (s >= S) {
         s -= S;
         ph ^= 1u;
       }
-      const uint32_t acc = tmem_d + (uint32_t)((odd + 2 * (j & rot_mask)) * p.acc_stride);
-      const uint32_t fresh = j <= rot_mask ? 0u : 1u;   // the accumulator's first step overwrites it
+      const uint32_t acc = tmem_d + (uint32_t)((DUAL ? odd : odd + 2 * (j & rot_mask)) * p.acc_stride);
+      const uint32_t fresh = (DUAL ? j == 0 : j <= rot_mask) ? 0u : 1u;   // the accumulator's first step overwrites it
       ++j;
       if (leader) {
 #pragma unroll
         for (int k16 = 0; k16 < kUmmaK / 16; ++k16) {
-          const uint64_t bd = ad + b_off_u + 2 * k16;
+          const uint64_t bd = ad + b_off_u + tile_off_u + 2 * k16;
           if constexpr (TS) {
             // the stage's weights sit in tensor memory: 32 columns (64 k) of the hi term, then 32 of the lo term
             const uint32_t a_t = tmem_d + (uint32_t)(p.a_col0 + s_cur * (32 * TERMS) + 8 * k16);
@@ -378,10 +387,12 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
       const int q4 = warp & 3;                                 // tensor-memory lane quarter this warp may read
       const int n = blockIdx.x * kUmmaRows + 32 * q4 + lane;
       // two warps share a lane quarter and alternate over the 16-column chunks
+      for (int tile = 0; tile < kTokTiles; ++tile)
       for (int c0 = 16 * ((warp - kUmmaFirstDqWarp) >> 2); c0 < p.ntok; c0 += 16 * (kUmmaDqWarps / 4)) {
         float v[16], v1[16];
-        tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)c0, v);
-        const int used = min(p.n_acc, n_kb);              // step kb < n_acc is the first to touch accumulator kb
+        tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)(tile * p.acc_stride + c0), v);
+        const int mt = m0 + tile * p.ntok;                // first token of the tile
+        const int used = DUAL ? 1 : min(p.n_acc, n_kb);   // step kb < n_acc is the first to touch accumulator kb
         for (int a = 1; a < used; ++a) {
           tmem_ld16(tmem_d + ((uint32_t)(32 * q4) << 16) + (uint32_t)(a * p.acc_stride + c0), v1);
 #pragma unroll
@@ -399,7 +410,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
           float* part = p.partial + (size_t)blockIdx.z * p.m_total * p.n_rows;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int m = m0 + c0 + i;
+            const int m = mt + c0 + i;
             if (m < m_end) __stcg(part + (size_t)m * p.n_rows + n, v[i]);
           }
         } else if (p.swiglu) {
@@ -408,7 +419,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float up = __shfl_down_sync(0xffffffffu, v[i], 8);
-            const int m = m0 + c0 + i;
+            const int m = mt + c0 + i;
             if ((lane & 8) == 0 && m < m_end) {
               const float g = v[i];
               const float act = g * (1.0f / (1.0f + expf(-g))) * up;   // the formula of swiglu_kernel, term for term
@@ -419,7 +430,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int m = m0 + c0 + i;
+            const int m = mt + c0 + i;
             if (m < m_end) {
               if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(v[i]);
               else reinterpret_cast<float*>(p.y)[(size_t)m * p.ldy + n] = v[i];
@@ -525,17 +536,34 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   // the same; 512 rows, three tiles either way: 95 -> 77 us).
   const size_t m_basis = grp ? (size_t)grp->expected_rows : m;
   const int ts_cap = terms == 2 ? 128 : 192;
-  const int ts = (terms == 2 || (m_basis + ts_cap - 1) / ts_cap <= (m_basis + ntok_max - 1) / ntok_max) ? 1 : 0;
+  // Many rows, one term: a CTA takes TWO token tiles (each MMA issuer multiplies every stage with its own tile's
+  // activations), so the weights are converted once per 2 x <= 192 tokens; the accumulators are 2 x 192 columns, the
+  // weights 128.  Only where that still gives about a wave of CTAs (no K split in this form).
+  bool dual = false;
+  int dual_ntok = 0;
+  size_t n_pairs = 0;
+  if (terms == 1 && !grp && m > 192) {
+    int cap = (int)(((budget - 4 * raw_tile) / kUmmaGroups) / 256) / 16 * 16;   // two activation boxes per stage
+    if (cap > 192) cap = 192;
+    if (cap >= 64) {
+      n_pairs = (m + 2 * (size_t)cap - 1) / (2 * (size_t)cap);
+      dual_ntok = (int)(((m + 2 * n_pairs - 1) / (2 * n_pairs) + 15) / 16 * 16);
+      dual = (long long)(w->rows / kUmmaRows) * (long long)n_pairs >= (ctx->sm_count * 3) / 4;
+    }
+  }
+  const int ts = (dual || terms == 2 || (m_basis + ts_cap - 1) / ts_cap <= (m_basis + ntok_max - 1) / ntok_max) ? 1 : 0;
   if (ts && (ntok_max > ts_cap || terms == 2)) ntok_max = ts_cap;
   const size_t rows_g = grp ? w->rows / grp->n_groups : w->rows;       // output features per group
   if (grp) TQ_REQUIRE(ctx, grp->n_groups > 0 && w->rows % grp->n_groups == 0 && rows_g % kUmmaRows == 0 && grp->counts && grp->offsets,
                       "tcgen05 GEMM: every group needs a multiple of 128 output features");
   // grouped: the token tile follows the expected rows per group (tiles past a group's rows leave at once)
   const size_t m_tile_basis = grp ? (size_t)grp->expected_rows : m;
-  const size_t n_tok_tiles = grp ? 1 : (m + ntok_max - 1) / ntok_max;
+  const size_t n_tok_tiles = dual ? n_pairs : grp ? 1 : (m + ntok_max - 1) / ntok_max;   // CTAs along the tokens
   int ntok = (int)(((m_tile_basis + n_tok_tiles - 1) / n_tok_tiles + 15) / 16 * 16);
   if (ntok > ntok_max) ntok = ntok_max;
   if (ntok < 16) ntok = 16;
+  if (dual) ntok = dual_ntok;
+  const int ntok_stage = dual ? 2 * ntok : ntok;   // activation rows per stage
   // Few output tiles (narrow layers, small batches) leave most SMs idle: split K over gridDim.z.
   const int base_ctas = (int)(w->rows / kUmmaRows) * (int)n_tok_tiles;
   int splits = 1;
@@ -555,15 +583,15 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   if (ts && ntok > 128) acc_stride = 192;
   const int acc_cols = ts ? 512 - 128 * terms : 512;
   int n_acc = 2;                       // a power of two: 16 accumulators up to 32 tokens, 8 at 64, 4 at 128, 2 at 256 in
-  while (n_acc < 16 && 2 * n_acc * acc_stride <= acc_cols) n_acc <<= 1;   // all of tensor memory, fewer beside the weights
+  while (!dual && n_acc < 16 && 2 * n_acc * acc_stride <= acc_cols) n_acc <<= 1;   // all of tensor memory, fewer beside the weights
   const int tmem_cols = ts ? 512 : n_acc * acc_stride;
   // Four A/B stages are what the dequant groups need; everything else goes to the packed-tile ring, because
   // the bytes in flight from HBM (ring slots not being read) are what hides its latency.  A ring slot holds
   // KT = 4 k-tiles of the eight row blocks (eight 4.6 KB copies) when three such slots fit, else KT = 2.
   int stages = kUmmaGroups;
-  if ((budget - 4 * raw_tile) / umma_stage_bytes(terms, ntok, ts) < (size_t)stages)
+  if ((budget - 4 * raw_tile) / umma_stage_bytes(terms, ntok_stage, ts) < (size_t)stages)
     return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: token tile of %d does not fit", ntok);
-  const size_t avail = budget - (size_t)stages * umma_stage_bytes(terms, ntok, ts);
+  const size_t avail = budget - (size_t)stages * umma_stage_bytes(terms, ntok_stage, ts);
   int kt = avail / (4 * raw_tile) >= 3 ? 4 : 2;
   int raw_stages = (int)(avail / ((size_t)kt * raw_tile));
   if (raw_stages > kUmmaMaxRawStages) raw_stages = kUmmaMaxRawStages;
@@ -612,9 +640,9 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
   p.stages = stages;
   p.raw_stages = raw_stages;
   p.kt = kt;
-  const size_t smem = umma_smem_bytes(w->kind, terms, ntok, stages, raw_stages * kt, ts);
+  const size_t smem = umma_smem_bytes(w->kind, terms, ntok_stage, stages, raw_stages * kt, ts);
   if (smem > kSmemMax) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: %zu bytes of shared memory needed", smem);
-  dim3 grid((unsigned)(rows_g / kUmmaRows), (unsigned)((m + ntok - 1) / ntok), (unsigned)splits);
+  dim3 grid((unsigned)(rows_g / kUmmaRows), (unsigned)((m + ntok_stage - 1) / ntok_stage), (unsigned)splits);
   if (grp) {
     grid.y = (unsigned)((grp->max_rows + ntok - 1) / ntok);
     grid.z = (unsigned)((grp->active && grp->max_active < grp->n_groups) ? grp->max_active : grp->n_groups);
@@ -625,7 +653,13 @@ int launch_qgemm_umma(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, size
     return launch_k(ctx, kern, grid, dim3(kUmmaThreads), smem, map, p);
   };
   cudaError_t e;
-  if (ts) {
+  if (dual) {
+    if (splits != 1) return fail(ctx, TQ_EUNSUPPORTED, "tcgen05 GEMM: two token tiles per CTA with K split");
+    if (w->kind == TQ_I8_ROW) e = go(qgemm_umma_kernel<I8_ROW, 1, true, true>);
+    else if (w->kind == TQ_Q4_F16) e = go(qgemm_umma_kernel<Q4_F16, 1, true, true>);
+    else if (w->kind == TQ_Q8_F32) e = go(qgemm_umma_kernel<Q8_F32, 1, true, true>);
+    else e = go(qgemm_umma_kernel<Q4_F32, 1, true, true>);
+  } else if (ts) {
     if (w->kind == TQ_I8_ROW) e = go(qgemm_umma_kernel<I8_ROW, 1, true>);
     else if (w->kind == TQ_Q4_F16) e = terms == 2 ? go(qgemm_umma_kernel<Q4_F16, 2, true>) : go(qgemm_umma_kernel<Q4_F16, 1, true>);
     else if (w->kind == TQ_Q8_F32) e = terms == 2 ? go(qgemm_umma_kernel<Q8_F32, 2, true>) : go(qgemm_umma_kernel<Q8_F32, 1, true>);

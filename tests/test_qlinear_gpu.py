@@ -230,6 +230,8 @@ def test_config1_int4_full_size(dev, orc, m):
     (2, 256, 512, 70),        # Q8 blocks (int8 values, an f32 scale per 32): scaled in the operand like Q4
     (2, 4096, 4096, 64),
     (2, 384, 1024, 300),
+    (1, 14336, 4096, 600),    # bf16 results over many rows and a wave of row tiles: two token tiles per CTA, ragged
+    (3, 14336, 4096, 700),
 ])
 def test_tensor_memory_gemm(dev, orc, kind, rows, cols, m):
     """Many activation rows take the tcgen05 kernel (weights dequantised into 128-byte-swizzled
