@@ -48,74 +48,108 @@ __device__ __forceinline__ int bf16_ulp_exp(unsigned short bits) {   // value is
   return (e ? e : 1) - 127 - 7;
 }
 
+// 16-bit halves: the unit-in-the-last-place exponent (biased by 134) of each bf16 of a pair, or 0x2000 for a zero
+// (a product with a zero operand is zero and does not enter the minimum).
+__device__ __forceinline__ unsigned bf16x2_ulp_code(unsigned pair) {
+  const unsigned e = (pair >> 7) & 0x00FF00FFu;
+  unsigned lo = e & 0xFFFFu, hi = e >> 16;
+  lo = (pair & 0x7FFFu) == 0u ? 0x2000u : (lo ? lo : 1u);
+  hi = (pair & 0x7FFF0000u) == 0u ? 0x2000u : (hi ? hi : 1u);
+  return lo | (hi << 16);
+}
+
+// TT tokens per CTA share every load of a gate row (many tokens: the rows then come from L2 once per TT tokens).
+template <int TT>
 __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, const __nv_bfloat16* wg, int T, int d, int E,
                                                      int top_k, int renorm, int* idx_out, float* w_out, double* logits_out, int* counters) {
-  extern __shared__ __align__(16) unsigned short hs[];   // the token's activations (bf16 bits)
-  __shared__ double lg[kMaxExperts];
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned short* hrow = reinterpret_cast<const unsigned short*>(h) + (size_t)t * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) hs[i] = hrow[i];
+  extern __shared__ __align__(16) unsigned short hs[];   // [TT][d] activations (bf16 bits), then [TT][d] their ulp codes
+  __shared__ double lg[TT][kMaxExperts];
+  unsigned short* he = hs + (size_t)TT * d;
+  const int t0 = blockIdx.x * TT, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = 2 * threadIdx.x; i < TT * d; i += 2 * blockDim.x) {
+    const int tt = i / d, t = t0 + tt;
+    const unsigned pair = t < T ? *reinterpret_cast<const unsigned*>(reinterpret_cast<const unsigned short*>(h) + (size_t)t0 * d + i) : 0u;
+    *reinterpret_cast<unsigned*>(hs + i) = pair;
+    *reinterpret_cast<unsigned*>(he + i) = bf16x2_ulp_code(pair);
+  }
   __syncthreads();
   // gridDim.y CTAs share a token's experts (few tokens would otherwise occupy few SMs); the CTA that
   // finishes last (counter) reads all logits back and makes the selection
   for (int e = blockIdx.y * 8 + warp; e < E; e += 8 * gridDim.y) {
     const unsigned short* wrow = reinterpret_cast<const unsigned short*>(wg) + (size_t)e * d;
-    double acc = 0.0;
-    float sabs = 0.f;
-    int qmin = 1 << 20;
-    auto term = [&](unsigned short hb, unsigned short wb) {
-      const float p = __uint_as_float((unsigned)hb << 16) * __uint_as_float((unsigned)wb << 16);   // 16 bits: exact
-      if (p != 0.f) qmin = min(qmin, bf16_ulp_exp(hb) + bf16_ulp_exp(wb));
-      acc += (double)p;
-      sabs += fabsf(p);          // a bound only (rounded f32 sum; the test below leaves a factor of two)
-    };
-    // eight consecutive k per lane and load, four loads in flight (d is a multiple of 8: checked by the host)
-    for (int k0 = 8 * lane; k0 < d; k0 += 4 * 256) {
-      uint4 wv[4], hv[4];
+    double acc[TT];
+    float sabs[TT];
+    unsigned qm[TT];           // per 16-bit half: the smallest sum of ulp codes over the non-zero products so far
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int k = k0 + 256 * u;
-        wv[u] = k < d ? *reinterpret_cast<const uint4*>(wrow + k) : make_uint4(0u, 0u, 0u, 0u);
-        hv[u] = k < d ? *reinterpret_cast<const uint4*>(hs + k) : make_uint4(0u, 0u, 0u, 0u);
+    for (int tt = 0; tt < TT; ++tt) {
+      acc[tt] = 0.0;
+      sabs[tt] = 0.f;
+      qm[tt] = 0xFFFFFFFFu;
+    }
+    // eight consecutive k per lane and load (d is a multiple of 8: checked by the host)
+#pragma unroll 2
+    for (int k0 = 8 * lane; k0 < d; k0 += 256) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k0);
+      const unsigned ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      float wl[4], wh[4];
+      unsigned wc[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        wl[j] = __uint_as_float(ww[j] << 16);
+        wh[j] = __uint_as_float(ww[j] & 0xFFFF0000u);
+        wc[j] = bf16x2_ulp_code(ww[j]);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const unsigned ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w}, hh[4] = {hv[u].x, hv[u].y, hv[u].z, hv[u].w};
+      for (int tt = 0; tt < TT; ++tt) {
+        const uint4 hv = *reinterpret_cast<const uint4*>(hs + (size_t)tt * d + k0);
+        const uint4 cv = *reinterpret_cast<const uint4*>(he + (size_t)tt * d + k0);
+        const unsigned hh[4] = {hv.x, hv.y, hv.z, hv.w}, hc[4] = {cv.x, cv.y, cv.z, cv.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          term((unsigned short)(hh[j] & 0xFFFFu), (unsigned short)(ww[j] & 0xFFFFu));
-          term((unsigned short)(hh[j] >> 16), (unsigned short)(ww[j] >> 16));
+          const float p0 = __uint_as_float(hh[j] << 16) * wl[j];          // 16 significant bits: exact
+          const float p1 = __uint_as_float(hh[j] & 0xFFFF0000u) * wh[j];
+          acc[tt] += (double)p0;
+          acc[tt] += (double)p1;
+          sabs[tt] += fabsf(p0) + fabsf(p1);   // a bound only (rounded f32 sum; the test below leaves a factor of two)
+          qm[tt] = __viaddmin_u16x2(hc[j], wc[j], qm[tt]);
         }
       }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      sabs += __shfl_xor_sync(0xffffffffu, sabs, o);
-      qmin = min(qmin, __shfl_xor_sync(0xffffffffu, qmin, o));
-    }
-    // NaN or infinity anywhere fails the comparison and takes the reference order as well
-    const bool exact = qmin == (1 << 20) || ((double)sabs < ldexp(1.0, 52 + qmin));
-    if (!exact && lane == 0) {
-      // the reference order, one addition per k: only the additions depend on one another, so the operands come
-      // eight at a time (16-byte loads) and the products of the next eight are formed while these are added
-      acc = 0.0;
-      for (int k0 = 0; k0 < d; k0 += 8) {
-        const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k0), hv = *reinterpret_cast<const uint4*>(hs + k0);
-        const unsigned ww[4] = {wv.x, wv.y, wv.z, wv.w}, hh[4] = {hv.x, hv.y, hv.z, hv.w};
-        double pr[8];
+    for (int tt = 0; tt < TT; ++tt) {
+      unsigned q = min(qm[tt] & 0xFFFFu, qm[tt] >> 16);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          pr[2 * j] = (double)__uint_as_float(hh[j] << 16) * (double)__uint_as_float(ww[j] << 16);
-          pr[2 * j + 1] = (double)__uint_as_float(hh[j] & 0xFFFF0000u) * (double)__uint_as_float(ww[j] & 0xFFFF0000u);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc += pr[j];
+      for (int o = 16; o > 0; o >>= 1) {
+        acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], o);
+        sabs[tt] += __shfl_xor_sync(0xffffffffu, sabs[tt], o);
+        q = min(q, __shfl_xor_sync(0xffffffffu, q, o));
       }
-    }
-    if (lane == 0) {
-      lg[e] = acc;
-      if (logits_out) logits_out[(size_t)t * E + e] = acc;
+      // every non-zero product is a multiple of 2^(q - 268); none at all: the sum is zero.  NaN or infinity anywhere,
+      // or a product that underflowed in f32, fails the comparison and takes the reference order as well
+      const bool exact = q >= 0x2000u || ((double)sabs[tt] < ldexp(1.0, 52 + (int)q - 268));
+      if (!exact && lane == 0) {
+        // the reference order, one addition per k: only the additions depend on one another, so the operands come
+        // eight at a time (16-byte loads) and the products of the next eight are formed while these are added
+        const unsigned short* hrow_s = hs + (size_t)tt * d;
+        double a = 0.0;
+        for (int k0 = 0; k0 < d; k0 += 8) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k0), hv = *reinterpret_cast<const uint4*>(hrow_s + k0);
+          const unsigned ww[4] = {wv.x, wv.y, wv.z, wv.w}, hh[4] = {hv.x, hv.y, hv.z, hv.w};
+          double pr[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            pr[2 * j] = (double)__uint_as_float(hh[j] << 16) * (double)__uint_as_float(ww[j] << 16);
+            pr[2 * j + 1] = (double)__uint_as_float(hh[j] & 0xFFFF0000u) * (double)__uint_as_float(ww[j] & 0xFFFF0000u);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a += pr[j];
+        }
+        acc[tt] = a;
+      }
+      if (lane == 0 && t0 + tt < T) {
+        lg[tt][e] = acc[tt];
+        if (logits_out) logits_out[(size_t)(t0 + tt) * E + e] = acc[tt];
+      }
     }
   }
   if (gridDim.y > 1) {
@@ -123,15 +157,19 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-      last = atomicAdd(&counters[t], 1) == (int)gridDim.y - 1;
-      if (last) counters[t] = 0;
+      last = atomicAdd(&counters[blockIdx.x], 1) == (int)gridDim.y - 1;
+      if (last) counters[blockIdx.x] = 0;
     }
     __syncthreads();
     if (!last) return;
     __threadfence();
-    for (int i = threadIdx.x; i < E; i += blockDim.x) lg[i] = __ldcg(logits_out + (size_t)t * E + i);
+    for (int i = threadIdx.x; i < TT * E; i += blockDim.x)
+      if (t0 + i / E < T) lg[i / E][i % E] = __ldcg(logits_out + (size_t)t0 * E + i);
   }
   __syncthreads();
+  for (int tt = 0; tt < TT && t0 + tt < T; ++tt) {
+  const int t = t0 + tt;
+  const double* lgt = lg[tt];
   // softmax terms in parallel (one f64 exp per thread), their sum in index order by one thread; the maximum and
   // the top-k selection by the first warp (lane l owns experts l, l + 32, ...): the rule is "highest logit first,
   // lowest index on ties, exactly top_k", which a (value, index) tournament reproduces for ordered values.  A NaN
@@ -140,11 +178,11 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
   __shared__ double mx_s;
   __shared__ int pick[kMaxTopK];
   if (warp == 0) {
-    double mx = lg[0];
+    double mx = lgt[0];
     bool any_nan = false;
     for (int i = lane; i < E; i += 32) {
-      mx = fmax(mx, lg[i]);
-      any_nan |= lg[i] != lg[i];
+      mx = fmax(mx, lgt[i]);
+      any_nan |= lgt[i] != lgt[i];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -156,8 +194,8 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
         double bv = 0.0;
         int bi = -1;
         for (int j = 0, i = lane; i < E; ++j, i += 32)
-          if (!((taken >> j) & 1u) && (bi < 0 || lg[i] > bv)) {   // ascending i: '>' keeps the lower index
-            bv = lg[i];
+          if (!((taken >> j) & 1u) && (bi < 0 || lgt[i] > bv)) {   // ascending i: '>' keeps the lower index
+            bv = lgt[i];
             bi = i;
           }
 #pragma unroll
@@ -178,7 +216,7 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
         int best = -1;
         for (int i = 0; i < E; ++i) {
           if ((taken[i >> 6] >> (i & 63)) & 1ull) continue;
-          if (best < 0 || lg[i] > lg[best]) best = i;   // strict '>' keeps the lower index on ties
+          if (best < 0 || lgt[i] > lgt[best]) best = i;   // strict '>' keeps the lower index on ties
         }
         taken[best >> 6] |= 1ull << (best & 63);
         pick[s] = best;
@@ -186,7 +224,7 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < E; i += blockDim.x) ex[i] = exp(lg[i] - mx_s);
+  for (int i = threadIdx.x; i < E; i += blockDim.x) ex[i] = exp(lgt[i] - mx_s);
   __syncthreads();
   if (threadIdx.x == 0) {
     double sum = 0.0;
@@ -201,6 +239,8 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
       idx_out[(size_t)t * top_k + s] = pick[s];
       w_out[(size_t)t * top_k + s] = (float)(renorm ? pw[s] / chosen : pw[s]);
     }
+  }
+  __syncthreads();   // (the selection arrays are reused by the next token)
   }
 }
 
@@ -332,12 +372,16 @@ static int launch_router(tq_ctx* ctx, const void* h_bf16_dev, const void* wg_bf1
              "tq_moe_router: need 1 <= top_k <= n_experts <= %d and top_k <= %d", kMaxExperts, kMaxTopK);
   if (n_tokens == 0) return TQ_OK;
   TQ_REQUIRE(ctx, h_bf16_dev && wg_bf16_dev && idx_out_dev && weight_out_dev, "tq_moe_router: null pointer");
-  const size_t smem = d_model * sizeof(unsigned short);
-  TQ_REQUIRE(ctx, smem <= 48 * 1024 && d_model % 8 == 0 && ((uintptr_t)h_bf16_dev & 15) == 0 && ((uintptr_t)wg_bf16_dev & 15) == 0,
+  TQ_REQUIRE(ctx, d_model <= 24576 && d_model % 8 == 0 && ((uintptr_t)h_bf16_dev & 15) == 0 && ((uintptr_t)wg_bf16_dev & 15) == 0,
              "tq_moe_router: d_model must be a multiple of 8 and at most 24576, arrays 16-byte aligned");
   unsigned gy = 1;
   if (logits_ws && n_tokens <= 64 && n_tokens <= (size_t)kTileCounters) gy = (unsigned)((n_experts + 7) / 8);
-  router_kernel<<<dim3((unsigned)n_tokens, gy), 256, smem, ctx->stream>>>(
+  // four tokens per CTA once there are several waves of CTAs anyway (their activations and ulp codes: 16 d bytes)
+  const bool four = n_tokens >= 1024 && 16 * d_model <= 64 * 1024;
+  const size_t smem = (four ? 4 : 1) * d_model * 2 * sizeof(unsigned short);
+  auto kern = four ? router_kernel<4> : router_kernel<1>;
+  if (smem > 48 * 1024) TQ_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3((unsigned)((n_tokens + (four ? 3 : 0)) / (four ? 4 : 1)), gy), 256, smem, ctx->stream>>>(
       static_cast<const __nv_bfloat16*>(h_bf16_dev), static_cast<const __nv_bfloat16*>(wg_bf16_dev), (int)n_tokens,
       (int)d_model, (int)n_experts, (int)top_k, renormalize, idx_out_dev, weight_out_dev, logits_ws, ctx->dev_err + 1);
   ctx->launches++;
