@@ -58,9 +58,68 @@ __device__ __forceinline__ unsigned bf16x2_ulp_code(unsigned pair) {
   return lo | (hi << 16);
 }
 
+// A gate row times a token in the reference order (one f64 addition per k, ascending), for rows whose additions may
+// round; called by a whole warp, every lane returns the sum.
+__device__ __noinline__ double router_ordered_sum(const unsigned short* hrow_s, const unsigned short* wrow, int d, int lane) {
+  // The reference order, without adding 2048 numbers one after the other.  Lane c takes the c-th run of
+  // consecutive k: its sum from zero in order, the sum of the magnitudes and the smallest ulp code.  Then the runs
+  // are joined in order: while the running sum s is a multiple of 2^qs, a run whose partial sums s + prefix all
+  // stay below 2^53 units of 2^min(qs, its own) adds without any rounding, so its sum is added in one step; a run
+  // that fails this is added term by term (by every lane alike), after which s is only known to be a multiple
+  // of its own last place.  Typically one run holds the offending tiny product.
+  const int CH = ((d + 255) >> 8) << 3;                   // terms per run, a multiple of eight
+  auto products = [&](int k0, double (&pr)[8], unsigned& code) {
+    const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k0), hv = *reinterpret_cast<const uint4*>(hrow_s + k0);
+    const unsigned ww[4] = {wv.x, wv.y, wv.z, wv.w}, hh[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      pr[2 * j] = (double)__uint_as_float(hh[j] << 16) * (double)__uint_as_float(ww[j] << 16);
+      pr[2 * j + 1] = (double)__uint_as_float(hh[j] & 0xFFFF0000u) * (double)__uint_as_float(ww[j] & 0xFFFF0000u);
+      code = __viaddmin_u16x2(bf16x2_ulp_code(hh[j]), bf16x2_ulp_code(ww[j]), code);
+    }
+  };
+  double cs = 0.0, ca = 0.0;
+  unsigned cq2 = 0xFFFFFFFFu;
+  for (int k0 = lane * CH; k0 < min(d, (lane + 1) * CH); k0 += 8) {
+    double pr[8];
+    products(k0, pr, cq2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      cs += pr[j];
+      ca += fabs(pr[j]);
+    }
+  }
+  const unsigned cq = min(cq2 & 0xFFFFu, cq2 >> 16);
+  constexpr int kAny = 1 << 20;                           // "a multiple of anything": s is zero
+  double sr = 0.0;
+  int qs = kAny;
+  for (int c = 0; c < 32; ++c) {
+    const double cs_c = __shfl_sync(0xffffffffu, cs, c), ca_c = __shfl_sync(0xffffffffu, ca, c);
+    const unsigned cq_c = __shfl_sync(0xffffffffu, cq, c);
+    if (c * CH >= d || cq_c >= 0x2000u) continue;         // nothing there, or zeros only: s + 0 = s
+    const int qq = min(qs, (int)cq_c - 268);
+    // integer multiples of 2^qq up to 2^53 of them are representable; the left side is an upper bound up to
+    // the rounding of its own additions, which the factor covers (false for NaN and infinity)
+    if ((fabs(sr) + ca_c) * (1.0 + 0x1p-30) < ldexp(1.0, 53 + qq)) {
+      sr += cs_c;
+      qs = sr == 0.0 ? kAny : qq;
+    } else {
+      for (int k0 = c * CH; k0 < min(d, (c + 1) * CH); k0 += 8) {
+        double pr[8];
+        unsigned unused = 0xFFFFFFFFu;
+        products(k0, pr, unused);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sr += pr[j];
+      }
+      qs = sr == 0.0 ? kAny : (sr == sr && fabs(sr) < 1.7e308 ? ilogb(sr) - 52 : -(1 << 20));
+    }
+  }
+  return sr;
+}
+
 // TT tokens per CTA share every load of a gate row (many tokens: the rows then come from L2 once per TT tokens).
 template <int TT>
-__global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, const __nv_bfloat16* wg, int T, int d, int E,
+__global__ void __launch_bounds__(256, 4) router_kernel(const __nv_bfloat16* h, const __nv_bfloat16* wg, int T, int d, int E,
                                                      int top_k, int renorm, int* idx_out, float* w_out, double* logits_out, int* counters) {
   extern __shared__ __align__(16) unsigned short hs[];   // [TT][d] activations (bf16 bits), then [TT][d] their ulp codes
   __shared__ double lg[TT][kMaxExperts];
@@ -126,26 +185,9 @@ __global__ void __launch_bounds__(256) router_kernel(const __nv_bfloat16* h, con
       }
       // every non-zero product is a multiple of 2^(q - 268); none at all: the sum is zero.  NaN or infinity anywhere,
       // or a product that underflowed in f32, fails the comparison and takes the reference order as well
-      const bool exact = q >= 0x2000u || ((double)sabs[tt] < ldexp(1.0, 52 + (int)q - 268));
-      if (!exact && lane == 0) {
-        // the reference order, one addition per k: only the additions depend on one another, so the operands come
-        // eight at a time (16-byte loads) and the products of the next eight are formed while these are added
-        const unsigned short* hrow_s = hs + (size_t)tt * d;
-        double a = 0.0;
-        for (int k0 = 0; k0 < d; k0 += 8) {
-          const uint4 wv = *reinterpret_cast<const uint4*>(wrow + k0), hv = *reinterpret_cast<const uint4*>(hrow_s + k0);
-          const unsigned ww[4] = {wv.x, wv.y, wv.z, wv.w}, hh[4] = {hv.x, hv.y, hv.z, hv.w};
-          double pr[8];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            pr[2 * j] = (double)__uint_as_float(hh[j] << 16) * (double)__uint_as_float(ww[j] << 16);
-            pr[2 * j + 1] = (double)__uint_as_float(hh[j] & 0xFFFF0000u) * (double)__uint_as_float(ww[j] & 0xFFFF0000u);
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) a += pr[j];
-        }
-        acc[tt] = a;
-      }
+      // (q < 140: some product lies below the normal range of f32, where p0 / p1 above are no longer exact)
+      const bool exact = q >= 0x2000u || (q >= 140u && (double)sabs[tt] < ldexp(1.0, 52 + (int)q - 268));
+      if (!exact) acc[tt] = router_ordered_sum(hs + (size_t)tt * d, wrow, d, lane);
       if (lane == 0 && t0 + tt < T) {
         lg[tt][e] = acc[tt];
         if (logits_out) logits_out[(size_t)(t0 + tt) * E + e] = acc[tt];

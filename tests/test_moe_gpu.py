@@ -70,6 +70,36 @@ def test_router_ties_pick_lower_index(dev, orc):
     assert list(idx[0]) == [2, 1, 4] == list(oi)
 
 
+def test_router_rows_that_round(dev, orc):
+    """Rows whose additions DO round (tiny products beside large ones, cancellation, a huge term): the logits must still
+    be the reference's sequential f64 sum bit for bit, which the kernel gets by joining runs of the row in order."""
+    import tang_b200 as tb
+
+    rng = np.random.default_rng(77)
+    T, d, E, k = 12, 2048, 64, 6
+    h = rng.standard_normal((T, d)).astype(np.float32)
+    wg = (rng.standard_normal((E, d)) * 0.05).astype(np.float32)
+    h[0, 5] = 3e-30
+    h[1, [0, 1000, 2047]] = [1e-25, -2e-31, 7e-28]
+    h[2, :] = 0.0
+    h[2, [3, 900]] = [1e-20, 1.0]
+    h[3, 100:140] *= 1e-22                      # a whole run of tiny terms
+    h[4, [10, 11]] = [3e4, -3e4]                # cancellation: the sum returns to a finer last place
+    wg[:, 10] = 1.0
+    wg[:, 11] = 1.0
+    h[5, 77] = 1e30                             # one huge term: everything after it rounds
+    h[6, ::2] = 0.0
+    wg[7, :] *= 1e-18
+    wg[9, 1234] = 1e-33
+    hb, hf = bf16_round(h)
+    wb, wf = bf16_round(wg)
+    idx, w, lg = tb.moe_router(dev, dev.upload(hb, tb.BF16), dev.upload(wb, tb.BF16), T, d, E, k)
+    for t in range(T):
+        oi, ow, ol = orc.router_f64(hf[t].astype(np.float64), wf.astype(np.float64), E, k)
+        assert np.array_equal(lg[t], ol), t
+        assert list(idx[t]) == list(oi), t
+
+
 def test_renormalised_weights(dev, orc):
     host = HostMoe(np.random.default_rng(6), d=256, ffn=128, n_experts=16, top_k=4, n_shared=0, renorm=True)
     check(dev, orc, host, 9, seed=3)
