@@ -15,7 +15,7 @@
 //     128-byte-swizzled layout UMMA reads.  The product q*scale (15 significant bits) is split into
 //     hi = bf16(q*scale) and lo = bf16(q*scale - hi); hi + lo equals q*scale EXACTLY, so two MMAs
 //     per k-step reproduce exact products with f32 accumulation (TERMS = 2).  TERMS = 1 keeps only
-//     hi (relative weight error 2^-9), for bf16 outputs;
+//     hi (relative weight error at most 2^-8), for bf16 outputs;
 //   * one elected lane of warp 1 (even steps) and of warp 3 (odd steps) issues tcgen05.mma (kind::f16,
 //     bf16 x bf16 -> f32), each into an accumulator of its own, and commits each stage back to the
 //     producers;

@@ -1221,7 +1221,7 @@ int qlinear_fused(tq_ctx* ctx, const tq_qweight* w, const void* x_bf16, const Ql
   if (!swiglu) return tq_qlinear(ctx, w, xin, TQ_BF16, cols, m, y, y_dtype, ldy, nullptr);
   // many rows: the tcgen05 kernel applies silu(gate) * up to its f32 sums itself.  As for every projection, the
   // result type decides the operand terms: exact products (two terms) for f32 results, the product rounded once to
-  // bf16 (2^-9, the step of the result type) for bf16 results.
+  // bf16 (at most 2^-8 relative, half a step of the result type) for bf16 results.
   if (m >= (size_t)umma_min_m(TQ_F32) && umma_supported(w, m) && w->cols == (size_t)w->n_kc * kTileK && ((uintptr_t)xin & 15) == 0)
     return launch_qgemm_umma(ctx, w, xin, cols, m, y, y_dtype, ldy, y_dtype == TQ_F32 ? 2 : 1, nullptr, true);
   TQ_REQUIRE(ctx, gu_tmp != nullptr, "fused linear: no buffer for the gate/up projection");
