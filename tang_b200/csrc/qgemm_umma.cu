@@ -341,7 +341,7 @@ qgemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const UmmaParams p)
         // With t = q*s_lo (7 bits, exact in bf16), hi = fma(q, s_hi, t) is the exact product rounded once;
         // lo = fma(q, s_hi, -hi) + t = q*scale - hi, both steps exact, so hi + lo reproduces the product.
         // (f32 scales keep their first 16 significant bits this way, and with int8 values t itself is rounded to 8
-        // bits: hi + lo is then the product to about 2^-16.)
+        // bits: hi + lo is then the product to within 2^-15 relative.)
         float2 f;
         if (KIND == Q4_F16) f = __half22float2(*reinterpret_cast<const __half2*>(raw + sc_off[i] + 4 * c));
         else f = *reinterpret_cast<const float2*>(raw + sc_off[i] + 8 * c);

@@ -46,3 +46,20 @@ def test_single_term_is_within_half_a_bf16_ulp():
         hi = rn_bf16(q * s_hi + rn_bf16(q * s_lo))
         assert np.all(np.abs(hi - q * scale) <= np.abs(q * scale) * 2.0 ** -8)
         assert np.array_equal(hi, rn_bf16(q * scale))                 # and it IS the correctly rounded product
+
+
+def test_f32_scales_keep_fifteen_bits():
+    """Block formats with f32 scales (tang-infer's native Q4 and Q8 blocks): s_hi + s_lo holds 16 of the scale's 24 bits
+    and q * s_lo is itself rounded for int8 codes, so hi + lo is the product to within 2^-15 relative, not exactly."""
+    rng = np.random.default_rng(0)
+    s = np.concatenate([(rng.random(200000) * 0.009 + 0.001), np.exp2(rng.uniform(-20, 4, 200000))])
+    s = s.astype(np.float32).astype(np.float64)
+    worst = 0.0
+    for q in list(range(-8, 0)) + list(range(1, 8)) + [-127, -101, -77, 64, 85, 100, 127]:
+        s_hi = rn_bf16(s)
+        s_lo = rn_bf16(s - s_hi)
+        t = rn_bf16(q * s_lo)
+        hi = rn_bf16(q * s_hi + t)
+        lo = rn_bf16(rn_bf16(q * s_hi - hi) + t)
+        worst = max(worst, float(np.max(np.abs(hi + lo - q * s) / np.abs(q * s))))
+    assert worst < 2.0 ** -15
